@@ -1,0 +1,8 @@
+"""dtas_b200: sm_100a kernels behind the DTAS (JackWeiw/dtas) Python surface.
+
+Mirrors the reference package surface (python/dtas/__init__.py:1-8): `arch`, `Config`,
+`get_log_level` / `set_log_level`; plus the entry points `Engine`
+(python/dtas/engine/tuner.py:22) and `load_module_from_file`
+(python/dtas/codegen/runtime_packer.py:260).
+"""
+from .logging import get_log_level, set_log_level  # noqa: F401

@@ -1,0 +1,120 @@
+// Shared host/device helpers of the dtas_b200 kernel library (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+#include <string.h>
+#include <atomic>
+
+#include "../../include/dtas_b200.h"
+
+namespace dtas {
+
+constexpr int kNumBuckets = 32;        // 32 buckets of 256 rows: m = 1 .. 8192, clamped above
+constexpr int kBucketWidth = 256;      // the reference's range_div_factor (engine/tuner.py:53-58)
+
+// ---- error reporting -------------------------------------------------------
+void set_error(const char* fmt, ...);
+extern std::atomic<int64_t> g_launches;
+
+#define DTAS_FAIL(code, ...)        \
+  do {                              \
+    ::dtas::set_error(__VA_ARGS__); \
+    return (code);                  \
+  } while (0)
+
+#define DTAS_CUDA(expr)                                                          \
+  do {                                                                           \
+    cudaError_t _e = (expr);                                                     \
+    if (_e != cudaSuccess) {                                                     \
+      ::dtas::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e),  \
+                        __FILE__, __LINE__);                                     \
+      return DTAS_ECUDA;                                                         \
+    }                                                                            \
+  } while (0)
+
+// Counts the launch and turns a launch error into DTAS_ECUDA.
+inline int after_launch(const char* what) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("launch of %s failed: %s", what, cudaGetErrorString(e));
+    return DTAS_ECUDA;
+  }
+  return DTAS_OK;
+}
+
+// ---- per-device context ------------------------------------------------------
+struct DeviceCtx {
+  bool ready = false;
+  int sm_count = 0;
+  // split-K scratch of the GEMM: fp32 partial tiles + one arrival counter per output tile
+  float* splitk_ws = nullptr;
+  size_t splitk_ws_bytes = 0;
+  int* tile_counters = nullptr;
+  int n_tile_counters = 0;
+  int* status = nullptr;  // device status word written by bounded waits that gave up
+};
+int get_ctx(int device, DeviceCtx** out);           // creates on first use (device must be current)
+int ensure_splitk_scratch(DeviceCtx* ctx);          // cudaMalloc on first use
+
+// Makes `device` current for the scope and restores the previous device.
+struct DeviceGuard {
+  int prev = -1;
+  bool switched = false;
+  int enter(int device) {
+    DTAS_CUDA(cudaGetDevice(&prev));
+    if (prev != device) {
+      DTAS_CUDA(cudaSetDevice(device));
+      switched = true;
+    }
+    return DTAS_OK;
+  }
+  ~DeviceGuard() {
+    if (switched) cudaSetDevice(prev);
+  }
+};
+
+inline int bucket_of(int64_t m) {
+  if (m <= 0) return -1;
+  int64_t b = (m - 1) / kBucketWidth;
+  return (int)(b >= kNumBuckets ? kNumBuckets - 1 : b);
+}
+
+inline int dtype_size(int dt) {
+  switch (dt) {
+    case DTAS_F16: return 2;
+    case DTAS_F32: return 4;
+    case DTAS_I8: return 1;
+    default: return 0;
+  }
+}
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- launchers implemented by the per-class translation units --------------------
+int launch_cast(const void* a, void* out, int64_t n, int src, int dst, const DeviceCtx* ctx,
+                cudaStream_t st, int bucket);
+int launch_add(const void* a, const void* b, void* out, int64_t n, int dt, const DeviceCtx* ctx,
+               cudaStream_t st, int bucket);
+int launch_copy(const void* a, void* out, int64_t nbytes, const DeviceCtx* ctx, cudaStream_t st,
+                int bucket);
+const char* ew_variant_name(const char* op, int64_t m, int64_t n_cols, const DeviceCtx* ctx);
+
+enum RowOp { ROW_RMSNORM = 0, ROW_SOFTMAX = 1, ROW_LAYERNORM = 2 };
+int launch_row_op(RowOp op, const void* x, const void* p0, const void* p1, void* y, int64_t m,
+                  int64_t n_cols, float eps, int in_dtype, const DeviceCtx* ctx, cudaStream_t st);
+void row_variant_name(RowOp op, int64_t m, int64_t n_cols, char* buf, int len);
+
+int launch_gemv(const void* x, const void* w, const void* bias, void* y, int64_t n, int64_t k,
+                const DeviceCtx* ctx, cudaStream_t st);
+void gemv_variant_name(int64_t n, int64_t k, const DeviceCtx* ctx, char* buf, int len);
+
+int launch_gemm(const void* x, const void* w, const void* bias, void* y, int64_t m, int64_t n,
+                int64_t k, int64_t ldy, DeviceCtx* ctx, cudaStream_t st);
+void gemm_variant_name(int64_t m, int64_t n, int64_t k, const DeviceCtx* ctx, char* buf, int len);
+void gemm_set_override(int bn, int split_k);
+
+}  // namespace dtas

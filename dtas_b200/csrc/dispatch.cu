@@ -1,0 +1,262 @@
+// C ABI of the library: argument checks, device / stream handling, m-bucket lookup and
+// the call into the per-class launcher.
+//
+// This file is the hand-written counterpart of the host code the reference generates per
+// PrimFunc (python/dtas/codegen/code_gen.py:242-405, an instance being
+// experiment/dtas_tuned/elementwise/cast/top10_256/host.cc:42-131): unpack arguments,
+// select the device, index = min(n/256, last), info = call_table[index_table[index]],
+// launch.  The bucket -> kernel-variant tables live next to the kernels they select
+// (ew_cfg, row_cfg, pick_wpr, plan_gemm).
+#include <mutex>
+
+#include "common.cuh"
+
+namespace dtas {
+
+static thread_local char tl_error[512] = {0};
+std::atomic<int64_t> g_launches{0};
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(tl_error, sizeof(tl_error), fmt, ap);
+  va_end(ap);
+}
+
+static constexpr int kMaxDevices = 64;
+static DeviceCtx g_ctx[kMaxDevices];
+static std::mutex g_ctx_mutex;
+
+int get_ctx(int device, DeviceCtx** out) {
+  if (device < 0 || device >= kMaxDevices) DTAS_FAIL(DTAS_EINVAL, "device ordinal %d out of range", device);
+  DeviceCtx* c = &g_ctx[device];
+  if (!c->ready) {
+    std::lock_guard<std::mutex> lock(g_ctx_mutex);
+    if (!c->ready) {
+      cudaDeviceProp prop;
+      DTAS_CUDA(cudaGetDeviceProperties(&prop, device));
+      if (prop.major != 10)
+        DTAS_FAIL(DTAS_EUNSUPPORTED, "device %d is sm_%d%d; this library only carries sm_100a code", device,
+                  prop.major, prop.minor);
+      c->sm_count = prop.multiProcessorCount;
+      DTAS_CUDA(cudaMalloc(&c->status, sizeof(int)));
+      DTAS_CUDA(cudaMemset(c->status, 0, sizeof(int)));
+      c->ready = true;
+    }
+  }
+  *out = c;
+  return DTAS_OK;
+}
+
+namespace {
+
+struct Call {
+  DeviceGuard guard;
+  DeviceCtx* ctx = nullptr;
+  cudaStream_t stream = nullptr;
+  int begin(int device, void* stream_handle) {
+    int rc = guard.enter(device);
+    if (rc != DTAS_OK) return rc;
+    stream = static_cast<cudaStream_t>(stream_handle);
+    return get_ctx(device, &ctx);
+  }
+};
+
+int check_rows_cols(const char* op, int64_t m, int64_t n_cols) {
+  if (m <= 0) DTAS_FAIL(DTAS_EINVAL, "%s: dynamic dim m must be > 0, got %lld", op, (long long)m);
+  if (n_cols <= 0) DTAS_FAIL(DTAS_EINVAL, "%s: n_cols must be > 0, got %lld", op, (long long)n_cols);
+  if (n_cols > ((int64_t)1 << 30) || m > ((int64_t)1 << 40) / n_cols)
+    DTAS_FAIL(DTAS_EINVAL, "%s: shape [%lld, %lld] too large", op, (long long)m, (long long)n_cols);
+  return DTAS_OK;
+}
+
+int op_index(const char* op) {
+  static const char* names[] = {"cast", "add", "copy", "rms_norm", "softmax", "layer_norm", "gemv", "gemm"};
+  if (op == nullptr) return -1;
+  for (int i = 0; i < 8; ++i)
+    if (strcmp(op, names[i]) == 0) return i;
+  return -1;
+}
+
+}  // namespace
+}  // namespace dtas
+
+using namespace dtas;
+
+#define DTAS_NONNULL(op, p) \
+  if ((p) == nullptr) DTAS_FAIL(DTAS_EINVAL, "%s: argument %s is NULL", op, #p)
+
+extern "C" {
+
+int dtas_cast(const void* a, void* out, int64_t m, int64_t n_cols, int src_dtype, int dst_dtype,
+              int device, void* stream) {
+  DTAS_NONNULL("cast", a);
+  DTAS_NONNULL("cast", out);
+  int rc = check_rows_cols("cast", m, n_cols);
+  if (rc) return rc;
+  Call c;
+  if ((rc = c.begin(device, stream))) return rc;
+  return launch_cast(a, out, m * n_cols, src_dtype, dst_dtype, c.ctx, c.stream, bucket_of(m));
+}
+
+int dtas_add(const void* a, const void* b, void* out, int64_t m, int64_t n_cols, int dtype, int device,
+             void* stream) {
+  DTAS_NONNULL("add", a);
+  DTAS_NONNULL("add", b);
+  DTAS_NONNULL("add", out);
+  int rc = check_rows_cols("add", m, n_cols);
+  if (rc) return rc;
+  Call c;
+  if ((rc = c.begin(device, stream))) return rc;
+  return launch_add(a, b, out, m * n_cols, dtype, c.ctx, c.stream, bucket_of(m));
+}
+
+int dtas_copy(const void* a, void* out, int64_t m, int64_t n_cols, int dtype, int device, void* stream) {
+  DTAS_NONNULL("copy", a);
+  DTAS_NONNULL("copy", out);
+  int rc = check_rows_cols("copy", m, n_cols);
+  if (rc) return rc;
+  const int es = dtype_size(dtype);
+  if (es == 0) DTAS_FAIL(DTAS_EUNSUPPORTED, "copy: unknown dtype %d", dtype);
+  Call c;
+  if ((rc = c.begin(device, stream))) return rc;
+  return launch_copy(a, out, m * n_cols * es, c.ctx, c.stream, bucket_of(m));
+}
+
+int dtas_rms_norm(const void* x, const void* weight, void* y, int64_t m, int64_t n_cols, float eps,
+                  int in_dtype, int device, void* stream) {
+  DTAS_NONNULL("rms_norm", x);
+  DTAS_NONNULL("rms_norm", weight);
+  DTAS_NONNULL("rms_norm", y);
+  int rc = check_rows_cols("rms_norm", m, n_cols);
+  if (rc) return rc;
+  Call c;
+  if ((rc = c.begin(device, stream))) return rc;
+  return launch_row_op(ROW_RMSNORM, x, weight, nullptr, y, m, n_cols, eps, in_dtype, c.ctx, c.stream);
+}
+
+int dtas_softmax(const void* x, void* y, int64_t m, int64_t n_cols, int in_dtype, int device, void* stream) {
+  DTAS_NONNULL("softmax", x);
+  DTAS_NONNULL("softmax", y);
+  int rc = check_rows_cols("softmax", m, n_cols);
+  if (rc) return rc;
+  Call c;
+  if ((rc = c.begin(device, stream))) return rc;
+  return launch_row_op(ROW_SOFTMAX, x, nullptr, nullptr, y, m, n_cols, 0.f, in_dtype, c.ctx, c.stream);
+}
+
+int dtas_layer_norm(const void* x, const void* gamma, const void* beta, void* y, int64_t m, int64_t n_cols,
+                    float eps, int in_dtype, int device, void* stream) {
+  DTAS_NONNULL("layer_norm", x);
+  DTAS_NONNULL("layer_norm", gamma);
+  DTAS_NONNULL("layer_norm", beta);
+  DTAS_NONNULL("layer_norm", y);
+  int rc = check_rows_cols("layer_norm", m, n_cols);
+  if (rc) return rc;
+  Call c;
+  if ((rc = c.begin(device, stream))) return rc;
+  return launch_row_op(ROW_LAYERNORM, x, gamma, beta, y, m, n_cols, eps, in_dtype, c.ctx, c.stream);
+}
+
+int dtas_gemv(const void* x, const void* w, const void* bias, void* y, int64_t n, int64_t k, int dtype,
+              int device, void* stream) {
+  DTAS_NONNULL("gemv", x);
+  DTAS_NONNULL("gemv", w);
+  DTAS_NONNULL("gemv", y);
+  if (n <= 0 || k <= 0) DTAS_FAIL(DTAS_EINVAL, "gemv: n and k must be > 0, got n=%lld k=%lld", (long long)n, (long long)k);
+  if (dtype != DTAS_F16) DTAS_FAIL(DTAS_EUNSUPPORTED, "gemv: only fp16 is implemented (dtype %d)", dtype);
+  Call c;
+  int rc;
+  if ((rc = c.begin(device, stream))) return rc;
+  return launch_gemv(x, w, bias, y, n, k, c.ctx, c.stream);
+}
+
+int dtas_gemm_nt(const void* x, const void* w, const void* bias, void* y, int64_t m, int64_t n, int64_t k,
+                 int64_t ldy, int dtype, int device, void* stream) {
+  DTAS_NONNULL("gemm", x);
+  DTAS_NONNULL("gemm", w);
+  DTAS_NONNULL("gemm", y);
+  if (m <= 0) DTAS_FAIL(DTAS_EINVAL, "gemm: dynamic dim m must be > 0, got %lld", (long long)m);
+  if (n <= 0 || k <= 0) DTAS_FAIL(DTAS_EINVAL, "gemm: n and k must be > 0, got n=%lld k=%lld", (long long)n, (long long)k);
+  if (ldy < n) DTAS_FAIL(DTAS_EINVAL, "gemm: ldy (%lld) must be >= n (%lld)", (long long)ldy, (long long)n);
+  if (dtype != DTAS_F16) DTAS_FAIL(DTAS_EUNSUPPORTED, "gemm: only fp16 is implemented (dtype %d)", dtype);
+  Call c;
+  int rc;
+  if ((rc = c.begin(device, stream))) return rc;
+  return launch_gemm(x, w, bias, y, m, n, k, ldy, c.ctx, c.stream);
+}
+
+int dtas_bucket_of(const char* op, int64_t m) {
+  if (op_index(op) < 0) return -1;
+  return bucket_of(m);
+}
+
+int dtas_bucket_count(const char* op) { return op_index(op) < 0 ? -1 : kNumBuckets; }
+
+int dtas_variant_of(const char* op, int64_t m, int64_t n, int64_t k, int device, char* buf, int buf_len) {
+  if (buf == nullptr || buf_len <= 0) DTAS_FAIL(DTAS_EINVAL, "variant_of: no buffer");
+  const int idx = op_index(op);
+  if (idx < 0) DTAS_FAIL(DTAS_EINVAL, "variant_of: unknown op '%s'", op ? op : "(null)");
+  if (m <= 0 || n <= 0) DTAS_FAIL(DTAS_EINVAL, "variant_of: m and n must be > 0");
+  // The SM count only matters for the grid caps; without a device the B200 count is assumed.
+  DeviceCtx fake;
+  fake.sm_count = 148;
+  const DeviceCtx* ctx = &fake;
+  if (device >= 0 && device < kMaxDevices && g_ctx[device].ready) ctx = &g_ctx[device];
+  switch (idx) {
+    case 0: case 1: case 2:
+      snprintf(buf, buf_len, "%s", ew_variant_name(op, m, n, ctx));
+      break;
+    case 3: row_variant_name(ROW_RMSNORM, m, n, buf, buf_len); break;
+    case 4: row_variant_name(ROW_SOFTMAX, m, n, buf, buf_len); break;
+    case 5: row_variant_name(ROW_LAYERNORM, m, n, buf, buf_len); break;
+    case 6: gemv_variant_name(n, k, ctx, buf, buf_len); break;
+    default: gemm_variant_name(m, n, k, ctx, buf, buf_len); break;
+  }
+  return DTAS_OK;
+}
+
+int dtas_gemm_set_override(int bn, int split_k) {
+  if (!(bn == 0 || bn == 64 || bn == 128 || bn == 256)) DTAS_FAIL(DTAS_EINVAL, "gemm override: bn must be 0, 64, 128 or 256");
+  if (split_k < 0 || split_k > 64) DTAS_FAIL(DTAS_EINVAL, "gemm override: split_k must be in [0, 64]");
+  gemm_set_override(bn, split_k);
+  return DTAS_OK;
+}
+
+const char* dtas_last_error(void) { return tl_error; }
+
+int64_t dtas_launch_count(void) { return g_launches.load(); }
+
+int dtas_poll_status(int device) {
+  if (device < 0 || device >= kMaxDevices || !g_ctx[device].ready) return DTAS_OK;
+  DeviceGuard g;
+  int rc = g.enter(device);
+  if (rc) return rc;
+  int host = 0;
+  DTAS_CUDA(cudaDeviceSynchronize());
+  DTAS_CUDA(cudaMemcpy(&host, g_ctx[device].status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (host != 0) {
+    DTAS_CUDA(cudaMemset(g_ctx[device].status, 0, sizeof(int)));
+    DTAS_FAIL(DTAS_ETIMEOUT, "a bounded device-side wait gave up (code 0x%x)", host);
+  }
+  return DTAS_OK;
+}
+
+int dtas_shutdown(void) {
+  std::lock_guard<std::mutex> lock(g_ctx_mutex);
+  for (int d = 0; d < kMaxDevices; ++d) {
+    DeviceCtx& c = g_ctx[d];
+    if (!c.ready) continue;
+    DeviceGuard g;
+    if (g.enter(d) != DTAS_OK) continue;
+    if (c.splitk_ws) cudaFree(c.splitk_ws);
+    if (c.tile_counters) cudaFree(c.tile_counters);
+    if (c.status) cudaFree(c.status);
+    c = DeviceCtx();
+  }
+  return DTAS_OK;
+}
+
+const char* dtas_version(void) { return "dtas_b200 0.1.0 sm_100a"; }
+
+}  // extern "C"

@@ -1,0 +1,271 @@
+// Elementwise class: cast, add, copy.
+//
+// Counterpart of the kernels the reference generates from TIRElementwiseScheduler
+// (python/dtas/schedule/tir_elementwise.py:22-47): the flat index space is cut into
+// [grid, iterations, 256 threads, vector], with the vector width capped at 128 bits
+// (python/dtas/policy/elementwise_config_emiter.py:9-33).  Here that is one
+// grid-stride kernel template: every thread moves UNROLL 16-byte vectors per
+// iteration (all loads issued before the first store, so a thread keeps
+// UNROLL x 16..32 bytes in flight), the grid is capped at a per-bucket multiple of
+// the SM count, and the ragged tail and unaligned buffers take a scalar path.
+//
+// Algorithmic HBM bytes per element: cast f32->f16 6, cast f16->f32 6, add 3*size,
+// copy 2*size.  The kernels are pure streams: their roofline is HBM bandwidth.
+#include "common.cuh"
+
+namespace dtas {
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
+__device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(uint4* p, uint4 v) { __stcs(p, v); }
+__device__ __forceinline__ void st_stream(float4* p, float4 v) { __stcs(p, v); }
+
+__device__ __forceinline__ uint32_t pack_half2_rn(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);  // round-to-nearest-even, like a C cast
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ float2 unpack_half2(uint32_t v) {
+  return __half22float2(*reinterpret_cast<__half2*>(&v));
+}
+__device__ __forceinline__ uint32_t hadd2_bits(uint32_t a, uint32_t b) {
+  __half2 r = __hadd2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
+// Each Op describes one vector of work: Reg = registers held between load and store,
+// kVec = elements per vector, scalar() = the one-element fallback.
+struct CastF32F16 {
+  static constexpr int kVec = 8;
+  const float* a;
+  __half* o;
+  struct Reg { float4 lo, hi; };
+  __device__ __forceinline__ void load(Reg& r, int64_t v) const {
+    const float4* p = reinterpret_cast<const float4*>(a) + 2 * v;
+    r.lo = ld_stream(p);
+    r.hi = ld_stream(p + 1);
+  }
+  __device__ __forceinline__ void store(const Reg& r, int64_t v) const {
+    uint4 w;
+    w.x = pack_half2_rn(r.lo.x, r.lo.y);
+    w.y = pack_half2_rn(r.lo.z, r.lo.w);
+    w.z = pack_half2_rn(r.hi.x, r.hi.y);
+    w.w = pack_half2_rn(r.hi.z, r.hi.w);
+    st_stream(reinterpret_cast<uint4*>(o) + v, w);
+  }
+  __device__ __forceinline__ void scalar(int64_t i) const { o[i] = __float2half_rn(a[i]); }
+};
+
+struct CastF16F32 {
+  static constexpr int kVec = 8;
+  const __half* a;
+  float* o;
+  struct Reg { uint4 v; };
+  __device__ __forceinline__ void load(Reg& r, int64_t v) const {
+    r.v = ld_stream(reinterpret_cast<const uint4*>(a) + v);
+  }
+  __device__ __forceinline__ void store(const Reg& r, int64_t v) const {
+    float2 f0 = unpack_half2(r.v.x), f1 = unpack_half2(r.v.y);
+    float2 f2 = unpack_half2(r.v.z), f3 = unpack_half2(r.v.w);
+    float4* p = reinterpret_cast<float4*>(o) + 2 * v;
+    st_stream(p, make_float4(f0.x, f0.y, f1.x, f1.y));
+    st_stream(p + 1, make_float4(f2.x, f2.y, f3.x, f3.y));
+  }
+  __device__ __forceinline__ void scalar(int64_t i) const { o[i] = __half2float(a[i]); }
+};
+
+struct AddF16 {
+  static constexpr int kVec = 8;
+  const __half *a, *b;
+  __half* o;
+  struct Reg { uint4 x, y; };
+  __device__ __forceinline__ void load(Reg& r, int64_t v) const {
+    r.x = ld_stream(reinterpret_cast<const uint4*>(a) + v);
+    r.y = ld_stream(reinterpret_cast<const uint4*>(b) + v);
+  }
+  __device__ __forceinline__ void store(const Reg& r, int64_t v) const {
+    uint4 w;
+    w.x = hadd2_bits(r.x.x, r.y.x);
+    w.y = hadd2_bits(r.x.y, r.y.y);
+    w.z = hadd2_bits(r.x.z, r.y.z);
+    w.w = hadd2_bits(r.x.w, r.y.w);
+    st_stream(reinterpret_cast<uint4*>(o) + v, w);
+  }
+  __device__ __forceinline__ void scalar(int64_t i) const { o[i] = __hadd(a[i], b[i]); }
+};
+
+struct AddF32 {
+  static constexpr int kVec = 4;
+  const float *a, *b;
+  float* o;
+  struct Reg { float4 x, y; };
+  __device__ __forceinline__ void load(Reg& r, int64_t v) const {
+    r.x = ld_stream(reinterpret_cast<const float4*>(a) + v);
+    r.y = ld_stream(reinterpret_cast<const float4*>(b) + v);
+  }
+  __device__ __forceinline__ void store(const Reg& r, int64_t v) const {
+    st_stream(reinterpret_cast<float4*>(o) + v,
+              make_float4(__fadd_rn(r.x.x, r.y.x), __fadd_rn(r.x.y, r.y.y),
+                          __fadd_rn(r.x.z, r.y.z), __fadd_rn(r.x.w, r.y.w)));
+  }
+  __device__ __forceinline__ void scalar(int64_t i) const { o[i] = __fadd_rn(a[i], b[i]); }
+};
+
+struct AddI8 {  // two's-complement wrap-around per byte, like the int8 PrimFunc
+  static constexpr int kVec = 16;
+  const int8_t *a, *b;
+  int8_t* o;
+  struct Reg { uint4 x, y; };
+  __device__ __forceinline__ void load(Reg& r, int64_t v) const {
+    r.x = ld_stream(reinterpret_cast<const uint4*>(a) + v);
+    r.y = ld_stream(reinterpret_cast<const uint4*>(b) + v);
+  }
+  __device__ __forceinline__ void store(const Reg& r, int64_t v) const {
+    uint4 w;
+    w.x = __vadd4(r.x.x, r.y.x);
+    w.y = __vadd4(r.x.y, r.y.y);
+    w.z = __vadd4(r.x.z, r.y.z);
+    w.w = __vadd4(r.x.w, r.y.w);
+    st_stream(reinterpret_cast<uint4*>(o) + v, w);
+  }
+  __device__ __forceinline__ void scalar(int64_t i) const {
+    o[i] = (int8_t)((uint8_t)a[i] + (uint8_t)b[i]);
+  }
+};
+
+struct CopyBytes {
+  static constexpr int kVec = 16;
+  const uint8_t* a;
+  uint8_t* o;
+  struct Reg { uint4 v; };
+  __device__ __forceinline__ void load(Reg& r, int64_t v) const {
+    r.v = ld_stream(reinterpret_cast<const uint4*>(a) + v);
+  }
+  __device__ __forceinline__ void store(const Reg& r, int64_t v) const {
+    st_stream(reinterpret_cast<uint4*>(o) + v, r.v);
+  }
+  __device__ __forceinline__ void scalar(int64_t i) const { o[i] = a[i]; }
+};
+
+// Vector path: n_vec full vectors, then (n_elem - n_vec*kVec) tail elements handled
+// by the first threads of block 0.
+template <typename Op, int UNROLL>
+__global__ void __launch_bounds__(kThreads) ew_vec_kernel(const Op op, int64_t n_vec,
+                                                          int64_t n_elem) {
+  constexpr int64_t kTile = (int64_t)kThreads * UNROLL;
+  for (int64_t base = (int64_t)blockIdx.x * kTile; base < n_vec;
+       base += (int64_t)gridDim.x * kTile) {
+    typename Op::Reg r[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      int64_t v = base + (int64_t)u * kThreads + threadIdx.x;
+      if (v < n_vec) op.load(r[u], v);
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      int64_t v = base + (int64_t)u * kThreads + threadIdx.x;
+      if (v < n_vec) op.store(r[u], v);
+    }
+  }
+  if (blockIdx.x == 0) {
+    int64_t i = n_vec * Op::kVec + threadIdx.x;
+    if (i < n_elem) op.scalar(i);  // tail is shorter than one vector (< 256 elements)
+  }
+}
+
+// Scalar path for buffers that are not 16-byte aligned.
+template <typename Op>
+__global__ void __launch_bounds__(kThreads) ew_scalar_kernel(const Op op, int64_t n_elem) {
+  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n_elem;
+       i += (int64_t)gridDim.x * kThreads)
+    op.scalar(i);
+}
+
+// Per-bucket launch shape, the static counterpart of the reference's per-range best
+// ElementwiseConfig (python/dtas/common/config.py:407-429).  Small buckets spread the
+// few vectors over as many CTAs as possible (latency-bound); large buckets use deeper
+// per-thread unrolling and a grid capped at a multiple of the SM count.
+struct EwCfg {
+  int unroll;
+  int ctas_per_sm;
+};
+inline EwCfg ew_cfg(int bucket) {
+  if (bucket <= 0) return {1, 8};
+  if (bucket <= 3) return {2, 8};
+  return {4, 8};
+}
+
+template <typename Op>
+int launch_ew(const Op& op, int64_t n_elem, bool aligned, const DeviceCtx* ctx, cudaStream_t st,
+              int bucket, const char* name) {
+  if (!aligned) {
+    int64_t blocks = (n_elem + kThreads - 1) / kThreads;
+    int64_t cap = (int64_t)ctx->sm_count * 8;
+    ew_scalar_kernel<Op><<<(unsigned)(blocks < cap ? blocks : cap), kThreads, 0, st>>>(op, n_elem);
+    return after_launch(name);
+  }
+  const int64_t n_vec = n_elem / Op::kVec;
+  const EwCfg cfg = ew_cfg(bucket);
+  const int64_t tile = (int64_t)kThreads * cfg.unroll;
+  int64_t blocks = (n_vec + tile - 1) / tile;
+  const int64_t cap = (int64_t)ctx->sm_count * cfg.ctas_per_sm;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  switch (cfg.unroll) {
+    case 1: ew_vec_kernel<Op, 1><<<(unsigned)blocks, kThreads, 0, st>>>(op, n_vec, n_elem); break;
+    case 2: ew_vec_kernel<Op, 2><<<(unsigned)blocks, kThreads, 0, st>>>(op, n_vec, n_elem); break;
+    default: ew_vec_kernel<Op, 4><<<(unsigned)blocks, kThreads, 0, st>>>(op, n_vec, n_elem); break;
+  }
+  return after_launch(name);
+}
+
+}  // namespace
+
+int launch_cast(const void* a, void* out, int64_t n, int src, int dst, const DeviceCtx* ctx,
+                cudaStream_t st, int bucket) {
+  const bool al = aligned16(a) && aligned16(out);
+  if (src == DTAS_F32 && dst == DTAS_F16)
+    return launch_ew(CastF32F16{(const float*)a, (__half*)out}, n, al, ctx, st, bucket,
+                     "cast_f32_f16");
+  if (src == DTAS_F16 && dst == DTAS_F32)
+    return launch_ew(CastF16F32{(const __half*)a, (float*)out}, n, al, ctx, st, bucket,
+                     "cast_f16_f32");
+  DTAS_FAIL(DTAS_EUNSUPPORTED, "cast: unsupported dtype pair %d -> %d", src, dst);
+}
+
+int launch_add(const void* a, const void* b, void* out, int64_t n, int dt, const DeviceCtx* ctx,
+               cudaStream_t st, int bucket) {
+  const bool al = aligned16(a) && aligned16(b) && aligned16(out);
+  switch (dt) {
+    case DTAS_F16:
+      return launch_ew(AddF16{(const __half*)a, (const __half*)b, (__half*)out}, n, al, ctx, st,
+                       bucket, "add_f16");
+    case DTAS_F32:
+      return launch_ew(AddF32{(const float*)a, (const float*)b, (float*)out}, n, al, ctx, st,
+                       bucket, "add_f32");
+    case DTAS_I8:
+      return launch_ew(AddI8{(const int8_t*)a, (const int8_t*)b, (int8_t*)out}, n, al, ctx, st,
+                       bucket, "add_i8");
+  }
+  DTAS_FAIL(DTAS_EUNSUPPORTED, "add: unsupported dtype %d", dt);
+}
+
+int launch_copy(const void* a, void* out, int64_t nbytes, const DeviceCtx* ctx, cudaStream_t st,
+                int bucket) {
+  const bool al = aligned16(a) && aligned16(out);
+  return launch_ew(CopyBytes{(const uint8_t*)a, (uint8_t*)out}, nbytes, al, ctx, st, bucket,
+                   "copy");
+}
+
+const char* ew_variant_name(const char* op, int64_t m, int64_t, const DeviceCtx*) {
+  (void)op;
+  switch (ew_cfg(bucket_of(m)).unroll) {
+    case 1: return "ew_vec16_unroll1";
+    case 2: return "ew_vec16_unroll2";
+    default: return "ew_vec16_unroll4";
+  }
+}
+
+}  // namespace dtas

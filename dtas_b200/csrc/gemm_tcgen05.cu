@@ -1,0 +1,735 @@
+// Dynamic-m NT GEMM on the 5th-generation tensor cores:
+//   Y[m,n] = X[m,k] * W[n,k]^T (+ bias[n]),  fp16 operands, fp32 accumulation in TMEM, fp16 out.
+//
+// Counterpart of the reference's tensor-core GEMM schedule
+// (python/dtas/schedule/tir_wmma.py:20-222: block tile, shared-memory double buffering of
+// both operands, software pipeline, L2-friendly block swizzle, accumulator written back
+// through a fused epilogue; tile choice per m-range by the roofline/wave model of
+// python/dtas/policy/wmma_config_emiter.py:148-353).  Nothing of nvcuda::wmma survives:
+//
+//   * operands arrive by TMA (cp.async.bulk.tensor, 128-byte swizzle) into a ring of
+//     shared-memory stages guarded by mbarriers; rows >= m and columns >= k are
+//     zero-filled by the TMA unit, so no padding pass over X is needed for ragged m;
+//   * one elected thread issues tcgen05.mma (M=128, N=BN, K=16, kind::f16) with both
+//     operands read from shared memory through matrix descriptors; the 128 x BN fp32
+//     accumulator lives in tensor memory, double-buffered so the epilogue of one tile
+//     overlaps the main loop of the next;
+//   * four epilogue warps pull the accumulator out with tcgen05.ld (lane = row,
+//     32 columns per instruction), add the bias, round to fp16 and store;
+//   * the kernel is persistent: at most one CTA per SM walks a list of
+//     (m-tile, n-tile, k-split) work items ordered so that CTAs running at the same time
+//     share X and W tiles in L2;
+//   * tall-skinny m is HBM-bound on W, so small-m buckets cut K into `splits` slices to
+//     put every SM to work: each slice stores its fp32 partial tile to a workspace, and
+//     the last CTA to arrive at a tile (atomic ticket, no spinning) sums the slices in
+//     slice order - deterministic - and writes fp16.
+//
+// No TMA multicast is used anywhere: every CTA loads its own operand tiles.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocator + MMA issuer,
+// warps 2..5 = epilogue (warp w owns TMEM lanes 32*(w%4) .. +31).
+//
+// Every mbarrier wait is bounded: after about a second without progress the waiting role
+// records a code in the device status word and leaves its loop; the CTA then drains,
+// frees its tensor memory and exits.
+//
+// Work per launch: 2*m*n*k flop; bytes 2*(m*k + n*k + m*n).  Bound: tensor pipe for
+// m >= ~1024, HBM (W stream) for small m.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace dtas {
+namespace {
+
+constexpr int BM = 128;         // rows of X per tile = MMA M
+constexpr int BK = 64;          // k elements per stage = one 128-byte swizzle row of fp16
+constexpr int UMMA_K = 16;      // k per tcgen05.mma for 16-bit operands
+constexpr int kGemmThreads = 192;
+constexpr int kEpilogueThreads = 128;
+constexpr int kStageBudget = 192 * 1024;   // bytes of operand ring per CTA
+constexpr int kGroupM = 16;     // m-tiles per rasterisation band
+
+constexpr int ERR_PRODUCER = 0x101, ERR_MMA_FULL = 0x102, ERR_MMA_TMEM = 0x103, ERR_EPILOGUE = 0x104;
+
+// ---------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Bounded wait: gives up after ~1 s of wall time, records `code` and returns false.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int* status, int code) {
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+    for (int i = 0; i < 2048; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (global_timer_ns() - t0 > 1000000000ull) {
+      atomicExch(status, code);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+  for (int i = 0; i < 64; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, status, code);
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3}], [%4];"
+      :
+      : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc]; accumulate == 0 overwrites D.
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                         uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the mbarrier once every tcgen05.mma issued so far by this thread has retired.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void epilogue_bar_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 fp16)
+// laid out by TMA with the 128-byte swizzle: 8-row groups are 1024 bytes apart (stride
+// byte offset), the leading byte offset is unused for swizzled K-major layouts,
+// descriptor version 1 (sm_100), layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Instruction descriptor for kind::f16: D fp32, A and B fp16, both K-major, M=128, N=BN.
+__host__ __device__ constexpr uint32_t make_idesc_f16_f32(int n) {
+  return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+struct GemmArgs {
+  __half* y;
+  const __half* bias;
+  float* ws;          // split-K partials: [splits][m][n] fp32
+  int* counters;      // one arrival counter per output tile (zero between launches)
+  int* status;
+  int64_t ldy;
+  int m, n, k;
+  int m_tiles, n_tiles, splits, kb_per_split, num_kb;
+  int vec_store;      // 1 when 16-byte stores into Y are aligned
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = kStageBudget / kStageBytes;
+  static constexpr int kTmemCols = 2 * BN;  // two accumulators
+  static constexpr int kBarBytes = (2 * kStages + 4) * 8 + 16;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kBarBytes;
+  static_assert(kTmemCols >= 32 && kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "tmem");
+  static_assert(kSmemBytes <= 227 * 1024, "smem");
+};
+
+// Work item -> (m_tile, n_tile, split).  Tiles are visited band by band (kGroupM m-tiles
+// per band); inside a band the m index runs fastest, so CTAs that run side by side read
+// the same W tile and a small set of X tiles.
+__device__ __forceinline__ void decode_work(const GemmArgs& a, int w, int& mt, int& nt, int& sp) {
+  sp = w % a.splits;
+  const int tile = w / a.splits;
+  const int band_tiles = kGroupM * a.n_tiles;
+  const int band = tile / band_tiles;
+  const int in_band = tile - band * band_tiles;
+  const int band_rows = min(kGroupM, a.m_tiles - band * kGroupM);
+  mt = band * kGroupM + in_band % band_rows;
+  nt = in_band / band_rows;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                            const __grid_constant__ CUtensorMap tmap_w, const GemmArgs a) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzle atoms need 1024 B
+  const uint32_t bars = base + C::kStages * C::kStageBytes;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (C::kStages + s); };
+  auto tfull_bar = [&](int i) { return bars + 8u * (2 * C::kStages + i); };
+  auto tempty_bar = [&](int i) { return bars + 8u * (2 * C::kStages + 2 + i); };
+  const uint32_t tmem_slot = bars + 8u * (2 * C::kStages + 4);
+  const uint32_t last_flag = tmem_slot + 4;
+  uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(gen_base + C::kStages * C::kStageBytes + 8 * (2 * C::kStages + 4));
+  volatile uint32_t* last_flag_ptr = tmem_slot_ptr + 1;
+  (void)last_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_work = a.m_tiles * a.n_tiles * a.splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(tfull_bar(i), 1);
+      mbar_init(tempty_bar(i), kEpilogueThreads / 32);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_x)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w)) : "memory");
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        int mt, nt, sp;
+        decode_work(a, w, mt, nt, sp);
+        const int kb0 = sp * a.kb_per_split;
+        const int kb1 = min(kb0 + a.kb_per_split, a.num_kb);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, a.status, ERR_PRODUCER)) { ok = false; break; }
+          mbar_expect_tx(full_bar(stage), C::kStageBytes);
+          const uint32_t sa = base + stage * C::kStageBytes;
+          tma_load_2d(sa, &tmap_x, kb * BK, mt * BM, full_bar(stage));
+          tma_load_2d(sa + C::kABytes, &tmap_w, kb * BK, nt * BN, full_bar(stage));
+          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16_f32(BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int iter = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++iter) {
+        int mt, nt, sp;
+        decode_work(a, w, mt, nt, sp);
+        const int kb0 = sp * a.kb_per_split;
+        const int kb1 = min(kb0 + a.kb_per_split, a.num_kb);
+        const int acc = iter & 1;
+        const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, a.status, ERR_MMA_TMEM)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, a.status, ERR_MMA_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = base + stage * C::kStageBytes;
+          const uint64_t da = make_kmajor_sw128_desc(sa);
+          const uint64_t db = make_kmajor_sw128_desc(sa + C::kABytes);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            // advancing 16 fp16 along K inside the swizzle row = +32 bytes = +2 in the address field
+            umma_f16(d_tmem, da + 2u * kk, db + 2u * kk, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));   // stage reusable once these MMAs have read it
+          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(tfull_bar(acc));  // accumulator complete
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;                 // TMEM lanes 32*quarter .. +31
+    const int epi_tid = threadIdx.x - 64;
+    int iter = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++iter) {
+      int mt, nt, sp;
+      decode_work(a, w, mt, nt, sp);
+      const int acc = iter & 1;
+      const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
+      if (!mbar_wait(tfull_bar(acc), acc_phase, a.status, ERR_EPILOGUE)) { ok = false; break; }
+      tc_fence_after();
+      const int row = mt * BM + quarter * 32 + lane;
+      const bool row_ok = row < a.m;
+      const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+      const int col_base = nt * BN;
+
+      if (a.splits == 1) {
+        __half* yrow = a.y + (int64_t)row * a.ldy;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_addr + c * 32, r);
+          tmem_ld_wait();
+          const int col0 = col_base + c * 32;
+          if (row_ok && col0 < a.n) {
+            if (a.bias != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < a.n) r[j] = __float_as_uint(__uint_as_float(r[j]) + __half2float(a.bias[col0 + j]));
+            }
+            if (a.vec_store && col0 + 32 <= a.n) {
+              uint4* dst = reinterpret_cast<uint4*>(yrow + col0);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 v;
+                __half2 h0 = __floats2half2_rn(__uint_as_float(r[8 * q + 0]), __uint_as_float(r[8 * q + 1]));
+                __half2 h1 = __floats2half2_rn(__uint_as_float(r[8 * q + 2]), __uint_as_float(r[8 * q + 3]));
+                __half2 h2 = __floats2half2_rn(__uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5]));
+                __half2 h3 = __floats2half2_rn(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7]));
+                v.x = *reinterpret_cast<uint32_t*>(&h0);
+                v.y = *reinterpret_cast<uint32_t*>(&h1);
+                v.z = *reinterpret_cast<uint32_t*>(&h2);
+                v.w = *reinterpret_cast<uint32_t*>(&h3);
+                dst[q] = v;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < a.n) yrow[col0 + j] = __float2half_rn(__uint_as_float(r[j]));
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
+      } else {
+        // split-K: park the fp32 partial, then the last slice to arrive reduces.
+        float* wrow = a.ws + ((int64_t)sp * a.m + row) * a.n;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_addr + c * 32, r);
+          tmem_ld_wait();
+          const int col0 = col_base + c * 32;
+          if (row_ok && col0 < a.n) {
+            if (col0 + 32 <= a.n && (a.n & 3) == 0) {
+              float4* dst = reinterpret_cast<float4*>(wrow + col0);
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                dst[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                     __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < a.n) wrow[col0 + j] = __uint_as_float(r[j]);
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));   // TMEM no longer needed for this tile
+
+        __threadfence();
+        epilogue_bar_sync();
+        if (epi_tid == 0) {
+          const int tile = mt * a.n_tiles + nt;
+          const int old = atomicAdd(&a.counters[tile], 1);
+          const uint32_t last = (old == a.splits - 1) ? 1u : 0u;
+          if (last) a.counters[tile] = 0;   // every slice has arrived: re-arm for the next launch
+          *last_flag_ptr = last;
+        }
+        epilogue_bar_sync();
+        const bool is_last = *last_flag_ptr != 0;
+        epilogue_bar_sync();                 // flag consumed before a later tile rewrites it
+        if (is_last) {
+          __threadfence();
+          if (row_ok) {
+            __half* yrow = a.y + (int64_t)row * a.ldy;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+              const int col0 = col_base + c * 32;
+              if (col0 >= a.n) break;
+              float acc32[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) acc32[j] = 0.f;
+              const bool full = (col0 + 32 <= a.n) && ((a.n & 3) == 0);
+              for (int s = 0; s < a.splits; ++s) {
+                const float* src = a.ws + ((int64_t)s * a.m + row) * a.n + col0;
+                if (full) {
+#pragma unroll
+                  for (int q = 0; q < 8; ++q) {
+                    float4 v = __ldcg(reinterpret_cast<const float4*>(src) + q);
+                    acc32[4 * q] += v.x; acc32[4 * q + 1] += v.y;
+                    acc32[4 * q + 2] += v.z; acc32[4 * q + 3] += v.w;
+                  }
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j)
+                    if (col0 + j < a.n) acc32[j] += __ldcg(src + j);
+                }
+              }
+              if (a.bias != nullptr) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < a.n) acc32[j] += __half2float(a.bias[col0 + j]);
+              }
+              if (a.vec_store && col0 + 32 <= a.n) {
+                uint4* dst = reinterpret_cast<uint4*>(yrow + col0);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  uint4 v;
+                  __half2 h0 = __floats2half2_rn(acc32[8 * q + 0], acc32[8 * q + 1]);
+                  __half2 h1 = __floats2half2_rn(acc32[8 * q + 2], acc32[8 * q + 3]);
+                  __half2 h2 = __floats2half2_rn(acc32[8 * q + 4], acc32[8 * q + 5]);
+                  __half2 h3 = __floats2half2_rn(acc32[8 * q + 6], acc32[8 * q + 7]);
+                  v.x = *reinterpret_cast<uint32_t*>(&h0);
+                  v.y = *reinterpret_cast<uint32_t*>(&h1);
+                  v.z = *reinterpret_cast<uint32_t*>(&h2);
+                  v.w = *reinterpret_cast<uint32_t*>(&h3);
+                  dst[q] = v;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < a.n) yrow[col0 + j] = __float2half_rn(acc32[j]);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// SIMT fallback for shapes TMA cannot describe (k % 8 != 0 or unaligned bases): one thread
+// per output element, fp32 accumulation.  Correct for every shape, not a performance path.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+    gemm_f16_simt_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
+                         const __half* __restrict__ bias, __half* __restrict__ y, int m, int n,
+                         int k, int64_t ldy) {
+  const int col = blockIdx.x * 16 + (threadIdx.x & 15);
+  const int row = blockIdx.y * 16 + (threadIdx.x >> 4);
+  if (row >= m || col >= n) return;
+  const __half* xr = x + (int64_t)row * k;
+  const __half* wr = w + (int64_t)col * k;
+  float acc = 0.f;
+  for (int i = 0; i < k; ++i) acc = fmaf(__half2float(xr[i]), __half2float(wr[i]), acc);
+  if (bias != nullptr) acc += __half2float(bias[col]);
+  y[(int64_t)row * ldy + col] = __float2half_rn(acc);
+}
+
+// ---------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D fp16 row-major [rows, cols] tensor, box = [box_rows, 64 cols], 128-byte swizzle,
+// out-of-bounds elements read as zero.
+int make_tmap(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) DTAS_FAIL(DTAS_ECUDA, "gemm: cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) DTAS_FAIL(DTAS_ECUDA, "gemm: cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return DTAS_OK;
+}
+
+struct GemmPlan {
+  int bn;
+  int splits;
+  int kb_per_split;
+  bool simt;
+};
+
+std::atomic<int> g_override_bn{0};
+std::atomic<int> g_override_split{0};
+
+constexpr size_t kSplitKWorkspaceBytes = 64ull << 20;
+constexpr int kTileCounters = 4096;
+
+// Tile width and split factor for a call shape: the idea of the reference's policy
+// (python/dtas/policy/wmma_config_emiter.py:148-259 - score every candidate tile with a
+// wave-quantised roofline model and keep the best), restated for one persistent CTA per
+// SM.  For each (BN, splits) candidate the model charges per k-block the larger of
+//   * the tensor/shared-memory time: max(2*BN MMA clocks, operand bytes / 128 B per clock),
+//   * the HBM time of the W tile (plus the amortised X tile) at this CTA's share of the
+//     device bandwidth,
+// adds a fixed fill/drain cost per work item, multiplies by the number of rounds
+// ceil(work / SMs), and adds the partial-sum traffic of a split.  Larger BN wins ties.
+GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
+  GemmPlan p{256, 1, 0, !tma_ok};
+  const int num_kb = (int)((k + BK - 1) / BK);
+  p.kb_per_split = num_kb;
+  if (p.simt) return p;
+  const int64_t m_tiles = (m + BM - 1) / BM;
+  auto tiles = [&](int bn) { return m_tiles * ((n + bn - 1) / bn); };
+  auto ws_ok = [&](int bn, int splits) {
+    return tiles(bn) <= kTileCounters && (int64_t)splits * m * n * 4 <= (int64_t)kSplitKWorkspaceBytes;
+  };
+
+  constexpr double kClockGHz = 1.7, kHbmGBs = 6500.0, kItemFixedNs = 1500.0;
+  static const int kBn[3] = {256, 128, 64};
+  static const int kSplits[10] = {1, 2, 3, 4, 5, 6, 8, 10, 12, 16};
+  double best = 1e30;
+  int best_bn = 256, best_splits = 1;
+  for (int bi = 0; bi < 3; ++bi) {
+    const int bn = kBn[bi];
+    const int64_t n_tiles = (n + bn - 1) / bn;
+    const int64_t t = m_tiles * n_tiles;
+    for (int si = 0; si < 10; ++si) {
+      const int want = kSplits[si];
+      if (want > 1 && (m > 512 || !ws_ok(bn, want))) continue;
+      const int kb_per = (num_kb + want - 1) / want;
+      const int s = (num_kb + kb_per - 1) / kb_per;
+      if (s != want || (want > 1 && kb_per < 2)) continue;
+      const int64_t work = t * s;
+      const int64_t rounds = (work + sm_count - 1) / sm_count;
+      const double active = (double)(work < sm_count ? work : sm_count);
+      const double smem_clk = (double)(BM * BK * 2 + bn * BK * 2) / 128.0;
+      const double mma_clk = 2.0 * bn;
+      const double t_core = (mma_clk > smem_clk ? mma_clk : smem_clk) / kClockGHz;
+      const double rows_x = (double)(m < BM ? m : BM);
+      const double share = (double)(n_tiles < 8 ? n_tiles : 8);
+      const double bytes = 128.0 * bn + 128.0 * rows_x / share;
+      const double t_hbm = bytes / (kHbmGBs / active);
+      double cost = (double)rounds * (kb_per * (t_core > t_hbm ? t_core : t_hbm) + kItemFixedNs);
+      if (s > 1) cost += 2.0 * s * (double)m * (double)n * 4.0 / kHbmGBs + 1000.0;
+      if (cost < best * 0.999) {
+        best = cost;
+        best_bn = bn;
+        best_splits = s;
+      }
+    }
+  }
+  int bn = best_bn, splits = best_splits;
+  const int obn = g_override_bn.load(), osp = g_override_split.load();
+  if (obn == 64 || obn == 128 || obn == 256) {
+    bn = obn;
+    if (osp <= 0 && !ws_ok(bn, splits)) splits = 1;
+  }
+  if (osp > 0) {
+    splits = osp > num_kb ? num_kb : osp;
+    if (splits > 1 && !ws_ok(bn, splits)) splits = 1;
+  }
+  const int kb_per = (num_kb + splits - 1) / splits;
+  splits = (num_kb + kb_per - 1) / kb_per;   // no empty slice
+  p.bn = bn;
+  p.splits = splits;
+  p.kb_per_split = kb_per;
+  return p;
+}
+
+template <int BN>
+int launch_tc(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a, int sm_count,
+              cudaStream_t st) {
+  using C = Cfg<BN>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  DTAS_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_set[dev]) {
+    DTAS_CUDA(cudaFuncSetAttribute(gemm_f16_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   C::kSmemBytes));
+    attr_set[dev] = true;
+  }
+  const int total = a.m_tiles * a.n_tiles * a.splits;
+  const int grid = total < sm_count ? total : sm_count;
+  gemm_f16_tcgen05_kernel<BN><<<grid, kGemmThreads, C::kSmemBytes, st>>>(tx, tw, a);
+  return after_launch("gemm_f16_tcgen05_kernel");
+}
+
+bool gemm_tma_ok(const void* x, const void* w, int64_t k) {
+  return (k % 8 == 0) && aligned16(x) && aligned16(w);
+}
+
+}  // namespace
+
+void gemm_set_override(int bn, int split_k) {
+  g_override_bn.store(bn);
+  g_override_split.store(split_k);
+}
+
+int ensure_splitk_scratch(DeviceCtx* ctx) {
+  if (ctx->splitk_ws != nullptr) return DTAS_OK;
+  DTAS_CUDA(cudaMalloc(&ctx->splitk_ws, kSplitKWorkspaceBytes));
+  ctx->splitk_ws_bytes = kSplitKWorkspaceBytes;
+  DTAS_CUDA(cudaMalloc(&ctx->tile_counters, kTileCounters * sizeof(int)));
+  DTAS_CUDA(cudaMemset(ctx->tile_counters, 0, kTileCounters * sizeof(int)));
+  ctx->n_tile_counters = kTileCounters;
+  return DTAS_OK;
+}
+
+int launch_gemm(const void* x, const void* w, const void* bias, void* y, int64_t m, int64_t n,
+                int64_t k, int64_t ldy, DeviceCtx* ctx, cudaStream_t st) {
+  if (m > 0x7fffffffLL / 2 || n > 0x7fffffffLL / 2 || k > 0x7fffffffLL / 2)
+    DTAS_FAIL(DTAS_EINVAL, "gemm: dimension too large");
+  const GemmPlan p = plan_gemm(m, n, k, ctx->sm_count, gemm_tma_ok(x, w, k));
+  if (p.simt) {
+    dim3 grid((unsigned)((n + 15) / 16), (unsigned)((m + 15) / 16));
+    if (grid.y > 65535) DTAS_FAIL(DTAS_EUNSUPPORTED, "gemm: unaligned operands with m > 1048560");
+    gemm_f16_simt_kernel<<<grid, 256, 0, st>>>((const __half*)x, (const __half*)w, (const __half*)bias,
+                                               (__half*)y, (int)m, (int)n, (int)k, ldy);
+    return after_launch("gemm_f16_simt_kernel");
+  }
+  if (p.splits > 1) {
+    int rc = ensure_splitk_scratch(ctx);
+    if (rc != DTAS_OK) return rc;
+  }
+  CUtensorMap tx, tw;
+  int rc = make_tmap(&tx, x, m, k, BM);
+  if (rc != DTAS_OK) return rc;
+  rc = make_tmap(&tw, w, n, k, p.bn);
+  if (rc != DTAS_OK) return rc;
+
+  GemmArgs a;
+  a.y = (__half*)y;
+  a.bias = (const __half*)bias;
+  a.ws = ctx->splitk_ws;
+  a.counters = ctx->tile_counters;
+  a.status = ctx->status;
+  a.ldy = ldy;
+  a.m = (int)m;
+  a.n = (int)n;
+  a.k = (int)k;
+  a.m_tiles = (int)((m + BM - 1) / BM);
+  a.n_tiles = (int)((n + p.bn - 1) / p.bn);
+  a.splits = p.splits;
+  a.kb_per_split = p.kb_per_split;
+  a.num_kb = (int)((k + BK - 1) / BK);
+  a.vec_store = (aligned16(y) && (ldy % 8 == 0)) ? 1 : 0;
+  if ((int64_t)a.m_tiles * a.n_tiles * a.splits > 0x7fffffffLL)
+    DTAS_FAIL(DTAS_EINVAL, "gemm: too many tiles");
+  switch (p.bn) {
+    case 256: return launch_tc<256>(tx, tw, a, ctx->sm_count, st);
+    case 128: return launch_tc<128>(tx, tw, a, ctx->sm_count, st);
+    default: return launch_tc<64>(tx, tw, a, ctx->sm_count, st);
+  }
+}
+
+void gemm_variant_name(int64_t m, int64_t n, int64_t k, const DeviceCtx* ctx, char* buf, int len) {
+  const GemmPlan p = plan_gemm(m, n, k, ctx ? ctx->sm_count : 148, k % 8 == 0);
+  if (p.simt) {
+    snprintf(buf, len, "gemm_simt_fallback");
+    return;
+  }
+  const int stages = p.bn == 256 ? Cfg<256>::kStages : (p.bn == 128 ? Cfg<128>::kStages : Cfg<64>::kStages);
+  snprintf(buf, len, "gemm_tcgen05_bm128_bn%d_bk64_s%d_splitk%d", p.bn, stages, p.splits);
+}
+
+}  // namespace dtas

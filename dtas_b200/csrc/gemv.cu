@@ -1,0 +1,160 @@
+// Decode-time GEMV: y[n] = sum_k W[n,k] * x[k] (+ bias[n]), fp16 in/out, fp32 accumulate.
+//
+// Counterpart of the reference GEMV template (python/dtas/schedule/tir_gemv.py:33-249):
+// W rows streamed with 16-byte vector loads, the reduction over K split over the lanes
+// of a warp (and over several warps for short N) and combined with shuffles.
+//
+// Design: the kernel is a pure stream over W (2*N*K bytes; x and y are noise), so the
+// only goal is enough 16-byte loads in flight on every SM.  A row is owned by WPR warps
+// (1, 2, 4 or 8) of a 256-thread CTA; each lane issues UNROLL independent 16-byte loads
+// of W per step with the matching x chunks read through L1 (x is 8-22 KB and hot in
+// L1/L2), accumulates 8 products per chunk in fp32, and the partials meet through warp
+// shuffles and one shared-memory hop.  WPR grows as N shrinks (column-sharded ranks) so
+// that the grid still covers all SMs several times.
+// Algorithmic bytes: 2*N*K + 2*K + 2*N.  Bound: HBM bandwidth.
+#include "common.cuh"
+
+namespace dtas {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+__device__ __forceinline__ float dot8(uint4 w, uint4 x, float acc) {
+  const __half2* wh = reinterpret_cast<const __half2*>(&w);
+  const __half2* xh = reinterpret_cast<const __half2*>(&x);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 a = __half22float2(wh[i]);
+    float2 b = __half22float2(xh[i]);
+    acc = fmaf(a.x, b.x, acc);
+    acc = fmaf(a.y, b.y, acc);
+  }
+  return acc;
+}
+
+template <int WPR, int UNROLL>
+__global__ void __launch_bounds__(kThreads)
+    gemv_f16_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
+                    const __half* __restrict__ bias, __half* __restrict__ y, int n, int k) {
+  constexpr int kRowsPerCta = kWarps / WPR;
+  __shared__ float partial[kWarps];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * kRowsPerCta + warp / WPR;
+  const int part = warp % WPR;  // which K-slice of the row this warp owns
+  const bool live = row < n;
+
+  const int n_chunks = k >> 3;                       // 16-byte chunks per row
+  const int per_part = (n_chunks + WPR - 1) / WPR;   // chunks per K-slice
+  const int c0 = part * per_part;
+  const int c1 = min(c0 + per_part, n_chunks);
+
+  const uint4* wr = reinterpret_cast<const uint4*>(w + (int64_t)(live ? row : 0) * k);
+  const uint4* xv = reinterpret_cast<const uint4*>(x);
+
+  float acc[UNROLL];
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) acc[u] = 0.f;
+
+  if (live) {
+    int c = c0 + lane;
+    // Full steps: UNROLL independent 16-byte loads of W per lane before any use.
+    for (; c + (UNROLL - 1) * 32 < c1; c += UNROLL * 32) {
+      uint4 wv[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) wv[u] = __ldcs(wr + c + u * 32);
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) acc[u] = dot8(wv[u], __ldg(xv + c + u * 32), acc[u]);
+    }
+    for (; c < c1; c += 32) acc[0] = dot8(__ldcs(wr + c), __ldg(xv + c), acc[0]);
+  }
+
+  float s = 0.f;
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) s += acc[u];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+
+  if constexpr (WPR > 1) {
+    if (lane == 0) partial[warp] = s;
+    __syncthreads();
+    if (part == 0 && lane == 0 && live) {
+      float r = partial[warp];
+#pragma unroll
+      for (int i = 1; i < WPR; ++i) r += partial[warp + i];
+      if (bias != nullptr) r += __half2float(bias[row]);
+      y[row] = __float2half_rn(r);
+    }
+  } else {
+    if (lane == 0 && live) {
+      if (bias != nullptr) s += __half2float(bias[row]);
+      y[row] = __float2half_rn(s);
+    }
+  }
+}
+
+// Any K / any alignment: one warp per row, scalar loads.
+__global__ void __launch_bounds__(kThreads)
+    gemv_f16_scalar_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
+                           const __half* __restrict__ bias, __half* __restrict__ y, int n, int k) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * kWarps + warp;
+  float s = 0.f;
+  if (row < n) {
+    const __half* wr = w + (int64_t)row * k;
+    for (int i = lane; i < k; i += 32) s = fmaf(__half2float(wr[i]), __half2float(x[i]), s);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0 && row < n) {
+    if (bias != nullptr) s += __half2float(bias[row]);
+    y[row] = __float2half_rn(s);
+  }
+}
+
+// Warps per row: aim for at least 4 CTAs per SM.
+inline int pick_wpr(int64_t n, int64_t k, int sm_count) {
+  int wpr = 1;
+  while (wpr < 8 && (n * wpr) / kWarps < (int64_t)sm_count * 4 && (k >> 3) / (wpr * 2) >= 64)
+    wpr *= 2;
+  return wpr;
+}
+
+}  // namespace
+
+int launch_gemv(const void* x, const void* w, const void* bias, void* y, int64_t n, int64_t k,
+                const DeviceCtx* ctx, cudaStream_t st) {
+  if (n > 0x7fffffffLL || k > 0x7fffffffLL) DTAS_FAIL(DTAS_EINVAL, "gemv: n or k too large");
+  const __half* xp = (const __half*)x;
+  const __half* wp = (const __half*)w;
+  const __half* bp = (const __half*)bias;
+  __half* yp = (__half*)y;
+  const bool vec_ok = (k % 8 == 0) && aligned16(x) && aligned16(w);
+  if (!vec_ok) {
+    const unsigned grid = (unsigned)((n + kWarps - 1) / kWarps);
+    gemv_f16_scalar_kernel<<<grid, kThreads, 0, st>>>(xp, wp, bp, yp, (int)n, (int)k);
+    return after_launch("gemv_f16_scalar_kernel");
+  }
+  const int wpr = pick_wpr(n, k, ctx->sm_count);
+  const int rows_per_cta = kWarps / wpr;
+  const unsigned grid = (unsigned)((n + rows_per_cta - 1) / rows_per_cta);
+  switch (wpr) {
+    case 1: gemv_f16_kernel<1, 8><<<grid, kThreads, 0, st>>>(xp, wp, bp, yp, (int)n, (int)k); break;
+    case 2: gemv_f16_kernel<2, 8><<<grid, kThreads, 0, st>>>(xp, wp, bp, yp, (int)n, (int)k); break;
+    case 4: gemv_f16_kernel<4, 4><<<grid, kThreads, 0, st>>>(xp, wp, bp, yp, (int)n, (int)k); break;
+    default: gemv_f16_kernel<8, 4><<<grid, kThreads, 0, st>>>(xp, wp, bp, yp, (int)n, (int)k); break;
+  }
+  return after_launch("gemv_f16_kernel");
+}
+
+void gemv_variant_name(int64_t n, int64_t k, const DeviceCtx* ctx, char* buf, int len) {
+  if (k % 8 != 0) {
+    snprintf(buf, len, "gemv_scalar_warp_per_row");
+    return;
+  }
+  const int wpr = pick_wpr(n, k, ctx ? ctx->sm_count : 148);
+  snprintf(buf, len, "gemv_vec16_wpr%d_unroll%d", wpr, wpr <= 2 ? 8 : 4);
+}
+
+}  // namespace dtas

@@ -1,0 +1,383 @@
+// Row-reduction class: RMSNorm, softmax, LayerNorm (+ fused cast to fp16).
+//
+// Counterpart of the reference's "general reduction" schedule
+// (python/dtas/schedule/tir_reduction.py:36-105): one thread group per row, the row
+// cached on chip between the reduction and the normalising epilogue, fp32 arithmetic,
+// launch shape picked per m-bucket (python/dtas/policy/reduction_config_emiter.py:77-158).
+//
+// Design: a row is owned by TPR threads (a power of two, 32..1024).  Each thread loads
+// its 16-byte chunks (8 fp16, or 2 x 16 B for fp32 input) with all loads in flight at
+// once, keeps the row in registers as fp32, reduces with warp shuffles (+ one shared
+// memory hop when TPR > 32) and writes 16-byte fp16 vectors.  HBM sees each element
+// once in and once out: algorithmic bytes 4*n_cols per row for fp16 in/out
+// (+ 2*n_cols once for the RMSNorm weight).  Bound: HBM bandwidth.
+#include "common.cuh"
+
+namespace dtas {
+namespace {
+
+constexpr int kCtaThreads = 256;
+
+__device__ __forceinline__ float2 h2f(uint32_t v) {
+  return __half22float2(*reinterpret_cast<__half2*>(&v));
+}
+__device__ __forceinline__ uint32_t f2h(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Loads chunk `c` (8 consecutive elements) of a row as fp32.
+__device__ __forceinline__ void load_chunk(const __half* row, int c, float* v) {
+  uint4 r = __ldcs(reinterpret_cast<const uint4*>(row) + c);
+  float2 a = h2f(r.x), b = h2f(r.y), d = h2f(r.z), e = h2f(r.w);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+  v[4] = d.x; v[5] = d.y; v[6] = e.x; v[7] = e.y;
+}
+__device__ __forceinline__ void load_chunk(const float* row, int c, float* v) {
+  float4 a = __ldcs(reinterpret_cast<const float4*>(row) + 2 * c);
+  float4 b = __ldcs(reinterpret_cast<const float4*>(row) + 2 * c + 1);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void store_chunk(__half* row, int c, const float* v) {
+  uint4 w;
+  w.x = f2h(v[0], v[1]);
+  w.y = f2h(v[2], v[3]);
+  w.z = f2h(v[4], v[5]);
+  w.w = f2h(v[6], v[7]);
+  __stcs(reinterpret_cast<uint4*>(row) + c, w);
+}
+
+struct SumOp {
+  __device__ __forceinline__ float operator()(float a, float b) const { return a + b; }
+};
+struct MaxOp {
+  __device__ __forceinline__ float operator()(float a, float b) const { return fmaxf(a, b); }
+};
+
+// All-reduce of `v` over the TPR threads that own one row.  `scratch` holds one float
+// per warp of the CTA and must not be reused before the next __syncthreads().
+template <int TPR, typename F>
+__device__ __forceinline__ float group_allreduce(float v, F f, float* scratch) {
+  constexpr int kShfl = TPR < 32 ? TPR : 32;
+#pragma unroll
+  for (int o = kShfl / 2; o > 0; o >>= 1) v = f(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if constexpr (TPR > 32) {
+    constexpr int kWarpsPerRow = TPR / 32;
+    const int warp = threadIdx.x >> 5;
+    if ((threadIdx.x & 31) == 0) scratch[warp] = v;
+    __syncthreads();
+    const int first = (warp / kWarpsPerRow) * kWarpsPerRow;
+    float r = scratch[first];
+#pragma unroll
+    for (int i = 1; i < kWarpsPerRow; ++i) r = f(r, scratch[first + i]);
+    v = r;
+  }
+  return v;
+}
+
+// One row per TPR threads, up to MAXCH chunks per thread held in registers.
+template <int OP, typename InT, int TPR, int MAXCH>
+__global__ void __launch_bounds__(TPR > kCtaThreads ? TPR : kCtaThreads)
+    row_regs_kernel(const InT* __restrict__ x, const void* __restrict__ p0,
+                    const void* __restrict__ p1, __half* __restrict__ y, int64_t m, int n_cols,
+                    float eps) {
+  constexpr int kThreads = TPR > kCtaThreads ? TPR : kCtaThreads;
+  constexpr int kRowsPerCta = kThreads / TPR;
+  __shared__ float scratch_a[kThreads / 32];
+  __shared__ float scratch_b[kThreads / 32];
+
+  const int t = threadIdx.x % TPR;
+  const int64_t row = (int64_t)blockIdx.x * kRowsPerCta + threadIdx.x / TPR;
+  const bool live = row < m;
+  const int n_chunks = n_cols >> 3;
+  const InT* xr = x + (live ? row : 0) * (int64_t)n_cols;
+
+  float v[MAXCH][8];
+#pragma unroll
+  for (int c = 0; c < MAXCH; ++c) {
+    const int ch = c * TPR + t;
+    if (live && ch < n_chunks) {
+      load_chunk(xr, ch, v[c]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[c][i] = (OP == ROW_SOFTMAX) ? -3.4028234663852886e+38f : 0.f;
+    }
+  }
+
+  if constexpr (OP == ROW_RMSNORM) {
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < MAXCH; ++c)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss = fmaf(v[c][i], v[c][i], ss);
+    ss = group_allreduce<TPR>(ss, SumOp(), scratch_a);
+    const float r = 1.0f / sqrtf(ss * (1.0f / (float)n_cols) + eps);
+    const __half* w = static_cast<const __half*>(p0);
+#pragma unroll
+    for (int c = 0; c < MAXCH; ++c) {
+      const int ch = c * TPR + t;
+      if (live && ch < n_chunks) {
+        float wv[8];
+        uint4 wr = __ldg(reinterpret_cast<const uint4*>(w) + ch);
+        float2 a = h2f(wr.x), b = h2f(wr.y), d = h2f(wr.z), e = h2f(wr.w);
+        wv[0] = a.x; wv[1] = a.y; wv[2] = b.x; wv[3] = b.y;
+        wv[4] = d.x; wv[5] = d.y; wv[6] = e.x; wv[7] = e.y;
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = __fmul_rn(__fmul_rn(v[c][i], r), wv[i]);
+        store_chunk(y + row * (int64_t)n_cols, ch, o);
+      }
+    }
+  } else if constexpr (OP == ROW_SOFTMAX) {
+    float mx = -3.4028234663852886e+38f;
+#pragma unroll
+    for (int c = 0; c < MAXCH; ++c)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mx = fmaxf(mx, v[c][i]);
+    mx = group_allreduce<TPR>(mx, MaxOp(), scratch_a);
+    float sum = 0.f;
+#pragma unroll
+    for (int c = 0; c < MAXCH; ++c) {
+      const bool on = (c * TPR + t) < n_chunks;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        v[c][i] = on ? __expf(v[c][i] - mx) : 0.f;
+        sum += v[c][i];
+      }
+    }
+    sum = group_allreduce<TPR>(sum, SumOp(), scratch_b);
+    const float inv = 1.0f / sum;
+#pragma unroll
+    for (int c = 0; c < MAXCH; ++c) {
+      const int ch = c * TPR + t;
+      if (live && ch < n_chunks) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = v[c][i] * inv;
+        store_chunk(y + row * (int64_t)n_cols, ch, o);
+      }
+    }
+  } else {  // ROW_LAYERNORM
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < MAXCH; ++c)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        s1 += v[c][i];
+        s2 = fmaf(v[c][i], v[c][i], s2);
+      }
+    s1 = group_allreduce<TPR>(s1, SumOp(), scratch_a);
+    s2 = group_allreduce<TPR>(s2, SumOp(), scratch_b);
+    const float inv_n = 1.0f / (float)n_cols;
+    const float mean = s1 * inv_n;
+    const float r = 1.0f / sqrtf(__fadd_rn(__fsub_rn(s2 * inv_n, __fmul_rn(mean, mean)), eps));
+    const float* g = static_cast<const float*>(p0);
+    const float* be = static_cast<const float*>(p1);
+#pragma unroll
+    for (int c = 0; c < MAXCH; ++c) {
+      const int ch = c * TPR + t;
+      if (live && ch < n_chunks) {
+        float4 g0 = __ldg(reinterpret_cast<const float4*>(g) + 2 * ch);
+        float4 g1 = __ldg(reinterpret_cast<const float4*>(g) + 2 * ch + 1);
+        float4 b0 = __ldg(reinterpret_cast<const float4*>(be) + 2 * ch);
+        float4 b1 = __ldg(reinterpret_cast<const float4*>(be) + 2 * ch + 1);
+        const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          o[i] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v[c][i], mean), r), gv[i]), bv[i]);
+        store_chunk(y + row * (int64_t)n_cols, ch, o);
+      }
+    }
+  }
+}
+
+// Any n_cols / any alignment: one CTA per row, scalar accesses, the row re-read from
+// global memory (L2) for each pass.  Only used when the vector path does not apply.
+__device__ __forceinline__ float ld_as_f32(const __half* p, int64_t i) { return __half2float(p[i]); }
+__device__ __forceinline__ float ld_as_f32(const float* p, int64_t i) { return p[i]; }
+
+template <typename F>
+__device__ __forceinline__ float cta_allreduce(float v, F f, float* scratch) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = f(v, __shfl_xor_sync(0xffffffffu, v, o));
+  const int warp = threadIdx.x >> 5;
+  __syncthreads();  // scratch may still be read by the previous reduction
+  if ((threadIdx.x & 31) == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = scratch[0];
+  for (int i = 1; i < kCtaThreads / 32; ++i) r = f(r, scratch[i]);
+  return r;
+}
+
+template <int OP, typename InT>
+__global__ void __launch_bounds__(kCtaThreads)
+    row_generic_kernel(const InT* __restrict__ x, const void* __restrict__ p0,
+                       const void* __restrict__ p1, __half* __restrict__ y, int64_t m,
+                       int64_t n_cols, float eps) {
+  __shared__ float scratch[kCtaThreads / 32];
+  for (int64_t row = blockIdx.x; row < m; row += gridDim.x) {
+    const InT* xr = x + row * n_cols;
+    __half* yr = y + row * n_cols;
+    if constexpr (OP == ROW_RMSNORM) {
+      float ss = 0.f;
+      for (int64_t i = threadIdx.x; i < n_cols; i += kCtaThreads) {
+        float a = ld_as_f32(xr, i);
+        ss = fmaf(a, a, ss);
+      }
+      ss = cta_allreduce(ss, SumOp(), scratch);
+      const float r = 1.0f / sqrtf(ss * (1.0f / (float)n_cols) + eps);
+      const __half* w = static_cast<const __half*>(p0);
+      for (int64_t i = threadIdx.x; i < n_cols; i += kCtaThreads)
+        yr[i] = __float2half_rn(__fmul_rn(__fmul_rn(ld_as_f32(xr, i), r), __half2float(w[i])));
+    } else if constexpr (OP == ROW_SOFTMAX) {
+      float mx = -3.4028234663852886e+38f;
+      for (int64_t i = threadIdx.x; i < n_cols; i += kCtaThreads) mx = fmaxf(mx, ld_as_f32(xr, i));
+      mx = cta_allreduce(mx, MaxOp(), scratch);
+      float sum = 0.f;
+      for (int64_t i = threadIdx.x; i < n_cols; i += kCtaThreads)
+        sum += __expf(ld_as_f32(xr, i) - mx);
+      sum = cta_allreduce(sum, SumOp(), scratch);
+      const float inv = 1.0f / sum;
+      for (int64_t i = threadIdx.x; i < n_cols; i += kCtaThreads)
+        yr[i] = __float2half_rn(__expf(ld_as_f32(xr, i) - mx) * inv);
+    } else {
+      float s1 = 0.f, s2 = 0.f;
+      for (int64_t i = threadIdx.x; i < n_cols; i += kCtaThreads) {
+        float a = ld_as_f32(xr, i);
+        s1 += a;
+        s2 = fmaf(a, a, s2);
+      }
+      s1 = cta_allreduce(s1, SumOp(), scratch);
+      s2 = cta_allreduce(s2, SumOp(), scratch);
+      const float inv_n = 1.0f / (float)n_cols;
+      const float mean = s1 * inv_n;
+      const float r = 1.0f / sqrtf(__fadd_rn(__fsub_rn(s2 * inv_n, __fmul_rn(mean, mean)), eps));
+      const float* g = static_cast<const float*>(p0);
+      const float* be = static_cast<const float*>(p1);
+      for (int64_t i = threadIdx.x; i < n_cols; i += kCtaThreads)
+        yr[i] = __float2half_rn(
+            __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(ld_as_f32(xr, i), mean), r), g[i]), be[i]));
+    }
+  }
+}
+
+// ---- dispatch ------------------------------------------------------------------
+// Threads per row: few rows -> wide groups (short dependent chains, low latency);
+// many rows -> narrower groups (more rows per CTA, fewer barriers).  Always at least
+// enough threads that a row fits in 8 chunks per thread, never more threads than chunks.
+struct RowCfg {
+  int tpr;
+  int maxch;     // 2 or 8
+  bool generic;
+};
+
+inline int pow2_ceil(int v) {
+  int p = 1;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+inline RowCfg row_cfg(int64_t m, int64_t n_cols, bool vec_ok) {
+  RowCfg c{0, 0, false};
+  if (!vec_ok || n_cols > 65536) {
+    c.generic = true;
+    return c;
+  }
+  const int n_chunks = (int)(n_cols >> 3);
+  const int bucket = bucket_of(m);
+  int want = bucket == 0 ? 512 : (bucket <= 3 ? 256 : 128);
+  int min_tpr = pow2_ceil((n_chunks + 7) / 8);
+  if (min_tpr < 32) min_tpr = 32;
+  int max_tpr = pow2_ceil(n_chunks);
+  if (max_tpr < 32) max_tpr = 32;
+  if (max_tpr > 1024) max_tpr = 1024;
+  int tpr = want;
+  if (tpr < min_tpr) tpr = min_tpr;
+  if (tpr > max_tpr) tpr = max_tpr;
+  c.tpr = tpr;
+  c.maxch = ((n_chunks + tpr - 1) / tpr) <= 2 ? 2 : 8;
+  return c;
+}
+
+template <int OP, typename InT, int TPR, int MAXCH>
+int launch_regs(const InT* x, const void* p0, const void* p1, __half* y, int64_t m, int n_cols,
+                float eps, cudaStream_t st) {
+  constexpr int kThreads = TPR > kCtaThreads ? TPR : kCtaThreads;
+  constexpr int kRowsPerCta = kThreads / TPR;
+  const int64_t grid = (m + kRowsPerCta - 1) / kRowsPerCta;
+  if (grid > 0x7fffffffLL) DTAS_FAIL(DTAS_EINVAL, "row op: too many rows (%lld)", (long long)m);
+  row_regs_kernel<OP, InT, TPR, MAXCH><<<(unsigned)grid, kThreads, 0, st>>>(x, p0, p1, y, m, n_cols, eps);
+  return after_launch("row_regs_kernel");
+}
+
+template <int OP, typename InT, int MAXCH>
+int launch_tpr(int tpr, const InT* x, const void* p0, const void* p1, __half* y, int64_t m,
+               int n_cols, float eps, cudaStream_t st) {
+  switch (tpr) {
+    case 32: return launch_regs<OP, InT, 32, MAXCH>(x, p0, p1, y, m, n_cols, eps, st);
+    case 64: return launch_regs<OP, InT, 64, MAXCH>(x, p0, p1, y, m, n_cols, eps, st);
+    case 128: return launch_regs<OP, InT, 128, MAXCH>(x, p0, p1, y, m, n_cols, eps, st);
+    case 256: return launch_regs<OP, InT, 256, MAXCH>(x, p0, p1, y, m, n_cols, eps, st);
+    case 512: return launch_regs<OP, InT, 512, MAXCH>(x, p0, p1, y, m, n_cols, eps, st);
+    case 1024: return launch_regs<OP, InT, 1024, MAXCH>(x, p0, p1, y, m, n_cols, eps, st);
+  }
+  DTAS_FAIL(DTAS_EINVAL, "row op: bad threads-per-row %d", tpr);
+}
+
+template <int OP, typename InT>
+int launch_typed(const RowCfg& c, const InT* x, const void* p0, const void* p1, __half* y,
+                 int64_t m, int64_t n_cols, float eps, const DeviceCtx* ctx, cudaStream_t st) {
+  if (c.generic) {
+    int64_t grid = m < (int64_t)ctx->sm_count * 8 ? m : (int64_t)ctx->sm_count * 8;
+    row_generic_kernel<OP, InT><<<(unsigned)grid, kCtaThreads, 0, st>>>(x, p0, p1, y, m, n_cols, eps);
+    return after_launch("row_generic_kernel");
+  }
+  if (c.maxch == 2) return launch_tpr<OP, InT, 2>(c.tpr, x, p0, p1, y, m, (int)n_cols, eps, st);
+  return launch_tpr<OP, InT, 8>(c.tpr, x, p0, p1, y, m, (int)n_cols, eps, st);
+}
+
+template <int OP>
+int launch_op(const RowCfg& c, const void* x, const void* p0, const void* p1, void* y, int64_t m,
+              int64_t n_cols, float eps, int in_dtype, const DeviceCtx* ctx, cudaStream_t st) {
+  if (in_dtype == DTAS_F16)
+    return launch_typed<OP, __half>(c, (const __half*)x, p0, p1, (__half*)y, m, n_cols, eps, ctx, st);
+  if (in_dtype == DTAS_F32)
+    return launch_typed<OP, float>(c, (const float*)x, p0, p1, (__half*)y, m, n_cols, eps, ctx, st);
+  DTAS_FAIL(DTAS_EUNSUPPORTED, "row op: unsupported input dtype %d", in_dtype);
+}
+
+bool row_vec_ok(RowOp op, const void* x, const void* p0, const void* p1, const void* y,
+                int64_t n_cols, int in_dtype) {
+  (void)in_dtype;
+  bool ok = (n_cols % 8 == 0) && aligned16(x) && aligned16(y);
+  if (op == ROW_RMSNORM) ok = ok && aligned16(p0);
+  if (op == ROW_LAYERNORM) ok = ok && aligned16(p0) && aligned16(p1);
+  return ok;
+}
+
+}  // namespace
+
+int launch_row_op(RowOp op, const void* x, const void* p0, const void* p1, void* y, int64_t m,
+                  int64_t n_cols, float eps, int in_dtype, const DeviceCtx* ctx, cudaStream_t st) {
+  const RowCfg c = row_cfg(m, n_cols, row_vec_ok(op, x, p0, p1, y, n_cols, in_dtype));
+  switch (op) {
+    case ROW_RMSNORM: return launch_op<ROW_RMSNORM>(c, x, p0, p1, y, m, n_cols, eps, in_dtype, ctx, st);
+    case ROW_SOFTMAX: return launch_op<ROW_SOFTMAX>(c, x, p0, p1, y, m, n_cols, eps, in_dtype, ctx, st);
+    case ROW_LAYERNORM: return launch_op<ROW_LAYERNORM>(c, x, p0, p1, y, m, n_cols, eps, in_dtype, ctx, st);
+  }
+  DTAS_FAIL(DTAS_EINVAL, "row op: unknown op %d", (int)op);
+}
+
+void row_variant_name(RowOp op, int64_t m, int64_t n_cols, char* buf, int len) {
+  static const char* names[] = {"rms_norm", "softmax", "layer_norm"};
+  const RowCfg c = row_cfg(m, n_cols, n_cols % 8 == 0);
+  if (c.generic)
+    snprintf(buf, len, "%s_generic_cta256", names[op]);
+  else
+    snprintf(buf, len, "%s_regs_tpr%d_ch%d", names[op], c.tpr, c.maxch);
+}
+
+}  // namespace dtas

@@ -1,0 +1,172 @@
+"""Torch-tensor front end of the C ABI: one function per operator.
+
+Calling convention follows the reference's packed functions: inputs first, the
+pre-allocated output last (experiment/dtas_tuned/elementwise/cast/profile_cast.py:15-18);
+the symbolic dim is read from the tensor shape, never passed
+(experiment/dtas_tuned/elementwise/cast/top10_256/host.cc:52-53).  Tensors may be
+`[m, H]` or the reference's `[1, m, H]`.  Every function launches on the current torch
+stream of the tensor's device and returns the output tensor.
+"""
+import torch
+
+from . import _abi
+
+_DTYPE_CODE = {torch.float16: _abi.F16, torch.float32: _abi.F32, torch.int8: _abi.I8}
+
+
+def _code(t):
+    try:
+        return _DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise _abi.DtasError(_abi.EUNSUPPORTED, f"dtype {t.dtype} has no kernel") from None
+
+
+def _rows_cols(t, name):
+    """[m, H] or [1, m, H] -> (m, H)."""
+    if t.dim() == 3 and t.shape[0] == 1:
+        return int(t.shape[1]), int(t.shape[2])
+    if t.dim() == 2:
+        return int(t.shape[0]), int(t.shape[1])
+    raise _abi.DtasError(_abi.EINVAL, f"{name}: expected [m, H] or [1, m, H], got {tuple(t.shape)}")
+
+
+def _check(name, *tensors):
+    dev = tensors[0].device
+    if dev.type != "cuda":
+        raise _abi.DtasError(_abi.EINVAL, f"{name}: tensors must live on a CUDA device, got {dev}")
+    for t in tensors:
+        if t.device != dev:
+            raise _abi.DtasError(_abi.EINVAL, f"{name}: tensors on different devices")
+        if not t.is_contiguous():
+            raise _abi.DtasError(_abi.EINVAL, f"{name}: tensors must be contiguous")
+    index = dev.index if dev.index is not None else torch.cuda.current_device()
+    return index, torch.cuda.current_stream(index).cuda_stream
+
+
+def _same_shape(name, a, b):
+    if _rows_cols(a, name) != _rows_cols(b, name):
+        raise _abi.DtasError(_abi.EINVAL, f"{name}: shape mismatch {tuple(a.shape)} vs {tuple(b.shape)}")
+
+
+def cast(a, out):
+    """out = a converted to out.dtype (fp32 -> fp16 round-to-nearest-even, or fp16 -> fp32)."""
+    dev, st = _check("cast", a, out)
+    _same_shape("cast", a, out)
+    m, h = _rows_cols(a, "cast")
+    _abi.check(_abi.lib().dtas_cast(a.data_ptr(), out.data_ptr(), m, h, _code(a), _code(out), dev, st))
+    return out
+
+
+def add(a, b, out):
+    """out = a + b, all three of one dtype (fp16, fp32 or int8)."""
+    dev, st = _check("add", a, b, out)
+    _same_shape("add", a, b)
+    _same_shape("add", a, out)
+    if not (a.dtype == b.dtype == out.dtype):
+        raise _abi.DtasError(_abi.EINVAL, "add: dtypes differ")
+    m, h = _rows_cols(a, "add")
+    _abi.check(_abi.lib().dtas_add(a.data_ptr(), b.data_ptr(), out.data_ptr(), m, h, _code(a), dev, st))
+    return out
+
+
+def copy(a, out):
+    """out = a."""
+    dev, st = _check("copy", a, out)
+    _same_shape("copy", a, out)
+    if a.dtype != out.dtype:
+        raise _abi.DtasError(_abi.EINVAL, "copy: dtypes differ")
+    m, h = _rows_cols(a, "copy")
+    _abi.check(_abi.lib().dtas_copy(a.data_ptr(), out.data_ptr(), m, h, _code(a), dev, st))
+    return out
+
+
+def rms_norm(x, weight, out, eps=1e-6):
+    """out = x * rsqrt(mean(x^2, -1) + eps) * weight; fp32 arithmetic, fp16 result."""
+    dev, st = _check("rms_norm", x, weight, out)
+    _same_shape("rms_norm", x, out)
+    m, h = _rows_cols(x, "rms_norm")
+    if weight.dtype != torch.float16 or weight.numel() != h or out.dtype != torch.float16:
+        raise _abi.DtasError(_abi.EINVAL, "rms_norm: weight must be fp16 [H] and out fp16")
+    _abi.check(_abi.lib().dtas_rms_norm(x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, h,
+                                        float(eps), _code(x), dev, st))
+    return out
+
+
+def softmax(x, out):
+    """out = softmax(x, dim=-1); fp32 arithmetic, fp16 result."""
+    dev, st = _check("softmax", x, out)
+    _same_shape("softmax", x, out)
+    if out.dtype != torch.float16:
+        raise _abi.DtasError(_abi.EINVAL, "softmax: out must be fp16")
+    m, h = _rows_cols(x, "softmax")
+    _abi.check(_abi.lib().dtas_softmax(x.data_ptr(), out.data_ptr(), m, h, _code(x), dev, st))
+    return out
+
+
+def layer_norm(x, gamma, beta, out, eps=1e-5):
+    """out = (x - mean) * rsqrt(var + eps) * gamma + beta; gamma/beta fp32 [H]; fp16 result."""
+    dev, st = _check("layer_norm", x, gamma, beta, out)
+    _same_shape("layer_norm", x, out)
+    m, h = _rows_cols(x, "layer_norm")
+    if gamma.dtype != torch.float32 or beta.dtype != torch.float32 or gamma.numel() != h or beta.numel() != h:
+        raise _abi.DtasError(_abi.EINVAL, "layer_norm: gamma and beta must be fp32 [H]")
+    if out.dtype != torch.float16:
+        raise _abi.DtasError(_abi.EINVAL, "layer_norm: out must be fp16")
+    _abi.check(_abi.lib().dtas_layer_norm(x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), out.data_ptr(),
+                                          m, h, float(eps), _code(x), dev, st))
+    return out
+
+
+def gemv(x, w, out, bias=None):
+    """out[1, N] = x[1, K] @ w[N, K]^T (+ bias[N]); fp16, fp32 accumulation."""
+    tensors = (x, w, out) if bias is None else (x, w, out, bias)
+    dev, st = _check("gemv", *tensors)
+    n, k = int(w.shape[0]), int(w.shape[1])
+    if w.dim() != 2 or x.numel() != k or out.numel() != n:
+        raise _abi.DtasError(_abi.EINVAL, f"gemv: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if not (x.dtype == w.dtype == out.dtype == torch.float16) or (bias is not None and bias.dtype != torch.float16):
+        raise _abi.DtasError(_abi.EUNSUPPORTED, "gemv: only fp16 is implemented")
+    if bias is not None and bias.numel() != n:
+        raise _abi.DtasError(_abi.EINVAL, "gemv: bias must have N elements")
+    _abi.check(_abi.lib().dtas_gemv(x.data_ptr(), w.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                    out.data_ptr(), n, k, _abi.F16, dev, st))
+    return out
+
+
+def gemm_nt(x, w, out, bias=None):
+    """out[m, N] = x[m, K] @ w[N, K]^T (+ bias[N]); fp16, fp32 accumulation, fp16 result.
+
+    `out` may be a column slab of a wider row-major buffer (last-dim stride 1, any row
+    stride >= N): a column-sharded rank writes its part of the full output in place.
+    """
+    dev_t = x.device
+    if dev_t.type != "cuda":
+        raise _abi.DtasError(_abi.EINVAL, f"gemm: tensors must live on a CUDA device, got {dev_t}")
+    m, k = _rows_cols(x, "gemm")
+    mo, n = _rows_cols(out, "gemm")
+    if w.dim() != 2 or int(w.shape[1]) != k or int(w.shape[0]) != n or mo != m:
+        raise _abi.DtasError(_abi.EINVAL, f"gemm: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if not (x.dtype == w.dtype == out.dtype == torch.float16) or (bias is not None and bias.dtype != torch.float16):
+        raise _abi.DtasError(_abi.EUNSUPPORTED, "gemm: only fp16 is implemented")
+    if not x.is_contiguous() or not w.is_contiguous() or (bias is not None and not bias.is_contiguous()):
+        raise _abi.DtasError(_abi.EINVAL, "gemm: x, w and bias must be contiguous")
+    if out.stride(-1) != 1:
+        raise _abi.DtasError(_abi.EINVAL, "gemm: out must have unit stride in its last dim")
+    ldy = int(out.stride(-2)) if m > 1 else max(int(out.stride(-2)), n)
+    for t in (w, out) + (() if bias is None else (bias,)):
+        if t.device != dev_t:
+            raise _abi.DtasError(_abi.EINVAL, "gemm: tensors on different devices")
+    if bias is not None and bias.numel() != n:
+        raise _abi.DtasError(_abi.EINVAL, "gemm: bias must have N elements")
+    dev = dev_t.index if dev_t.index is not None else torch.cuda.current_device()
+    st = torch.cuda.current_stream(dev).cuda_stream
+    _abi.check(_abi.lib().dtas_gemm_nt(x.data_ptr(), w.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                       out.data_ptr(), m, n, k, ldy, _abi.F16, dev, st))
+    return out
+
+
+def poll_status(device=None):
+    """Synchronises `device` and raises DtasError(ETIMEOUT) if a bounded device-side wait gave up."""
+    if device is None:
+        device = torch.cuda.current_device()
+    _abi.check(_abi.lib().dtas_poll_status(int(device)))

@@ -1,0 +1,134 @@
+/*
+ * dtas_b200 — C ABI of the sm_100a kernel library that stands in for the
+ * packed functions DTAS generates with TVM.
+ *
+ * In the reference every tuned PrimFunc becomes one generated host function
+ *   extern "C" int32_t <name>(void* args, int32_t* arg_type_ids, int32_t num_args,
+ *                             void* out_ret_value, int32_t* out_ret_tcode, void* resource_handle)
+ * (experiment/dtas_tuned/elementwise/cast/top10_256/host.cc:38-42) that unpacks
+ * DLTensor arguments, reads the symbolic dim from the tensor shape, looks up
+ * call_table[index_table[min(n/256, last)]] and launches one kernel of the cubin
+ * (host.cc:92-131; generator: python/dtas/codegen/code_gen.py:242-405).
+ *
+ * Here the same thing is a plain C entry point per operator class: raw device
+ * pointers, the runtime row count m, the static dims, a dtype code, the device
+ * ordinal and the CUDA stream.  Calling convention is destination-passing like
+ * the reference (inputs first, pre-allocated output last among the pointers).
+ *
+ * Every entry point
+ *   - returns DTAS_OK (0) or a positive DTAS_E* code; the message is available
+ *     from dtas_last_error() (thread-local), like TVM's last-error string;
+ *   - rejects m <= 0 (the reference asserts dynamic dims > 0,
+ *     python/dtas/IRpass/add_assert.py:36-37);
+ *   - launches on the given stream of the given device and restores the
+ *     caller's current device; never synchronises;
+ *   - allocates nothing per call.  The split-K GEMM keeps one workspace per
+ *     device that is created on the first call that needs it.
+ */
+#ifndef DTAS_B200_H_
+#define DTAS_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------ */
+#define DTAS_OK            0
+#define DTAS_EINVAL        1  /* bad argument: null pointer, m <= 0, bad dim, unknown dtype */
+#define DTAS_EALIGN        2  /* pointer / leading dimension alignment the kernel cannot honour */
+#define DTAS_ECUDA         3  /* a CUDA runtime / driver call failed                       */
+#define DTAS_ETIMEOUT      4  /* a bounded device-side wait gave up (reported by dtas_poll_status) */
+#define DTAS_EUNSUPPORTED  5  /* dtype / shape combination without a kernel                 */
+
+/* ---- dtype codes ------------------------------------------------------- */
+#define DTAS_F16  0
+#define DTAS_F32  1
+#define DTAS_I8   2
+
+/* ---- elementwise class --------------------------------------------------
+ * Replaces the generated `cast`, `add`, `copy` packed functions
+ * (tuning_test/tune_cast.py:10-21, tune_ele_add.py:10-22, tune_ele_copy.py:10-21;
+ *  kernels experiment/dtas_tuned/elementwise/{cast,add,copy}/...).
+ * Tensors are row-major contiguous [m, n_cols] (the reference's [1, n, H]).   */
+int dtas_cast(const void* a, void* out, int64_t m, int64_t n_cols,
+              int src_dtype, int dst_dtype, int device, void* stream);
+int dtas_add(const void* a, const void* b, void* out, int64_t m, int64_t n_cols,
+             int dtype, int device, void* stream);
+int dtas_copy(const void* a, void* out, int64_t m, int64_t n_cols,
+              int dtype, int device, void* stream);
+
+/* ---- row-reduction class -------------------------------------------------
+ * Replaces the "general reduction" packed functions
+ * (fused_layer_norm_cast / fused_softmax_cast,
+ *  experiment/dtas_tuned/general_reduction/{layernorm,softmax}/profile_dlight.py;
+ *  scheduler python/dtas/schedule/tir_reduction.py:36-105).
+ * x is [m, n_cols] of in_dtype (DTAS_F16 or DTAS_F32); the result is fp16;
+ * all arithmetic is fp32.
+ *   rms_norm  : y = x * rsqrt(mean(x^2) + eps) * weight      (weight fp16 [n_cols])
+ *   softmax   : y = exp(x - max) / sum(exp(x - max)) over the last dim
+ *   layer_norm: y = (x - mean) * rsqrt(E[x^2] - mean^2 + eps) * gamma + beta
+ *               (gamma, beta fp32 [n_cols], as in the reference workload)      */
+int dtas_rms_norm(const void* x, const void* weight, void* y, int64_t m, int64_t n_cols,
+                  float eps, int in_dtype, int device, void* stream);
+int dtas_softmax(const void* x, void* y, int64_t m, int64_t n_cols,
+                 int in_dtype, int device, void* stream);
+int dtas_layer_norm(const void* x, const void* gamma, const void* beta, void* y,
+                    int64_t m, int64_t n_cols, float eps, int in_dtype, int device, void* stream);
+
+/* ---- GEMV ----------------------------------------------------------------
+ * y[n] = sum_k W[n,k] * x[k] (+ bias[n]); fp16 in/out, fp32 accumulation.
+ * Replaces the NT_matmul(+add) GEMV packed function
+ * (experiment/testIR/GEMV/m1n2560k10240/dlight_gemv.py:8-27,
+ *  python/dtas/schedule/tir_gemv.py:33-249).  bias may be NULL.               */
+int dtas_gemv(const void* x, const void* w, const void* bias, void* y,
+              int64_t n, int64_t k, int dtype, int device, void* stream);
+
+/* ---- GEMM ----------------------------------------------------------------
+ * Y[m,n] = X[m,k] * W[n,k]^T (+ bias[n]); fp16 in/out, fp32 accumulation on
+ * the tcgen05 tensor cores.  Replaces fused_NT_matmul*_add*
+ * (experiment/testIR/GEMM/dlight.py:30-50, python/dtas/schedule/tir_wmma.py:20-222).
+ * X and W are row-major contiguous; Y has row stride ldy elements (ldy >= n), so
+ * a column-sharded rank can write its slab straight into a wider buffer.
+ * bias may be NULL.                                                            */
+int dtas_gemm_nt(const void* x, const void* w, const void* bias, void* y,
+                 int64_t m, int64_t n, int64_t k, int64_t ldy,
+                 int dtype, int device, void* stream);
+
+/* ---- dispatch introspection ---------------------------------------------
+ * dtas_bucket_of: index of the m-bucket the op dispatches on, the counterpart of
+ * the generated `index = (n/256) > L ? L : n/256` statement
+ * (python/dtas/engine/tuner.py:156-209) with the off-by-one at multiples of the
+ * width removed: bucket = min((m-1)/256, last).  op is one of "cast", "add",
+ * "copy", "rms_norm", "softmax", "layer_norm", "gemv", "gemm".  Returns -1 for
+ * an unknown op or m <= 0.
+ * dtas_variant_of: writes the name of the kernel variant that the given call
+ * shape would launch (e.g. "gemm_tc_bn256_s4_splitk1") into buf; returns DTAS_OK. */
+int dtas_bucket_of(const char* op, int64_t m);
+int dtas_bucket_count(const char* op);
+int dtas_variant_of(const char* op, int64_t m, int64_t n, int64_t k, int device,
+                    char* buf, int buf_len);
+
+/* Overrides the GEMM dispatch for testing and offline re-tuning: block-tile
+ * width bn in {64,128,256} (0 = automatic) and split-K factor (0 = automatic). */
+int dtas_gemm_set_override(int bn, int split_k);
+
+/* ---- bookkeeping ---------------------------------------------------------
+ * dtas_last_error : message of the last failing call on this thread ("" if none).
+ * dtas_launch_count: kernels launched by this library since load (all threads).
+ * dtas_poll_status : reads the device-side status word of `device` (written by a
+ *                    kernel whose bounded wait gave up); synchronises the device.
+ *                    Returns DTAS_OK or DTAS_ETIMEOUT, and clears the word.
+ * dtas_shutdown    : frees per-device workspaces.
+ * dtas_version     : "dtas_b200 <semver> sm_100a".                              */
+const char* dtas_last_error(void);
+int64_t dtas_launch_count(void);
+int dtas_poll_status(int device);
+int dtas_shutdown(void);
+const char* dtas_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DTAS_B200_H_ */

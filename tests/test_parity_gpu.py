@@ -1,0 +1,345 @@
+"""Parity of the CUDA kernels against the CPU oracle and the TVM-made golden fixtures.
+
+Every call goes through the C ABI (dtas_b200.ops -> ctypes -> libdtas_b200.so).  Rules:
+cast / add / copy bit-exact; reductions within 1e-3 relative + 1 fp16 ULP; GEMV / GEMM within
+1e-2 relative of an fp32-accumulated reference (tests/util.py).
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from dtas_b200 import _abi, ops
+from dtas_b200.reference import config_seed, seeded_normal
+from tests import util
+from tests.golden.golden_cases import CASES, make_inputs
+
+pytestmark = pytest.mark.gpu
+
+GUARD = 2048  # elements of guard band on each side of every output
+
+
+def guarded(shape, dtype, device, fill):
+    """Output tensor carved out of a larger buffer whose borders hold a sentinel."""
+    n = int(np.prod(shape))
+    pad = GUARD + (-n) % 8  # keeps the payload 16-byte aligned for every dtype
+    big = torch.full((GUARD + n + pad,), fill, dtype=dtype, device=device)
+    return big, big[GUARD:GUARD + n].view(*shape)
+
+
+def assert_guards(big, n, fill, what):
+    head, tail = big[:GUARD], big[GUARD + n:]
+    assert bool((head == fill).all()) and bool((tail == fill).all()), f"{what}: wrote outside its output"
+
+
+def np_of(t):
+    return t.detach().cpu().numpy()
+
+
+# ---------------------------------------------------------------------------------------
+# elementwise
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("m", [1, 17, 128, 4096])
+def test_cast_f32_f16_baseline(cuda_device, m):
+    x = seeded_normal((m, 4096), config_seed(0, 0), "float32")
+    big, y = guarded((m, 4096), torch.float16, cuda_device, 7.0)
+    ops.cast(x.to(cuda_device), y)
+    torch.cuda.synchronize()
+    util.assert_bit_exact(np_of(y), oracle.cast(x.numpy(), np.float16), f"cast m={m}")
+    assert_guards(big, m * 4096, 7.0, f"cast m={m}")
+
+
+@pytest.mark.parametrize("m", [1, 7, 64, 512, 8192])
+def test_add_copy_f16_baseline(cuda_device, m):
+    a = seeded_normal((m, 11008), config_seed(1, 0), "float16")
+    b = seeded_normal((m, 11008), config_seed(1, 1), "float16")
+    ad, bd = a.to(cuda_device), b.to(cuda_device)
+    big, c = guarded((m, 11008), torch.float16, cuda_device, 7.0)
+    ops.add(ad, bd, c)
+    torch.cuda.synchronize()
+    util.assert_bit_exact(np_of(c), oracle.add(a.numpy(), b.numpy()), f"add m={m}")
+    assert_guards(big, m * 11008, 7.0, f"add m={m}")
+    big, c = guarded((m, 11008), torch.float16, cuda_device, 7.0)
+    ops.copy(ad, c)
+    torch.cuda.synchronize()
+    util.assert_bit_exact(np_of(c), oracle.copy(a.numpy()), f"copy m={m}")
+    assert_guards(big, m * 11008, 7.0, f"copy m={m}")
+
+
+def test_elementwise_reference_signature_and_dtypes(cuda_device):
+    """The reference's own shapes: [1, n, 2560], cast fp16->fp32, add int8 / fp32, copy fp32."""
+    n = 300
+    a16 = seeded_normal((1, n, 2560), 5, "float16")
+    out = torch.empty((1, n, 2560), dtype=torch.float32, device=cuda_device)
+    ops.cast(a16.to(cuda_device), out)
+    util.assert_bit_exact(np_of(out), oracle.cast(a16.numpy(), np.float32), "cast f16->f32")
+    for dt in ("int8", "float32", "float16"):
+        a = seeded_normal((1, n, 2560), 6, dt)
+        b = seeded_normal((1, n, 2560), 7, dt)
+        out = torch.empty_like(a, device=cuda_device)
+        ops.add(a.to(cuda_device), b.to(cuda_device), out)
+        util.assert_bit_exact(np_of(out), oracle.add(a.numpy(), b.numpy()), f"add {dt}")
+        ops.copy(a.to(cuda_device), out)
+        util.assert_bit_exact(np_of(out), a.numpy(), f"copy {dt}")
+
+
+def test_elementwise_ragged_lengths_and_misalignment(cuda_device):
+    """Every m in 1..40 at a tiny odd H (tails shorter than a vector), a few random
+    lengths up to ~70k elements, and buffers that start 2 bytes off a 16-byte boundary."""
+    rng = np.random.default_rng(0)
+    shapes = [(m, 37) for m in range(1, 41)] + [(1, int(v)) for v in rng.integers(1, 70000, 12)]
+    for (m, h) in shapes:
+        a = seeded_normal((m, h), 100 + m + h, "float16")
+        b = seeded_normal((m, h), 200 + m + h, "float16")
+        big, c = guarded((m, h), torch.float16, cuda_device, 3.0)
+        ops.add(a.to(cuda_device), b.to(cuda_device), c)
+        util.assert_bit_exact(np_of(c), oracle.add(a.numpy(), b.numpy()), f"add {m}x{h}")
+        assert_guards(big, m * h, 3.0, f"add {m}x{h}")
+        x = seeded_normal((m, h), 300 + m + h, "float32")
+        big, y = guarded((m, h), torch.float16, cuda_device, 3.0)
+        ops.cast(x.to(cuda_device), y)
+        util.assert_bit_exact(np_of(y), oracle.cast(x.numpy(), np.float16), f"cast {m}x{h}")
+        assert_guards(big, m * h, 3.0, f"cast {m}x{h}")
+    # misaligned: views starting one element into a buffer
+    m, h = 9, 1001
+    a = seeded_normal((m * h + 1,), 1, "float16")
+    b = seeded_normal((m * h + 1,), 2, "float16")
+    ad, bd = a.to(cuda_device)[1:].view(m, h), b.to(cuda_device)[1:].view(m, h)
+    outbuf = torch.full((m * h + 2,), 3.0, dtype=torch.float16, device=cuda_device)
+    c = outbuf[1:1 + m * h].view(m, h)
+    ops.add(ad, bd, c)
+    util.assert_bit_exact(np_of(c), oracle.add(a.numpy()[1:].reshape(m, h), b.numpy()[1:].reshape(m, h)), "add misaligned")
+    assert float(outbuf[0]) == 3.0 and float(outbuf[-1]) == 3.0
+    ops.copy(ad, c)
+    util.assert_bit_exact(np_of(c), a.numpy()[1:].reshape(m, h), "copy misaligned")
+
+
+# ---------------------------------------------------------------------------------------
+# row reductions
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("m", [1, 33, 256, 4096])
+def test_rms_norm_softmax_baseline(cuda_device, m):
+    x = seeded_normal((m, 4096), config_seed(2, 0), "float16")
+    w = seeded_normal((4096,), config_seed(2, 1), "float16", scale=0.1, mean=1.0)
+    xd, wd = x.to(cuda_device), w.to(cuda_device)
+    big, y = guarded((m, 4096), torch.float16, cuda_device, 9.0)
+    ops.rms_norm(xd, wd, y, eps=1e-6)
+    torch.cuda.synchronize()
+    util.assert_reduction_close(np_of(y), oracle.rms_norm(x.numpy(), w.numpy(), 1e-6), f"rms_norm m={m}")
+    assert_guards(big, m * 4096, 9.0, f"rms_norm m={m}")
+    big, y = guarded((m, 4096), torch.float16, cuda_device, 9.0)
+    ops.softmax(xd, y)
+    torch.cuda.synchronize()
+    util.assert_reduction_close(np_of(y), oracle.softmax(x.numpy()), f"softmax m={m}")
+    assert_guards(big, m * 4096, 9.0, f"softmax m={m}")
+
+
+@pytest.mark.parametrize("m,h", [(3, 8), (5, 264), (2, 8192), (3, 32000), (2, 65536), (4, 101), (3, 1000), (2, 70000)])
+def test_row_ops_other_row_lengths(cuda_device, m, h):
+    """Short, long (vocabulary-sized), non-multiple-of-8 and over-long rows: register path
+    with every threads-per-row choice and the generic path."""
+    x = seeded_normal((m, h), 50 + h, "float16")
+    w = seeded_normal((h,), 51 + h, "float16", scale=0.1, mean=1.0)
+    xd = x.to(cuda_device)
+    y = torch.empty_like(xd)
+    ops.rms_norm(xd, w.to(cuda_device), y)
+    util.assert_reduction_close(np_of(y), oracle.rms_norm(x.numpy(), w.numpy(), 1e-6), f"rms_norm {m}x{h}")
+    ops.softmax(xd, y)
+    util.assert_reduction_close(np_of(y), oracle.softmax(x.numpy()), f"softmax {m}x{h}")
+
+
+def test_reference_reduction_workloads_fp32_in(cuda_device):
+    """The reference's own reductions: LayerNorm and softmax read fp32 and write fp16."""
+    for m in (1, 300):
+        x = seeded_normal((1, m, 2560), 60, "float32")
+        g = seeded_normal((2560,), 61, "float32", scale=0.1, mean=1.0)
+        b = seeded_normal((2560,), 62, "float32", scale=0.1)
+        y = torch.empty((1, m, 2560), dtype=torch.float16, device=cuda_device)
+        ops.layer_norm(x.to(cuda_device), g.to(cuda_device), b.to(cuda_device), y, eps=1e-5)
+        util.assert_reduction_close(np_of(y), oracle.layer_norm(x.numpy(), g.numpy(), b.numpy(), 1e-5), f"layer_norm m={m}")
+        ops.softmax(x.to(cuda_device), y)
+        util.assert_reduction_close(np_of(y), oracle.softmax(x.numpy()), f"softmax f32 m={m}")
+
+
+def test_reductions_row_permutation_invariance(cuda_device):
+    """Full-size property: permuting rows permutes the result, bit for bit."""
+    m = 4096
+    x = seeded_normal((m, 4096), 70, "float16").to(cuda_device)
+    perm = torch.randperm(m, generator=torch.Generator().manual_seed(1)).to(cuda_device)
+    y1, y2 = torch.empty_like(x), torch.empty_like(x)
+    ops.softmax(x, y1)
+    ops.softmax(x[perm].contiguous(), y2)
+    assert torch.equal(y1[perm], y2)
+    s = y1.float().sum(-1)
+    assert float((s - 1).abs().max()) < 2e-3
+
+
+# ---------------------------------------------------------------------------------------
+# GEMV
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("n,k", [(4096, 4096), (11008, 4096), (4096, 11008), (32000, 4096)])
+def test_gemv_baseline(cuda_device, n, k):
+    x = seeded_normal((1, k), config_seed(3, 0), "float16")
+    w = seeded_normal((n, k), config_seed(3, 1), "float16", scale=0.02)
+    big, y = guarded((1, n), torch.float16, cuda_device, 5.0)
+    ops.gemv(x.to(cuda_device), w.to(cuda_device), y)
+    torch.cuda.synchronize()
+    want = x.float().numpy() @ w.float().numpy().T
+    util.assert_matmul_close(np_of(y), want, f"gemv {n}x{k} vs fp32")
+    util.assert_matmul_close(np_of(y), oracle.gemv(x.numpy(), w.numpy()).astype(np.float32), f"gemv {n}x{k} vs oracle")
+    assert_guards(big, n, 5.0, f"gemv {n}x{k}")
+
+
+@pytest.mark.parametrize("n,k", [(512, 4096), (1376, 4096), (4000, 4096), (512, 11008), (7, 40), (33, 1001), (100, 264)])
+def test_gemv_sharded_and_odd_shapes(cuda_device, n, k):
+    """Per-rank shapes of 8-way column sharding (multi-warp rows), tiny and unaligned K."""
+    x = seeded_normal((1, k), 80, "float16")
+    w = seeded_normal((n, k), 81, "float16", scale=0.02)
+    b = seeded_normal((n,), 82, "float16", scale=0.1)
+    y = torch.empty((1, n), dtype=torch.float16, device=cuda_device)
+    ops.gemv(x.to(cuda_device), w.to(cuda_device), y, bias=b.to(cuda_device))
+    want = x.float().numpy() @ w.float().numpy().T + b.float().numpy()
+    util.assert_matmul_close(np_of(y), want, f"gemv+bias {n}x{k}")
+
+
+# ---------------------------------------------------------------------------------------
+# GEMM
+# ---------------------------------------------------------------------------------------
+GEMM_SHAPES = [(12288, 4096), (4096, 4096), (22016, 4096), (4096, 11008)]
+
+
+def _check_gemm_tiles(y_np, x, w, m, n, k, what, n_tiles=24):
+    """Oracle on sampled 128x128 tiles, always including the last (partial) row/column tiles."""
+    rng = np.random.default_rng(m * 131 + n)
+    mt, nt = (m + 127) // 128, (n + 127) // 128
+    picks = {(mt - 1, nt - 1), (0, 0), (mt - 1, 0), (0, nt - 1)}
+    while len(picks) < min(n_tiles, mt * nt):
+        picks.add((int(rng.integers(mt)), int(rng.integers(nt))))
+    xn, wn = x.numpy(), w.numpy()
+    for (i, j) in sorted(picks):
+        r0, r1, c0, c1 = i * 128, min(m, i * 128 + 128), j * 128, min(n, j * 128 + 128)
+        want = xn[r0:r1].astype(np.float32) @ wn[c0:c1].astype(np.float32).T
+        util.assert_matmul_close(y_np[r0:r1, c0:c1], want, f"{what} tile ({i},{j})")
+
+
+@pytest.mark.parametrize("n,k", GEMM_SHAPES)
+@pytest.mark.parametrize("m", [16, 64, 255, 1024, 4096, 8192])
+def test_gemm_baseline(cuda_device, m, n, k):
+    x = seeded_normal((m, k), config_seed(4, 0), "float16")
+    w = seeded_normal((n, k), config_seed(4, 1), "float16", scale=0.02)
+    xd, wd = x.to(cuda_device), w.to(cuda_device)
+    big, y = guarded((m, n), torch.float16, cuda_device, 5.0)
+    ops.gemm_nt(xd, wd, y)
+    ops.poll_status()
+    y_np = np_of(y)
+    assert_guards(big, m * n, 5.0, f"gemm m={m} n={n} k={k}")
+    _check_gemm_tiles(y_np, x, w, m, n, k, f"gemm m={m} n={n} k={k} [{_abi.variant_of('gemm', m, n, k)}]")
+    # Whole-matrix cross-check against the library GEMM (checker only, never the product path).
+    ref = (xd @ wd.T).float()
+    err = (y.float() - ref).abs().max().item()
+    scale = ref.abs().max().item()
+    assert err <= 2e-2 * scale, f"gemm m={m} n={n} k={k}: max abs diff {err} vs library GEMM (scale {scale})"
+
+
+def test_gemm_small_m_full_oracle(cuda_device):
+    """m <= 255 at (4096, 4096): every element against the C oracle (k-ordered fp32 sum)."""
+    n, k = 4096, 4096
+    w = seeded_normal((n, k), config_seed(4, 1), "float16", scale=0.02)
+    wd = w.to(cuda_device)
+    for m in (1, 16, 255):
+        x = seeded_normal((m, k), config_seed(4, 0), "float16")
+        y = torch.empty((m, n), dtype=torch.float16, device=cuda_device)
+        ops.gemm_nt(x.to(cuda_device), wd, y)
+        ops.poll_status()
+        util.assert_matmul_close(np_of(y), oracle.gemm_nt(x.numpy(), w.numpy()).astype(np.float32), f"gemm m={m} full")
+
+
+@pytest.mark.parametrize("bn,split", [(64, 1), (128, 1), (256, 1), (64, 4), (128, 3), (256, 2), (128, 16)])
+def test_gemm_every_tile_width_and_split(cuda_device, bn, split):
+    """Forces each kernel instantiation and split factor on ragged shapes (m, n, k not
+    multiples of the tile), with a bias, writing into a column slab of a wider buffer."""
+    m, n, k = 200, 1000, 2120
+    x = seeded_normal((m, k), 90, "float16")
+    w = seeded_normal((n, k), 91, "float16", scale=0.02)
+    b = seeded_normal((n,), 92, "float16", scale=0.1)
+    wide = torch.full((m, n + 24), 5.0, dtype=torch.float16, device=cuda_device)
+    y = wide[:, 8:8 + n]
+    _abi.check(_abi.lib().dtas_gemm_set_override(bn, split))
+    try:
+        ops.gemm_nt(x.to(cuda_device), w.to(cuda_device), y, bias=b.to(cuda_device))
+        ops.poll_status()
+        ops.gemm_nt(x.to(cuda_device), w.to(cuda_device), y, bias=b.to(cuda_device))  # counters re-armed?
+        ops.poll_status()
+    finally:
+        _abi.check(_abi.lib().dtas_gemm_set_override(0, 0))
+    want = x.float().numpy() @ w.float().numpy().T + b.float().numpy()
+    util.assert_matmul_close(np_of(y), want, f"gemm bn={bn} split={split}")
+    assert bool((wide[:, :8] == 5.0).all()) and bool((wide[:, 8 + n:] == 5.0).all()), "wrote outside its column slab"
+
+
+def test_gemm_unaligned_k_uses_fallback(cuda_device):
+    m, n, k = 33, 70, 101
+    x = seeded_normal((m, k), 93, "float16")
+    w = seeded_normal((n, k), 94, "float16", scale=0.02)
+    y = torch.empty((m, n), dtype=torch.float16, device=cuda_device)
+    ops.gemm_nt(x.to(cuda_device), w.to(cuda_device), y)
+    util.assert_matmul_close(np_of(y), x.float().numpy() @ w.float().numpy().T, "gemm simt fallback")
+
+
+def test_gemm_linearity_full_size(cuda_device):
+    """Size-independent property at the largest shape: X -> 2X doubles Y exactly (powers of
+    two commute with every rounding), and the split-K path is deterministic run to run."""
+    m, n, k = 8192, 22016, 4096
+    x = seeded_normal((m, k), 95, "float16").to(cuda_device)
+    w = seeded_normal((n, k), 96, "float16", scale=0.02).to(cuda_device)
+    y1 = torch.empty((m, n), dtype=torch.float16, device=cuda_device)
+    y2 = torch.empty_like(y1)
+    ops.gemm_nt(x, w, y1)
+    ops.gemm_nt(x * 2, w, y2)
+    ops.poll_status()
+    assert torch.equal(y1 * 2, y2)
+    del y1, y2
+    xs = x[:64].contiguous()
+    a = torch.empty((64, n), dtype=torch.float16, device=cuda_device)
+    b = torch.empty_like(a)
+    ops.gemm_nt(xs, w, a)
+    ops.gemm_nt(xs, w, b)
+    ops.poll_status()
+    assert torch.equal(a, b)
+
+
+# ---------------------------------------------------------------------------------------
+# golden fixtures (outputs of the TVM build of the PrimFuncs)
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_against_tvm_golden(cuda_device, name):
+    case = CASES[name]
+    ins, out = make_inputs(case)
+    want = util.load_golden(case["op"])[name]
+    d = [torch.from_numpy(a).to(cuda_device) for a in ins]
+    y = torch.from_numpy(out).to(cuda_device)
+    op = case["op"]
+    if op == "cast":
+        ops.cast(d[0], y)
+    elif op == "add":
+        ops.add(d[0], d[1], y)
+    elif op == "copy":
+        ops.copy(d[0], y)
+    elif op == "rms_norm":
+        ops.rms_norm(d[0], d[1], y, eps=case["eps"])
+    elif op == "softmax":
+        ops.softmax(d[0], y)
+    elif op == "layer_norm":
+        ops.layer_norm(d[0], d[1], d[2], y, eps=case["eps"])
+    elif op == "gemv":
+        ops.gemv(d[0].view(1, -1), d[1], y.view(1, -1))
+    elif op == "gemm":
+        ops.gemm_nt(d[0], d[1], y)
+        ops.poll_status()
+    got = np_of(y).reshape(want.shape)
+    if op in ("cast", "add", "copy"):
+        util.assert_bit_exact(got, want, name)
+    elif op in ("gemv", "gemm"):
+        util.assert_matmul_close(got, want.astype(np.float32), name)
+    else:
+        util.assert_reduction_close(got, want, name)

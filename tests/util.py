@@ -1,0 +1,62 @@
+"""Comparison rules of the parity tests.
+
+  * cast / add / copy: bit-exact (compared as raw integer views);
+  * row reductions: |a - b| <= 1e-3 * |b| + 1 fp16 ULP of b.  1e-3 relative is about one
+    fp16 ULP (2^-10), and a different summation order can flip the final fp16 rounding by
+    one ULP; softmax outputs reach the fp16 subnormal range where one ULP is far more than
+    1e-3 relative.  The ULP term is stated, not hidden;
+  * GEMM / GEMV: |a - b| <= 1e-2 * |b| + 1e-2 * rms(b), against an fp32-accumulated reference.
+"""
+import os
+
+import numpy as np
+
+GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def load_golden(op):
+    return np.load(os.path.join(GOLDEN_DIR, f"{op}.npz"))
+
+
+def bits(a):
+    a = np.ascontiguousarray(a)
+    return a.view({1: np.uint8, 2: np.uint16, 4: np.uint32}[a.dtype.itemsize])
+
+
+def assert_bit_exact(got, want, what=""):
+    got, want = np.asarray(got), np.asarray(want)
+    assert got.shape == want.shape and got.dtype == want.dtype, (what, got.shape, want.shape, got.dtype, want.dtype)
+    bad = np.nonzero(bits(got).reshape(-1) != bits(want).reshape(-1))[0]
+    assert bad.size == 0, f"{what}: {bad.size} of {got.size} elements differ, first at flat index {bad[0]}"
+
+
+def fp16_ulp(x):
+    """Spacing of fp16 numbers at |x| (subnormal spacing 2^-24 below 2^-14)."""
+    ax = np.abs(np.asarray(x, np.float32))
+    e = np.floor(np.log2(np.maximum(ax, 2.0 ** -14)))
+    return np.exp2(e - 10).astype(np.float32)
+
+
+def assert_reduction_close(got, want, what="", rel=1e-3):
+    g = np.asarray(got, np.float32).reshape(-1)
+    w = np.asarray(want, np.float32).reshape(-1)
+    assert g.shape == w.shape, (what, g.shape, w.shape)
+    assert np.isfinite(g).all(), f"{what}: non-finite values"
+    tol = rel * np.abs(w) + fp16_ulp(w)
+    err = np.abs(g - w)
+    bad = np.nonzero(err > tol)[0]
+    assert bad.size == 0, (f"{what}: {bad.size} of {g.size} outside 1e-3 rel + 1 fp16 ULP; worst "
+                           f"got {g[bad[0]]} want {w[bad[0]]}")
+
+
+def assert_matmul_close(got, want_f32, what="", rel=1e-2):
+    g = np.asarray(got, np.float32).reshape(-1)
+    w = np.asarray(want_f32, np.float32).reshape(-1)
+    assert g.shape == w.shape, (what, g.shape, w.shape)
+    assert np.isfinite(g).all(), f"{what}: non-finite values"
+    rms = float(np.sqrt(np.mean(w.astype(np.float64) ** 2)))
+    tol = rel * np.abs(w) + rel * rms
+    err = np.abs(g - w)
+    bad = np.nonzero(err > tol)[0]
+    assert bad.size == 0, (f"{what}: {bad.size} of {g.size} outside 1e-2 rel (+1e-2 rms floor); worst "
+                           f"got {g[bad[0]]} want {w[bad[0]]} rms {rms}")
