@@ -1,0 +1,126 @@
+"""Runtime module: what `Engine.tune_module` returns and `load_module_from_file` reloads.
+
+The reference packs generated host code and a cubin into a `tvm.runtime.Module`
+(python/dtas/codegen/runtime_packer.py:237-258) and reloads it from `work_dir`
+(:260-283); users then call `rt_mod["cast"](x, y)` and
+`rt_mod.time_evaluator("cast", dev, number=5, min_repeat_ms=50)`
+(experiment/dtas_tuned/elementwise/cast/profile_cast.py:8-20).  Here the kernels already live
+in libdtas_b200.so, so the module is the record of bound functions (operator, dtypes, static
+dims, merged ranges, index table) stored as JSON in `work_dir`; reloading rebuilds nothing.
+"""
+import json
+import os
+
+import torch
+
+from .. import _abi, ops
+from ..profiling import time_op
+from ..reference import torch_dtype
+from ..workloads.spec import OpSpec
+
+MODULE_FILE = "dtas_b200_module.json"
+
+
+class BenchmarkResult:
+    """Shape of TVM's time_evaluator result: `.mean`, `.min`, `.results` in seconds."""
+
+    def __init__(self, t):
+        self.mean = t["mean_us"] * 1e-6
+        self.min = t["min_us"] * 1e-6
+        self.results = [self.mean]
+        self.launches = t["launches"]
+
+    def __repr__(self):
+        return f"BenchmarkResult(mean={self.mean * 1e6:.2f} us, min={self.min * 1e6:.2f} us, launches={self.launches})"
+
+
+class PackedOp:
+    """One bound function: destination-passing call on torch tensors."""
+
+    def __init__(self, name, entry):
+        self.name = name
+        self.entry = entry
+        self.spec = OpSpec.from_dict(entry["spec"])
+
+    def bucket_index(self, m):
+        """Position in the merged range list that serves row count m (clamped above the bound)."""
+        table = self.entry["index_table"]
+        if not table:
+            return 0
+        width = self.entry["range_div_factor"]
+        return table[min((m - 1) // width, len(table) - 1)]
+
+    def _expect(self, t, dtype, cols, what):
+        if t.dtype != torch_dtype(dtype):
+            raise _abi.DtasError(_abi.EINVAL, f"{self.name}: {what} must be {dtype}, got {t.dtype}")
+        if cols and t.shape[-1] != cols:
+            raise _abi.DtasError(_abi.EINVAL, f"{self.name}: {what} last dim must be {cols}, got {t.shape[-1]}")
+
+    def __call__(self, *args):
+        s = self.spec
+        n_in = {"cast": 1, "copy": 1, "softmax": 1, "add": 2, "rms_norm": 2, "layer_norm": 3,
+                "gemv": 2 + int(s.bias), "gemm": 2 + int(s.bias)}[s.op]
+        if len(args) != n_in + 1:
+            raise _abi.DtasError(_abi.EINVAL, f"{self.name}: expected {n_in} input(s) and 1 output, got {len(args)} tensors")
+        out = args[-1]
+        if s.op in ("cast", "copy", "add", "rms_norm", "softmax", "layer_norm"):
+            self._expect(args[0], s.in_dtype, s.cols, "input")
+            self._expect(out, s.out_dtype, s.cols, "output")
+        if s.op == "cast":
+            return ops.cast(args[0], out)
+        if s.op == "copy":
+            return ops.copy(args[0], out)
+        if s.op == "add":
+            return ops.add(args[0], args[1], out)
+        if s.op == "rms_norm":
+            return ops.rms_norm(args[0], args[1], out, eps=s.eps)
+        if s.op == "softmax":
+            return ops.softmax(args[0], out)
+        if s.op == "layer_norm":
+            return ops.layer_norm(args[0], args[1], args[2], out, eps=s.eps)
+        if s.op in ("gemv", "gemm"):
+            self._expect(args[0], "float16", s.k, "x")
+            if tuple(args[1].shape) != (s.cols, s.k):
+                raise _abi.DtasError(_abi.EINVAL, f"{self.name}: weight must be [{s.cols}, {s.k}], got {tuple(args[1].shape)}")
+            bias = args[2] if s.bias else None
+            if s.op == "gemv":
+                return ops.gemv(args[0], args[1], out, bias=bias)
+            return ops.gemm_nt(args[0], args[1], out, bias=bias)
+        raise _abi.DtasError(_abi.EUNSUPPORTED, f"{self.name}: unknown op {s.op}")
+
+
+class RuntimeModule:
+    def __init__(self, record):
+        _abi.lib()   # fail here, loudly, if the kernel library is missing
+        self.record = record
+        self._funcs = {name: PackedOp(name, e) for name, e in record["functions"].items()}
+
+    def __getitem__(self, name):
+        return self._funcs[name]
+
+    get_function = __getitem__
+
+    def __contains__(self, name):
+        return name in self._funcs
+
+    def keys(self):
+        return self._funcs.keys()
+
+    def time_evaluator(self, func_name, dev=None, number=5, min_repeat_ms=50, repeat=1):
+        """Returns f(*tensors) -> BenchmarkResult; same knobs as TVM's time_evaluator."""
+        fn = self._funcs[func_name]
+
+        def evaluator(*args):
+            t = time_op(lambda i: fn(*args), warmup=3, number=max(number, repeat), min_repeat_ms=min_repeat_ms)
+            return BenchmarkResult(t)
+
+        return evaluator
+
+
+def load_module_from_file(work_dir: str) -> RuntimeModule:
+    """Reloads the module `Engine(work_dir=...).tune_module` stored in work_dir."""
+    path = os.path.join(work_dir, MODULE_FILE)
+    if not os.path.exists(path):
+        raise FileNotFoundError(f"{path} not found: run Engine(work_dir=...).tune_module first")
+    with open(path) as f:
+        return RuntimeModule(json.load(f))

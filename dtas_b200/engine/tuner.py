@@ -1,0 +1,150 @@
+"""Engine: the entry point of the library, same call shape as the reference.
+
+    Engine(topk, parallel_build, work_dir).tune_module(mod, arch, range_div_factor) -> runtime module
+
+In the reference this runs a search: per PrimFunc and per range of the symbolic dim it asks a
+policy for top-k schedule candidates, builds and times each with TVM, keeps the best, merges
+neighbouring ranges that chose the same config and emits the index table of the generated
+host code (python/dtas/engine/tuner.py:26-51, 53-133, 135-154, 156-209, 211-299).
+
+Here the kernels are hand-written and the choice per call shape is made inside the library
+(ew_cfg / row_cfg / pick_wpr / plan_gemm in dtas_b200/csrc), so nothing is built or timed:
+`tune_module` classifies each function, walks the same ranges, asks the library which kernel
+variant each range dispatches to, merges equal neighbours exactly as the reference does, and
+returns a runtime module whose functions call the C ABI.  `topk` and `parallel_build` are
+accepted for compatibility and unused.  The bucket index is min((m - 1) / width, last): the
+reference's `n / 256` sends n = 256 to the second bucket (tuner.py:171-174), which is not
+reproduced.
+"""
+import json
+import os
+from typing import Dict, List, Tuple
+
+from .. import _abi
+from ..codegen.runtime_packer import MODULE_FILE, RuntimeModule
+from ..common.analysis import FuncInfo, UnsupportedWorkload
+from ..common.config import Config, Range, config_for, generate_range_list
+from ..logging import debug_info, get_log_level
+from ..workloads.spec import OpSpec
+
+DEFAULT_UPPER_BOUND = 2048   # the reference's default when no tir_var_upper_bound is given
+
+
+class Engine:
+    def __init__(self, topk: int = 10, parallel_build: bool = True, work_dir: str = None) -> None:
+        self.topk = topk
+        self.parallel_build = parallel_build
+        self.work_dir = work_dir
+        self.upper_bound: Dict[str, int] = {}
+        if work_dir is not None:
+            os.makedirs(work_dir, exist_ok=True)
+
+    # -- module handling -------------------------------------------------------------------
+    @staticmethod
+    def _functions(mod) -> List[Tuple[str, object]]:
+        """(name, PrimFunc | OpSpec) pairs of an IRModule, a dict, a list of OpSpec or one OpSpec."""
+        if isinstance(mod, OpSpec):
+            return [(mod.name, mod)]
+        if isinstance(mod, (list, tuple)):
+            return [(s.name, s) for s in mod]
+        if isinstance(mod, dict):
+            return list(mod.items())
+        if hasattr(mod, "functions"):      # tvm.IRModule; Relax functions are not kernels
+            out = []
+            for gv, func in mod.functions.items():
+                if type(func).__name__ == "PrimFunc":
+                    out.append((gv.name_hint, func))
+            return out
+        raise TypeError(f"cannot read functions from {type(mod).__name__}")
+
+    def _collect_upper_bounds(self, mod):
+        """`tir_var_upper_bound` may sit on any function of the module (tuner.py:62-65)."""
+        if not hasattr(mod, "functions"):
+            return
+        for _, func in mod.functions.items():
+            if func.attrs is not None and "tir_var_upper_bound" in func.attrs:
+                for k, v in func.attrs["tir_var_upper_bound"].items():
+                    self.upper_bound[str(k)] = int(v)
+
+    # -- ranges ----------------------------------------------------------------------------
+    def gen_range_tuples(self, func_info: FuncInfo, range_div_factor: int):
+        if len(func_info.dynamic_args) == 0:
+            return [()]
+        range_lists = []
+        for dyn in func_info.dynamic_args:
+            upper = func_info.spec.upper or self.upper_bound.get(dyn) or DEFAULT_UPPER_BOUND
+            self.upper_bound[dyn] = upper
+            range_lists.append(generate_range_list(dyn, 1, upper, range_div_factor))
+        if len(range_lists) > 1:
+            raise UnsupportedWorkload("kernels of this library take one symbolic dim (the row count)")
+        return [(r,) for r in range_lists[0]]
+
+    @staticmethod
+    def merge_same_configs(range_to_config: Dict[Tuple[Range], Config]) -> Dict[Tuple[Range], Config]:
+        """Adjacent ranges with equal configs collapse into one (tuner.py:211-299)."""
+        merged: List[Tuple[Tuple[Range], Config]] = []
+        for rt, cfg in range_to_config.items():
+            if merged and len(rt) == 1 and merged[-1][1] == cfg:
+                prev = merged[-1][0][0]
+                merged[-1] = ((prev.merge(rt[0]),), cfg)
+            else:
+                merged.append((rt, cfg))
+        return dict(merged)
+
+    def get_index_table(self, merged: Dict[Tuple[Range], Config], range_div_factor: int):
+        """index_table[i] = position in `merged` of the config serving bucket i, plus the
+        statement that computes the bucket index from the dynamic dim (tuner.py:156-209)."""
+        items = list(merged.items())
+        if not items or len(items[0][0]) == 0:
+            return [], ""
+        name = items[0][0][0].var
+        table = []
+        for i, (rt, _) in enumerate(items):
+            table += [i] * len(range(rt[0].start, rt[0].end + 1, range_div_factor))
+        last = len(table) - 1
+        stmt = f"int64_t index = (({name} - 1)/{range_div_factor}) > {last} ? {last} : ({name} - 1)/{range_div_factor};"
+        return table, stmt
+
+    # -- per function ------------------------------------------------------------------------
+    def tune_func(self, func, name: str, arch, range_div_factor: int):
+        info = FuncInfo(func, name)
+        spec = info.spec
+        if get_log_level() >= 2:
+            debug_info(f"{name}: {info.kind.name} {spec}")
+        range_to_config: Dict[Tuple[Range], Config] = {}
+        for rt in self.gen_range_tuples(info, range_div_factor):
+            m = rt[0].end if rt else 1
+            variant = _abi.variant_of(spec.op, m, spec.cols, spec.k, getattr(arch, "dev_id", -1))
+            range_to_config[rt] = config_for(spec.kind, variant)
+        merged = self.merge_same_configs(range_to_config)
+        table, stmt = self.get_index_table(merged, range_div_factor)
+        return info, merged, table, stmt
+
+    def tune_module(self, mod, arch, range_div_factor: int = 256):
+        self._collect_upper_bounds(mod)
+        entries = {}
+        for name, func in self._functions(mod):
+            try:
+                info, merged, table, stmt = self.tune_func(func, name, arch, range_div_factor)
+            except UnsupportedWorkload as e:
+                if get_log_level() >= 1:
+                    debug_info(f"skipping {name}: {e}")
+                continue
+            entries[name] = {
+                "spec": info.spec.to_dict(),
+                "kind": info.kind.name,
+                "dynamic_args": info.dynamic_args,
+                "range_div_factor": range_div_factor,
+                "ranges": [{"start": rt[0].start, "end": rt[0].end, "suffix": rt[0].to_suffix(),
+                            "config": cfg.to_dict()} if rt else {"config": cfg.to_dict()}
+                           for rt, cfg in merged.items()],
+                "index_table": table,
+                "index_stmt": stmt,
+            }
+            if get_log_level() >= 1:
+                debug_info(f"{name}: {info.kind.name}, {len(merged)} merged range(s)")
+        record = {"library": _abi.lib().dtas_version().decode(), "arch": type(arch).__name__, "functions": entries}
+        if self.work_dir is not None:
+            with open(os.path.join(self.work_dir, MODULE_FILE), "w") as f:
+                json.dump(record, f, indent=1)
+        return RuntimeModule(record)

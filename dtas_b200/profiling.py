@@ -44,10 +44,17 @@ def rotation_for(bytes_per_call, min_total=2 * L2_BYTES, max_copies=64):
     return int(max(1, min(max_copies, n)))
 
 
-def time_op(fn, warmup=3, number=5, min_repeat_ms=50.0, batch=None, max_batches=200, stream=None):
+def time_op(fn, warmup=3, number=5, min_repeat_ms=50.0, batch=None, max_batches=200, stream=None,
+            graph=False):
     """fn(i) launches the op once (i = running launch index).  Returns
     {"mean_us", "min_us", "launches", "batches"} measured with CUDA events on `stream`
-    (default: the current torch stream, which is where dtas_b200.ops launches)."""
+    (default: the current torch stream, which is where dtas_b200.ops launches).
+
+    graph=False times eager calls: what a Python caller sees, host overhead included when the
+    kernel is shorter than the call path.  graph=True captures one batch of launches into a
+    CUDA graph and replays it: device time of the kernels back to back, the figure to hold
+    against a roofline.  The op calls allocate nothing and never synchronise, so they capture
+    as they are (first-use set-up happens in the warm-up calls)."""
     stream = stream or torch.cuda.current_stream()
     it = 0
     for _ in range(max(1, warmup)):
@@ -64,22 +71,39 @@ def time_op(fn, warmup=3, number=5, min_repeat_ms=50.0, batch=None, max_batches=
         e1.record(stream)
         e1.synchronize()
         per = max(e0.elapsed_time(e1) / 4.0, 1e-3)
-        batch = int(max(1, min(1000, round(2.0 / per))))
+        batch = int(max(1, min(400, round(2.0 / per))))
+    replay = None
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(stream)
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(g, stream=side):
+                for j in range(batch):
+                    fn(it + j)
+        it += batch
+        stream.wait_stream(side)
+        replay = g.replay
+        replay()
+        stream.synchronize()
     times = []
     total_ms = 0.0
     while (len(times) < number or total_ms < min_repeat_ms) and len(times) < max_batches:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
-        for _ in range(batch):
-            fn(it)
-            it += 1
+        if replay is not None:
+            replay()
+        else:
+            for _ in range(batch):
+                fn(it)
+                it += 1
         e1.record(stream)
         e1.synchronize()
         ms = e0.elapsed_time(e1)
         times.append(ms / batch)
         total_ms += ms
     return {"mean_us": 1e3 * sum(times) / len(times), "min_us": 1e3 * min(times),
-            "launches": batch * len(times), "batches": len(times)}
+            "launches": batch * len(times), "batches": len(times), "mode": "graph" if graph else "eager"}
 
 
 # Algorithmic bytes / flops per call of each operator (GB = 1e9 B).

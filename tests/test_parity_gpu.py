@@ -156,7 +156,8 @@ def test_reference_reduction_workloads_fp32_in(cuda_device):
         b = seeded_normal((2560,), 62, "float32", scale=0.1)
         y = torch.empty((1, m, 2560), dtype=torch.float16, device=cuda_device)
         ops.layer_norm(x.to(cuda_device), g.to(cuda_device), b.to(cuda_device), y, eps=1e-5)
-        util.assert_reduction_close(np_of(y), oracle.layer_norm(x.numpy(), g.numpy(), b.numpy(), 1e-5), f"layer_norm m={m}")
+        util.assert_reduction_close(np_of(y), oracle.layer_norm(x.numpy(), g.numpy(), b.numpy(), 1e-5), f"layer_norm m={m}",
+                                    abs_floor=1e-6)
         ops.softmax(x.to(cuda_device), y)
         util.assert_reduction_close(np_of(y), oracle.softmax(x.numpy()), f"softmax f32 m={m}")
 
@@ -287,8 +288,10 @@ def test_gemm_unaligned_k_uses_fallback(cuda_device):
 
 
 def test_gemm_linearity_full_size(cuda_device):
-    """Size-independent property at the largest shape: X -> 2X doubles Y exactly (powers of
-    two commute with every rounding), and the split-K path is deterministic run to run."""
+    """Size-independent properties at the largest shape: X -> 2X doubles Y exactly wherever Y
+    is a normal fp16 number (a power of two commutes with every rounding except the fixed
+    2^-24 grid of fp16 subnormals, where it may move the result by one grid step); the same
+    call twice gives the same bits, with and without split-K."""
     m, n, k = 8192, 22016, 4096
     x = seeded_normal((m, k), 95, "float16").to(cuda_device)
     w = seeded_normal((n, k), 96, "float16", scale=0.02).to(cuda_device)
@@ -297,8 +300,14 @@ def test_gemm_linearity_full_size(cuda_device):
     ops.gemm_nt(x, w, y1)
     ops.gemm_nt(x * 2, w, y2)
     ops.poll_status()
-    assert torch.equal(y1 * 2, y2)
-    del y1, y2
+    normal = y1.abs() >= 2.0 ** -14
+    assert torch.equal((y1 * 2)[normal], y2[normal])
+    assert float(((y1 * 2)[~normal].float() - y2[~normal].float()).abs().max()) <= 2.0 ** -24 + 1e-12
+    ops.gemm_nt(x, w, y2)
+    ops.gemm_nt(x, w, y2)
+    ops.poll_status()
+    assert torch.equal(y1, y2), "two runs of the same GEMM differ"
+    del y1, y2, normal
     xs = x[:64].contiguous()
     a = torch.empty((64, n), dtype=torch.float16, device=cuda_device)
     b = torch.empty_like(a)
@@ -342,4 +351,4 @@ def test_against_tvm_golden(cuda_device, name):
     elif op in ("gemv", "gemm"):
         util.assert_matmul_close(got, want.astype(np.float32), name)
     else:
-        util.assert_reduction_close(got, want, name)
+        util.assert_reduction_close(got, want, name, abs_floor=1e-6 if op == "layer_norm" else 0.0)
