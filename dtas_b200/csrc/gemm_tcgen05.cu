@@ -569,8 +569,8 @@ constexpr int kTileCounters = 4096;
 // wave-quantised roofline model and keep the best), restated for one persistent CTA per
 // SM.  For each (BN, splits) candidate the model charges per k-block the larger of
 //   * the tensor/shared-memory time: max(2*BN MMA clocks, operand bytes / 128 B per clock),
-//   * the HBM time of the W tile (plus the amortised X tile) at this CTA's share of the
-//     device bandwidth,
+//   * the HBM time of the distinct X and W tiles that the CTAs running side by side touch
+//     (tiles shared inside a rasterisation band come from L2),
 // adds a fixed fill/drain cost per work item, multiplies by the number of rounds
 // ceil(work / SMs), and adds the partial-sum traffic of a split.  Larger BN wins ties.
 GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
@@ -604,11 +604,16 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
       const double active = (double)(work < sm_count ? work : sm_count);
       const double smem_clk = (double)(BM * BK * 2 + bn * BK * 2) / 128.0;
       const double mma_clk = 2.0 * bn;
-      const double t_core = (mma_clk > smem_clk ? mma_clk : smem_clk) / kClockGHz;
+      // Narrow tiles re-read the X tile from shared memory per MMA and ran at 0.7x / 0.45x
+      // the per-flop rate of BN = 256 when measured on B200.
+      const double narrow = bn == 256 ? 1.0 : (bn == 128 ? 1.4 : 2.2);
+      const double t_core = narrow * (mma_clk > smem_clk ? mma_clk : smem_clk) / kClockGHz;
+      // HBM bytes per k-block over the whole machine: the CTAs running side by side cover
+      // am m-tiles x an n-tiles of one band and share those X and W tiles through L2.
       const double rows_x = (double)(m < BM ? m : BM);
-      const double share = (double)(n_tiles < 8 ? n_tiles : 8);
-      const double bytes = 128.0 * bn + 128.0 * rows_x / share;
-      const double t_hbm = bytes / (kHbmGBs / active);
+      const double am = (double)(m_tiles < kGroupM ? m_tiles : kGroupM);
+      const double an = active / am < 1.0 ? 1.0 : active / am;
+      const double t_hbm = 128.0 * (an * bn + am * rows_x) / kHbmGBs;
       double cost = (double)rounds * (kb_per * (t_core > t_hbm ? t_core : t_hbm) + kItemFixedNs);
       if (s > 1) cost += 2.0 * s * (double)m * (double)n * 4.0 / kHbmGBs + 1000.0;
       if (cost < best * 0.999) {

@@ -1,0 +1,111 @@
+"""Multi-GPU sharding of the operator classes: one process per GPU, torch.distributed plumbing.
+
+The reference is single-GPU.  The operators shard without any exchange on the data path:
+  * GEMM / GEMV by output columns: rank r owns W[r*N/g : (r+1)*N/g, :] (loaded once) and
+    computes Y[:, r*N/g : (r+1)*N/g] with the single-GPU kernel; X is replicated.  K is never
+    split across GPUs, so every output element is produced by exactly the arithmetic of the
+    single-GPU run and a gathered result is bit-identical to it.
+  * cast / add / copy / RMSNorm / softmax by rows, remainder rows to the low ranks; a rank
+    with no rows launches nothing.
+A collective is needed only when the caller wants the full GEMM / GEMV output on every rank:
+one all-gather (NCCL over NVLink on GPUs).  The kernel epilogue writes each rank's column slab
+straight into its slot of the gather buffer, laid out [g, m, N/g]; `as_row_major` turns that
+into [m, N] with one local copy when a caller needs the row-major form.
+"""
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_range(total: int, rank: int, world: int) -> Tuple[int, int]:
+    """Contiguous split of `total` items, remainder on the low ranks -> (start, count)."""
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError(f"bad rank {rank} of {world}")
+    base, rem = divmod(int(total), world)
+    count = base + (1 if rank < rem else 0)
+    start = rank * base + min(rank, rem)
+    return start, count
+
+
+def shard_rows(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """This rank's rows of a [m, H] tensor (a view; may have zero rows)."""
+    start, count = shard_range(t.shape[0], rank, world)
+    return t[start:start + count]
+
+
+def shard_weight(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """This rank's output columns of an NT weight: rows [start, start+count) of W[N, K]."""
+    start, count = shard_range(w.shape[0], rank, world)
+    return w[start:start + count].contiguous()
+
+
+class ColumnShardedLinear:
+    """Y = X W^T with W split by output columns over the ranks of `group`.
+
+    `compute` is the kernel entry (default: dtas_b200.ops.gemm_nt, or ops.gemv for one row);
+    it is a parameter so the host-side logic can be exercised on CPU ranks.
+    """
+
+    def __init__(self, w_full_or_shard: torch.Tensor, n_total: int, rank: Optional[int] = None,
+                 world: Optional[int] = None, group=None, compute: Optional[Callable] = None,
+                 already_sharded: bool = False):
+        self.group = group
+        self.rank = dist.get_rank(group) if rank is None else rank
+        self.world = dist.get_world_size(group) if world is None else world
+        self.n_total = int(n_total)
+        self.col_start, self.n_local = shard_range(self.n_total, self.rank, self.world)
+        self.w = w_full_or_shard if already_sharded else shard_weight(w_full_or_shard, self.rank, self.world)
+        if self.w.shape[0] != self.n_local:
+            raise ValueError(f"weight shard has {self.w.shape[0]} rows, expected {self.n_local}")
+        self.even = self.n_total % self.world == 0
+        self._compute = compute
+
+    def _kernel(self, x, w, out):
+        if self._compute is not None:
+            return self._compute(x, w, out)
+        from . import ops
+        if x.shape[0] == 1:
+            return ops.gemv(x, w, out)
+        return ops.gemm_nt(x, w, out)
+
+    def forward_local(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """This rank's column slab Y[:, col_start : col_start + n_local]; no communication."""
+        m = x.shape[0]
+        if out is None:
+            out = torch.empty((m, self.n_local), dtype=x.dtype, device=x.device)
+        self._kernel(x, self.w, out)
+        return out
+
+    def gather_buffer(self, m: int, dtype, device) -> torch.Tensor:
+        """[g, m, N/g] buffer; slot r is where rank r's kernel writes."""
+        if not self.even:
+            raise ValueError("gather buffer needs N divisible by the number of ranks")
+        return torch.empty((self.world, m, self.n_local), dtype=dtype, device=device)
+
+    def forward_gathered(self, x: torch.Tensor, buf: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Full output on every rank as [g, m, N/g]: kernel into this rank's slot, then one
+        all-gather in place."""
+        m = x.shape[0]
+        if buf is None:
+            buf = self.gather_buffer(m, x.dtype, x.device)
+        self._kernel(x, self.w, buf[self.rank])
+        if self.world > 1:
+            dist.all_gather_into_tensor(buf.view(-1), buf[self.rank].reshape(-1), group=self.group)
+        return buf
+
+    @staticmethod
+    def as_row_major(buf: torch.Tensor) -> torch.Tensor:
+        """[g, m, N/g] -> [m, N] (one local copy)."""
+        g, m, nl = buf.shape
+        return buf.permute(1, 0, 2).reshape(m, g * nl)
+
+
+def row_sharded(fn: Callable, rank: int, world: int, *tensors_then_out):
+    """Runs an elementwise / row-reduction op on this rank's rows of every [m, H] argument.
+    1-D arguments (norm weights) are passed whole.  Returns the output shard (maybe empty)."""
+    shards = [shard_rows(t, rank, world) if t.dim() >= 2 else t for t in tensors_then_out]
+    if shards[-1].shape[0] == 0:
+        return shards[-1]
+    fn(*shards)
+    return shards[-1]

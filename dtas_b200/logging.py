@@ -1,5 +1,6 @@
 """Global verbosity switch and a caller-tagged print, as in python/dtas/logging.py:1-19."""
 import inspect
+import sys
 
 _verbose = 1
 
@@ -15,4 +16,4 @@ def get_log_level():
 
 def debug_info(message: str):
     frame = inspect.stack()[1]
-    print(f"({frame[1]}:{frame[2]}):{message}")
+    print(f"({frame[1]}:{frame[2]}):{message}", file=sys.stderr)

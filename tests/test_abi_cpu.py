@@ -1,0 +1,95 @@
+"""C-ABI checks that need no GPU: the library loads, exports everything the header declares,
+and rejects bad arguments before it touches a device."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from dtas_b200 import _abi
+from dtas_b200.build import LIB_PATH, build_library
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    build_library()
+    return _abi.lib()
+
+
+def test_library_exports_every_declared_symbol(lib):
+    header = open(os.path.join(ROOT, "include", "dtas_b200.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(dtas_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    assert declared == set(_abi.PROTOTYPES), (declared ^ set(_abi.PROTOTYPES))
+    raw = ctypes.CDLL(LIB_PATH)
+    for name in declared:
+        assert hasattr(raw, name), f"{name} is declared in include/dtas_b200.h but not exported"
+    assert lib.dtas_version().decode().startswith("dtas_b200")
+
+
+def test_bucket_index_is_total_monotone_and_clamped(lib):
+    # bucket = min((m-1)/256, last): 1-based ranges, no off-by-one at multiples of the width
+    assert _abi.bucket_of("cast", 1) == 0
+    assert _abi.bucket_of("cast", 256) == 0
+    assert _abi.bucket_of("cast", 257) == 1
+    assert _abi.bucket_of("gemm", 4096) == 15
+    count = lib.dtas_bucket_count(b"gemm")
+    assert count == 32
+    prev = 0
+    for m in range(1, 2 * 8192 + 2, 7):
+        b = _abi.bucket_of("gemm", m)
+        assert 0 <= b < count and b >= prev
+        prev = b
+    assert _abi.bucket_of("gemm", 10 ** 9) == count - 1          # clamp above the bound
+    assert _abi.bucket_of("gemm", 0) == -1 and _abi.bucket_of("gemm", -5) == -1
+    assert _abi.bucket_of("nonsense", 5) == -1
+
+
+def test_variant_names(lib):
+    assert _abi.variant_of("cast", 1, 4096) == "ew_vec16_unroll1"
+    assert _abi.variant_of("add", 8192, 11008) == "ew_vec16_unroll4"
+    assert "softmax_regs" in _abi.variant_of("softmax", 4096, 4096)
+    assert "generic" in _abi.variant_of("rms_norm", 4, 101)
+    assert _abi.variant_of("gemv", 1, 4096, 4096).startswith("gemv_vec16")
+    assert _abi.variant_of("gemm", 8192, 22016, 4096) == "gemm_tcgen05_bm128_bn256_bk64_s4_splitk1"
+    assert _abi.variant_of("gemm", 33, 70, 101) == "gemm_simt_fallback"
+    with pytest.raises(_abi.DtasError):
+        _abi.variant_of("nope", 1, 1)
+
+
+def test_argument_validation_needs_no_device(lib):
+    buf = (ctypes.c_char * 64)()
+    p = ctypes.addressof(buf)
+    # m <= 0 is rejected (the reference asserts dynamic dims > 0)
+    assert lib.dtas_cast(p, p, 0, 4096, _abi.F32, _abi.F16, 0, None) == _abi.EINVAL
+    assert b"m must be > 0" in lib.dtas_last_error()
+    assert lib.dtas_add(p, p, p, -3, 8, _abi.F16, 0, None) == _abi.EINVAL
+    assert lib.dtas_copy(p, p, 1, 0, _abi.F16, 0, None) == _abi.EINVAL
+    assert lib.dtas_copy(p, p, 1, 8, 99, 0, None) == _abi.EUNSUPPORTED
+    # null pointers
+    assert lib.dtas_cast(None, p, 1, 8, _abi.F32, _abi.F16, 0, None) == _abi.EINVAL
+    assert b"NULL" in lib.dtas_last_error()
+    assert lib.dtas_rms_norm(p, None, p, 1, 8, 1e-6, _abi.F16, 0, None) == _abi.EINVAL
+    assert lib.dtas_softmax(p, p, 0, 8, _abi.F16, 0, None) == _abi.EINVAL
+    assert lib.dtas_gemv(p, p, None, p, 0, 8, _abi.F16, 0, None) == _abi.EINVAL
+    assert lib.dtas_gemv(p, p, None, p, 8, 8, _abi.F32, 0, None) == _abi.EUNSUPPORTED
+    assert lib.dtas_gemm_nt(p, p, None, p, 0, 8, 8, 8, _abi.F16, 0, None) == _abi.EINVAL
+    assert lib.dtas_gemm_nt(p, p, None, p, 4, 8, 8, 4, _abi.F16, 0, None) == _abi.EINVAL   # ldy < n
+    assert lib.dtas_gemm_set_override(100, 0) == _abi.EINVAL
+    assert lib.dtas_gemm_set_override(0, 0) == _abi.OK
+    with pytest.raises(_abi.DtasError) as e:
+        _abi.check(lib.dtas_cast(p, p, -1, 8, _abi.F32, _abi.F16, 0, None))
+    assert e.value.code == _abi.EINVAL
+
+
+def test_ops_reject_cpu_tensors():
+    import torch
+    from dtas_b200 import ops
+    a = torch.zeros(2, 8)
+    with pytest.raises(_abi.DtasError):
+        ops.cast(a, torch.zeros(2, 8, dtype=torch.float16))
+    with pytest.raises(_abi.DtasError):
+        ops.gemm_nt(a.half(), a.half(), torch.zeros(2, 2, dtype=torch.float16))
