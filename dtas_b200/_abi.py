@@ -41,6 +41,7 @@ PROTOTYPES = {
     "dtas_layer_norm": (_i, [_p, _p, _p, _p, _i64, _i64, _f, _i, _i, _p]),
     "dtas_gemv": (_i, [_p, _p, _p, _p, _i64, _i64, _i, _i, _p]),
     "dtas_gemm_nt": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _i, _p]),
+    "dtas_gemm_nt_static_scratch": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _i, _i, _p, _p]),
     "dtas_bucket_of": (_i, [ctypes.c_char_p, _i64]),
     "dtas_bucket_count": (_i, [ctypes.c_char_p]),
     "dtas_variant_of": (_i, [ctypes.c_char_p, _i64, _i64, _i64, _i, ctypes.c_char_p, _i]),

@@ -37,6 +37,8 @@
 // m >= ~1024, HBM (W stream) for small m.
 #include <cuda.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace dtas {
@@ -737,4 +739,124 @@ void gemm_variant_name(int64_t m, int64_t n, int64_t k, const DeviceCtx* ctx, ch
   snprintf(buf, len, "gemm_tcgen05_bm128_bn%d_bk64_s%d_splitk%d", p.bn, stages, p.splits);
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Split-K GEMM on scratch that lives inside the library image
+// ---------------------------------------------------------------------------------------
+// Some hosts of this library cannot create device memory at the moment they call it: an
+// inference runtime that handed the whole device to its own pool at start-up (a later
+// cudaMalloc fails or eats into what the pool left), or a process under a fixed memory
+// budget that is checked when the library is loaded, not while it runs.  For them the partial sums and the
+// arrival counters of the split-K reduction live in this file-scope array, which is part of
+// the module image: every GPU that loads the library holds these bytes from load to exit,
+// and nothing is ever allocated or freed by the entry point below.
+constexpr size_t kStaticPartialBytes = 8ull << 20;    // fp32 partial tiles: splits * m * n * 4 <= 8 MiB
+constexpr int kStaticTileCounters = 1024;             // one arrival counter per output tile
+constexpr size_t kStaticCounterBytes = kStaticTileCounters * sizeof(int);
+constexpr size_t kStaticTailBytes = kStaticCounterBytes + 256;   // counters + status word (padded)
+static __device__ __align__(256) unsigned char g_gemm_static_scratch[kStaticPartialBytes + kStaticTailBytes];
+
+namespace {
+
+struct StaticDev {
+  bool ready = false;
+  unsigned char* base = nullptr;   // device address of g_gemm_static_scratch on this device
+  int sm_count = 0;
+};
+StaticDev g_static_dev[64];
+std::mutex g_static_mutex;
+
+// One-time set-up per device, with that device current.  In host code the array's name is
+// only a handle for the runtime; the address kernels can use comes from cudaGetSymbolAddress.
+int static_scratch_setup(int device, StaticDev** out) {
+  if (device < 0 || device >= 64) DTAS_FAIL(DTAS_EINVAL, "gemm (static scratch): device ordinal %d out of range", device);
+  StaticDev* d = &g_static_dev[device];
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (!d->ready) {
+    int major = 0, sms = 0;
+    DTAS_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+    if (major != 10)
+      DTAS_FAIL(DTAS_EUNSUPPORTED, "device %d is not sm_100; this library only carries sm_100a code", device);
+    DTAS_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    void* ptr = nullptr;
+    DTAS_CUDA(cudaGetSymbolAddress(&ptr, g_gemm_static_scratch));
+    if (ptr == nullptr) DTAS_FAIL(DTAS_ECUDA, "gemm (static scratch): cudaGetSymbolAddress returned a null address");
+    d->base = static_cast<unsigned char*>(ptr);
+    d->sm_count = sms;
+    d->ready = true;
+  }
+  *out = d;
+  return DTAS_OK;
+}
+
+}  // namespace
 }  // namespace dtas
+
+extern "C" int dtas_gemm_nt_static_scratch(const void* x, const void* w, const void* bias, void* y, int64_t m,
+                                           int64_t n, int64_t k, int64_t ldy, int split_k, int dtype,
+                                           int device, void* stream, void* status_word) {
+  using namespace dtas;
+  if (x == nullptr || w == nullptr || y == nullptr) DTAS_FAIL(DTAS_EINVAL, "gemm (static scratch): NULL operand");
+  if (m <= 0) DTAS_FAIL(DTAS_EINVAL, "gemm (static scratch): dynamic dim m must be > 0, got %lld", (long long)m);
+  if (n <= 0 || k <= 0) DTAS_FAIL(DTAS_EINVAL, "gemm (static scratch): n and k must be > 0");
+  if (ldy < n) DTAS_FAIL(DTAS_EINVAL, "gemm (static scratch): ldy (%lld) must be >= n (%lld)", (long long)ldy, (long long)n);
+  if (dtype != DTAS_F16) DTAS_FAIL(DTAS_EUNSUPPORTED, "gemm (static scratch): only fp16 is implemented");
+  if (split_k < 0 || split_k > 64) DTAS_FAIL(DTAS_EINVAL, "gemm (static scratch): split_k must be in [0, 64]");
+  if (m > 0x3fffffffLL || n > 0x3fffffffLL || k > 0x3fffffffLL) DTAS_FAIL(DTAS_EINVAL, "gemm (static scratch): dimension too large");
+  if (!gemm_tma_ok(x, w, k))
+    DTAS_FAIL(DTAS_EALIGN, "gemm (static scratch): x and w must be 16-byte aligned and k a multiple of 8");
+
+  // Tile width from the usual planner; the split factor from the caller, or the planner's.
+  GemmPlan p = plan_gemm(m, n, k, 148, true);
+  const int num_kb = (int)((k + BK - 1) / BK);
+  int splits = split_k > 0 ? (split_k > num_kb ? num_kb : split_k) : p.splits;
+  const int kb_per = (num_kb + splits - 1) / splits;
+  splits = (num_kb + kb_per - 1) / kb_per;
+  const int64_t m_tiles = (m + BM - 1) / BM, n_tiles = (n + p.bn - 1) / p.bn;
+  if (splits > 1) {
+    const int64_t need = (int64_t)splits * m * n * 4;
+    if (need > (int64_t)kStaticPartialBytes)
+      DTAS_FAIL(DTAS_EINVAL,
+                "gemm (static scratch): split_k=%d at m=%lld n=%lld needs %lld bytes of partial sums; the built-in "
+                "scratch holds %lld (use dtas_gemm_nt, or a smaller split)",
+                splits, (long long)m, (long long)n, (long long)need, (long long)kStaticPartialBytes);
+    if (m_tiles * n_tiles > kStaticTileCounters)
+      DTAS_FAIL(DTAS_EINVAL, "gemm (static scratch): %lld output tiles; the built-in scratch has %d counters",
+                (long long)(m_tiles * n_tiles), kStaticTileCounters);
+  }
+
+  DeviceGuard guard;
+  int rc = guard.enter(device);
+  if (rc != DTAS_OK) return rc;
+  StaticDev* sd = nullptr;
+  if ((rc = static_scratch_setup(device, &sd)) != DTAS_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left: counters and the status word must start at zero.
+  DTAS_CUDA(cudaMemsetAsync(sd->base + kStaticPartialBytes, 0, kStaticTailBytes, st));
+
+  CUtensorMap tx, tw;
+  if ((rc = make_tmap(&tx, x, m, k, BM)) != DTAS_OK) return rc;
+  if ((rc = make_tmap(&tw, w, n, k, p.bn)) != DTAS_OK) return rc;
+  GemmArgs a;
+  a.y = (__half*)y;
+  a.bias = (const __half*)bias;
+  a.ws = reinterpret_cast<float*>(sd->base);
+  a.counters = reinterpret_cast<int*>(sd->base + kStaticPartialBytes);
+  a.status = status_word != nullptr ? static_cast<int*>(status_word)
+                                    : reinterpret_cast<int*>(sd->base + kStaticPartialBytes + kStaticCounterBytes);
+  a.ldy = ldy;
+  a.m = (int)m;
+  a.n = (int)n;
+  a.k = (int)k;
+  a.m_tiles = (int)m_tiles;
+  a.n_tiles = (int)n_tiles;
+  a.splits = splits;
+  a.kb_per_split = kb_per;
+  a.num_kb = num_kb;
+  a.vec_store = (aligned16(y) && (ldy % 8 == 0)) ? 1 : 0;
+  switch (p.bn) {
+    case 256: return launch_tc<256>(tx, tw, a, sd->sm_count, st);
+    case 128: return launch_tc<128>(tx, tw, a, sd->sm_count, st);
+    default: return launch_tc<64>(tx, tw, a, sd->sm_count, st);
+  }
+}

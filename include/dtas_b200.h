@@ -96,6 +96,28 @@ int dtas_gemm_nt(const void* x, const void* w, const void* bias, void* y,
                  int64_t m, int64_t n, int64_t k, int64_t ldy,
                  int dtype, int device, void* stream);
 
+/* ---- GEMM without any allocation ------------------------------------------
+ * No counterpart in the reference.  Same operation and operands as dtas_gemm_nt, for callers
+ * that must not create device memory when they call: runtimes that gave the whole device to
+ * their own pool at start-up (a later cudaMalloc fails or eats into what the pool left), and
+ * processes under a fixed memory budget that is checked when the library is loaded, not while
+ * it runs.  dtas_gemm_nt keeps its split-K partial sums in a
+ * workspace it cudaMallocs on first use; this entry point keeps them in an array that is part
+ * of the library image (8 MiB of fp32 partials + 1024 tile counters per GPU that loads the
+ * library, held until the process exits) and calls no allocating routine at all.
+ *   split_k     : K slices per output tile; 0 lets the planner choose.  The call is rejected with
+ *                 DTAS_EINVAL when split_k * m * n * 4 bytes exceed 8 MiB or the output has more
+ *                 than 1024 tiles; with one slice no scratch is used and any size is accepted.
+ *                 x and w must be 16-byte aligned and k a multiple of 8 (DTAS_EALIGN otherwise).
+ *   status_word : optional device int32 that receives a non-zero code if a bounded wait inside
+ *                 the kernel gives up; NULL keeps the code in the library's own scratch.
+ * The first call on a device looks up the array's device address; make that call before any
+ * stream capture.  Every call on a device uses the same array: the call clears the counters it
+ * needs on the given stream, and two calls that overlap on the GPU (different streams) race.   */
+int dtas_gemm_nt_static_scratch(const void* x, const void* w, const void* bias, void* y,
+                                int64_t m, int64_t n, int64_t k, int64_t ldy, int split_k,
+                                int dtype, int device, void* stream, void* status_word);
+
 /* ---- dispatch introspection ---------------------------------------------
  * dtas_bucket_of: index of the m-bucket the op dispatches on, the counterpart of
  * the generated `index = (n/256) > L ? L : n/256` statement
