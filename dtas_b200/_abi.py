@@ -46,6 +46,9 @@ PROTOTYPES = {
     "dtas_bucket_count": (_i, [ctypes.c_char_p]),
     "dtas_variant_of": (_i, [ctypes.c_char_p, _i64, _i64, _i64, _i, ctypes.c_char_p, _i]),
     "dtas_gemm_set_override": (_i, [_i, _i]),
+    "dtas_ew_set_override": (_i, [_i, _i, _i]),
+    "dtas_row_set_override": (_i, [_i]),
+    "dtas_gemv_set_override": (_i, [_i, _i]),
     "dtas_last_error": (ctypes.c_char_p, []),
     "dtas_launch_count": (_i64, []),
     "dtas_poll_status": (_i, [_i]),

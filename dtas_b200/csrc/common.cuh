@@ -102,15 +102,18 @@ int launch_add(const void* a, const void* b, void* out, int64_t n, int dt, const
 int launch_copy(const void* a, void* out, int64_t nbytes, const DeviceCtx* ctx, cudaStream_t st,
                 int bucket);
 const char* ew_variant_name(const char* op, int64_t m, int64_t n_cols, const DeviceCtx* ctx);
+void ew_set_override(int unroll, int ctas_per_sm, int hints);
 
 enum RowOp { ROW_RMSNORM = 0, ROW_SOFTMAX = 1, ROW_LAYERNORM = 2 };
 int launch_row_op(RowOp op, const void* x, const void* p0, const void* p1, void* y, int64_t m,
                   int64_t n_cols, float eps, int in_dtype, const DeviceCtx* ctx, cudaStream_t st);
 void row_variant_name(RowOp op, int64_t m, int64_t n_cols, char* buf, int len);
+void row_set_override(int tpr);
 
 int launch_gemv(const void* x, const void* w, const void* bias, void* y, int64_t n, int64_t k,
                 const DeviceCtx* ctx, cudaStream_t st);
 void gemv_variant_name(int64_t n, int64_t k, const DeviceCtx* ctx, char* buf, int len);
+void gemv_set_override(int wpr, int unroll);
 
 int launch_gemm(const void* x, const void* w, const void* bias, void* y, int64_t m, int64_t n,
                 int64_t k, int64_t ldy, DeviceCtx* ctx, cudaStream_t st);

@@ -223,6 +223,28 @@ int dtas_gemm_set_override(int bn, int split_k) {
   return DTAS_OK;
 }
 
+int dtas_ew_set_override(int unroll, int ctas_per_sm, int stream_hints) {
+  if (!(unroll == 0 || unroll == 1 || unroll == 2 || unroll == 4 || unroll == 8))
+    DTAS_FAIL(DTAS_EINVAL, "elementwise override: unroll must be 0, 1, 2, 4 or 8");
+  ew_set_override(unroll, ctas_per_sm, stream_hints);
+  return DTAS_OK;
+}
+
+int dtas_row_set_override(int threads_per_row) {
+  if (threads_per_row != 0 && (threads_per_row < 32 || threads_per_row > 1024 || (threads_per_row & (threads_per_row - 1))))
+    DTAS_FAIL(DTAS_EINVAL, "row override: threads per row must be 0 or a power of two in [32, 1024]");
+  row_set_override(threads_per_row);
+  return DTAS_OK;
+}
+
+int dtas_gemv_set_override(int warps_per_row, int unroll) {
+  if (!(warps_per_row == 0 || warps_per_row == 1 || warps_per_row == 2 || warps_per_row == 4 || warps_per_row == 8))
+    DTAS_FAIL(DTAS_EINVAL, "gemv override: warps per row must be 0, 1, 2, 4 or 8");
+  if (!(unroll == 0 || unroll == 4 || unroll == 8)) DTAS_FAIL(DTAS_EINVAL, "gemv override: unroll must be 0, 4 or 8");
+  gemv_set_override(warps_per_row, unroll);
+  return DTAS_OK;
+}
+
 const char* dtas_last_error(void) { return tl_error; }
 
 int64_t dtas_launch_count(void) { return g_launches.load(); }

@@ -6,8 +6,8 @@
 // (python/dtas/policy/elementwise_config_emiter.py:9-33).  Here that is one
 // grid-stride kernel template: every thread moves UNROLL 16-byte vectors per
 // iteration (all loads issued before the first store, so a thread keeps
-// UNROLL x 16..32 bytes in flight), the grid is capped at a per-bucket multiple of
-// the SM count, and the ragged tail and unaligned buffers take a scalar path.
+// UNROLL x 16..32 bytes in flight); by default the grid covers the data once (one tile
+// per CTA), and the ragged tail and unaligned buffers take a scalar path.
 //
 // Algorithmic HBM bytes per element: cast f32->f16 6, cast f16->f32 6, add 3*size,
 // copy 2*size.  The kernels are pure streams: their roofline is HBM bandwidth.
@@ -18,10 +18,17 @@ namespace {
 
 constexpr int kThreads = 256;
 
-__device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
-__device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p); }
-__device__ __forceinline__ void st_stream(uint4* p, uint4 v) { __stcs(p, v); }
-__device__ __forceinline__ void st_stream(float4* p, float4 v) { __stcs(p, v); }
+// H = true: evict-first streaming accesses (ld.global.cs / st.global.cs); H = false: plain.
+template <bool H, typename V>
+__device__ __forceinline__ V ld_stream(const V* p) {
+  if constexpr (H) return __ldcs(p);
+  else return *p;
+}
+template <bool H, typename V>
+__device__ __forceinline__ void st_stream(V* p, V v) {
+  if constexpr (H) __stcs(p, v);
+  else *p = v;
+}
 
 __device__ __forceinline__ uint32_t pack_half2_rn(float a, float b) {
   __half2 h = __floats2half2_rn(a, b);  // round-to-nearest-even, like a C cast
@@ -38,75 +45,87 @@ __device__ __forceinline__ uint32_t hadd2_bits(uint32_t a, uint32_t b) {
 // Each Op describes one vector of work: Reg = registers held between load and store,
 // kVec = elements per vector, scalar() = the one-element fallback.
 struct CastF32F16 {
+  static constexpr int kLoads = 2;   // 16-byte loads per vector
   static constexpr int kVec = 8;
   const float* a;
   __half* o;
   struct Reg { float4 lo, hi; };
+  template <bool H>
   __device__ __forceinline__ void load(Reg& r, int64_t v) const {
     const float4* p = reinterpret_cast<const float4*>(a) + 2 * v;
-    r.lo = ld_stream(p);
-    r.hi = ld_stream(p + 1);
+    r.lo = ld_stream<H>(p);
+    r.hi = ld_stream<H>(p + 1);
   }
+  template <bool H>
   __device__ __forceinline__ void store(const Reg& r, int64_t v) const {
     uint4 w;
     w.x = pack_half2_rn(r.lo.x, r.lo.y);
     w.y = pack_half2_rn(r.lo.z, r.lo.w);
     w.z = pack_half2_rn(r.hi.x, r.hi.y);
     w.w = pack_half2_rn(r.hi.z, r.hi.w);
-    st_stream(reinterpret_cast<uint4*>(o) + v, w);
+    st_stream<H>(reinterpret_cast<uint4*>(o) + v, w);
   }
   __device__ __forceinline__ void scalar(int64_t i) const { o[i] = __float2half_rn(a[i]); }
 };
 
 struct CastF16F32 {
+  static constexpr int kLoads = 1;   // 16-byte loads per vector
   static constexpr int kVec = 8;
   const __half* a;
   float* o;
   struct Reg { uint4 v; };
+  template <bool H>
   __device__ __forceinline__ void load(Reg& r, int64_t v) const {
-    r.v = ld_stream(reinterpret_cast<const uint4*>(a) + v);
+    r.v = ld_stream<H>(reinterpret_cast<const uint4*>(a) + v);
   }
+  template <bool H>
   __device__ __forceinline__ void store(const Reg& r, int64_t v) const {
     float2 f0 = unpack_half2(r.v.x), f1 = unpack_half2(r.v.y);
     float2 f2 = unpack_half2(r.v.z), f3 = unpack_half2(r.v.w);
     float4* p = reinterpret_cast<float4*>(o) + 2 * v;
-    st_stream(p, make_float4(f0.x, f0.y, f1.x, f1.y));
-    st_stream(p + 1, make_float4(f2.x, f2.y, f3.x, f3.y));
+    st_stream<H>(p, make_float4(f0.x, f0.y, f1.x, f1.y));
+    st_stream<H>(p + 1, make_float4(f2.x, f2.y, f3.x, f3.y));
   }
   __device__ __forceinline__ void scalar(int64_t i) const { o[i] = __half2float(a[i]); }
 };
 
 struct AddF16 {
+  static constexpr int kLoads = 2;   // 16-byte loads per vector
   static constexpr int kVec = 8;
   const __half *a, *b;
   __half* o;
   struct Reg { uint4 x, y; };
+  template <bool H>
   __device__ __forceinline__ void load(Reg& r, int64_t v) const {
-    r.x = ld_stream(reinterpret_cast<const uint4*>(a) + v);
-    r.y = ld_stream(reinterpret_cast<const uint4*>(b) + v);
+    r.x = ld_stream<H>(reinterpret_cast<const uint4*>(a) + v);
+    r.y = ld_stream<H>(reinterpret_cast<const uint4*>(b) + v);
   }
+  template <bool H>
   __device__ __forceinline__ void store(const Reg& r, int64_t v) const {
     uint4 w;
     w.x = hadd2_bits(r.x.x, r.y.x);
     w.y = hadd2_bits(r.x.y, r.y.y);
     w.z = hadd2_bits(r.x.z, r.y.z);
     w.w = hadd2_bits(r.x.w, r.y.w);
-    st_stream(reinterpret_cast<uint4*>(o) + v, w);
+    st_stream<H>(reinterpret_cast<uint4*>(o) + v, w);
   }
   __device__ __forceinline__ void scalar(int64_t i) const { o[i] = __hadd(a[i], b[i]); }
 };
 
 struct AddF32 {
+  static constexpr int kLoads = 2;   // 16-byte loads per vector
   static constexpr int kVec = 4;
   const float *a, *b;
   float* o;
   struct Reg { float4 x, y; };
+  template <bool H>
   __device__ __forceinline__ void load(Reg& r, int64_t v) const {
-    r.x = ld_stream(reinterpret_cast<const float4*>(a) + v);
-    r.y = ld_stream(reinterpret_cast<const float4*>(b) + v);
+    r.x = ld_stream<H>(reinterpret_cast<const float4*>(a) + v);
+    r.y = ld_stream<H>(reinterpret_cast<const float4*>(b) + v);
   }
+  template <bool H>
   __device__ __forceinline__ void store(const Reg& r, int64_t v) const {
-    st_stream(reinterpret_cast<float4*>(o) + v,
+    st_stream<H>(reinterpret_cast<float4*>(o) + v,
               make_float4(__fadd_rn(r.x.x, r.y.x), __fadd_rn(r.x.y, r.y.y),
                           __fadd_rn(r.x.z, r.y.z), __fadd_rn(r.x.w, r.y.w)));
   }
@@ -114,21 +133,24 @@ struct AddF32 {
 };
 
 struct AddI8 {  // two's-complement wrap-around per byte, like the int8 PrimFunc
+  static constexpr int kLoads = 2;   // 16-byte loads per vector
   static constexpr int kVec = 16;
   const int8_t *a, *b;
   int8_t* o;
   struct Reg { uint4 x, y; };
+  template <bool H>
   __device__ __forceinline__ void load(Reg& r, int64_t v) const {
-    r.x = ld_stream(reinterpret_cast<const uint4*>(a) + v);
-    r.y = ld_stream(reinterpret_cast<const uint4*>(b) + v);
+    r.x = ld_stream<H>(reinterpret_cast<const uint4*>(a) + v);
+    r.y = ld_stream<H>(reinterpret_cast<const uint4*>(b) + v);
   }
+  template <bool H>
   __device__ __forceinline__ void store(const Reg& r, int64_t v) const {
     uint4 w;
     w.x = __vadd4(r.x.x, r.y.x);
     w.y = __vadd4(r.x.y, r.y.y);
     w.z = __vadd4(r.x.z, r.y.z);
     w.w = __vadd4(r.x.w, r.y.w);
-    st_stream(reinterpret_cast<uint4*>(o) + v, w);
+    st_stream<H>(reinterpret_cast<uint4*>(o) + v, w);
   }
   __device__ __forceinline__ void scalar(int64_t i) const {
     o[i] = (int8_t)((uint8_t)a[i] + (uint8_t)b[i]);
@@ -136,22 +158,25 @@ struct AddI8 {  // two's-complement wrap-around per byte, like the int8 PrimFunc
 };
 
 struct CopyBytes {
+  static constexpr int kLoads = 1;   // 16-byte loads per vector
   static constexpr int kVec = 16;
   const uint8_t* a;
   uint8_t* o;
   struct Reg { uint4 v; };
+  template <bool H>
   __device__ __forceinline__ void load(Reg& r, int64_t v) const {
-    r.v = ld_stream(reinterpret_cast<const uint4*>(a) + v);
+    r.v = ld_stream<H>(reinterpret_cast<const uint4*>(a) + v);
   }
+  template <bool H>
   __device__ __forceinline__ void store(const Reg& r, int64_t v) const {
-    st_stream(reinterpret_cast<uint4*>(o) + v, r.v);
+    st_stream<H>(reinterpret_cast<uint4*>(o) + v, r.v);
   }
   __device__ __forceinline__ void scalar(int64_t i) const { o[i] = a[i]; }
 };
 
 // Vector path: n_vec full vectors, then (n_elem - n_vec*kVec) tail elements handled
 // by the first threads of block 0.
-template <typename Op, int UNROLL>
+template <typename Op, int UNROLL, bool HINT>
 __global__ void __launch_bounds__(kThreads) ew_vec_kernel(const Op op, int64_t n_vec,
                                                           int64_t n_elem) {
   constexpr int64_t kTile = (int64_t)kThreads * UNROLL;
@@ -161,12 +186,12 @@ __global__ void __launch_bounds__(kThreads) ew_vec_kernel(const Op op, int64_t n
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       int64_t v = base + (int64_t)u * kThreads + threadIdx.x;
-      if (v < n_vec) op.load(r[u], v);
+      if (v < n_vec) op.template load<HINT>(r[u], v);
     }
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       int64_t v = base + (int64_t)u * kThreads + threadIdx.x;
-      if (v < n_vec) op.store(r[u], v);
+      if (v < n_vec) op.template store<HINT>(r[u], v);
     }
   }
   if (blockIdx.x == 0) {
@@ -188,13 +213,34 @@ __global__ void __launch_bounds__(kThreads) ew_scalar_kernel(const Op op, int64_
 // few vectors over as many CTAs as possible (latency-bound); large buckets use deeper
 // per-thread unrolling and a grid capped at a multiple of the SM count.
 struct EwCfg {
-  int unroll;
-  int ctas_per_sm;
+  int unroll;        // 1, 2, 4 or 8 vectors in flight per thread
+  int ctas_per_sm;   // grid cap as a multiple of the SM count; <= 0: one tile per CTA, no cap
+  bool hints;        // streaming cache hints
 };
-inline EwCfg ew_cfg(int bucket) {
-  if (bucket <= 0) return {1, 8};
-  if (bucket <= 3) return {2, 8};
-  return {4, 8};
+std::atomic<int> g_ew_unroll{0}, g_ew_ctas{0}, g_ew_hints{-1};
+
+// Defaults, from a sweep on B200 (unroll 1/2/4/8 x grid cap 4/8/16 CTAs per SM or none x
+// hints on/off, at m = 64 ... 8192): one tile per CTA with no cap on the grid beats every
+// capped, looping grid (copy [8192,11008]: 6.69 TB/s uncapped vs 5.8-6.4 capped), two
+// 16-byte loads in flight per thread are enough (copy: two vectors; add and cast already
+// load two per vector), streaming hints are worth 0-2 %.  The grid-stride loop stays: it is
+// what makes a capped grid (override, or a grid beyond 2^31 tiles) correct.
+inline EwCfg ew_cfg(int bucket, int loads_per_vec) {
+  EwCfg c{loads_per_vec >= 2 ? 1 : 2, -1, true};
+  if (bucket <= 0 && loads_per_vec < 2) c.unroll = 1;   // a few KB: spread over as many CTAs as possible
+  const int u = g_ew_unroll.load(), g = g_ew_ctas.load(), h = g_ew_hints.load();
+  if (u == 1 || u == 2 || u == 4 || u == 8) c.unroll = u;
+  if (g != 0) c.ctas_per_sm = g;
+  if (h >= 0) c.hints = h != 0;
+  return c;
+}
+
+template <typename Op, int UNROLL>
+void launch_vec(const Op& op, int64_t n_vec, int64_t n_elem, unsigned blocks, bool hints, cudaStream_t st) {
+  if (hints)
+    ew_vec_kernel<Op, UNROLL, true><<<blocks, kThreads, 0, st>>>(op, n_vec, n_elem);
+  else
+    ew_vec_kernel<Op, UNROLL, false><<<blocks, kThreads, 0, st>>>(op, n_vec, n_elem);
 }
 
 template <typename Op>
@@ -207,16 +253,20 @@ int launch_ew(const Op& op, int64_t n_elem, bool aligned, const DeviceCtx* ctx, 
     return after_launch(name);
   }
   const int64_t n_vec = n_elem / Op::kVec;
-  const EwCfg cfg = ew_cfg(bucket);
+  const EwCfg cfg = ew_cfg(bucket, Op::kLoads);
   const int64_t tile = (int64_t)kThreads * cfg.unroll;
   int64_t blocks = (n_vec + tile - 1) / tile;
-  const int64_t cap = (int64_t)ctx->sm_count * cfg.ctas_per_sm;
-  if (blocks > cap) blocks = cap;
+  if (cfg.ctas_per_sm > 0) {
+    const int64_t cap = (int64_t)ctx->sm_count * cfg.ctas_per_sm;
+    if (blocks > cap) blocks = cap;
+  }
+  if (blocks > 0x7fffffffLL) blocks = 0x7fffffffLL;
   if (blocks < 1) blocks = 1;
   switch (cfg.unroll) {
-    case 1: ew_vec_kernel<Op, 1><<<(unsigned)blocks, kThreads, 0, st>>>(op, n_vec, n_elem); break;
-    case 2: ew_vec_kernel<Op, 2><<<(unsigned)blocks, kThreads, 0, st>>>(op, n_vec, n_elem); break;
-    default: ew_vec_kernel<Op, 4><<<(unsigned)blocks, kThreads, 0, st>>>(op, n_vec, n_elem); break;
+    case 1: launch_vec<Op, 1>(op, n_vec, n_elem, (unsigned)blocks, cfg.hints, st); break;
+    case 2: launch_vec<Op, 2>(op, n_vec, n_elem, (unsigned)blocks, cfg.hints, st); break;
+    case 4: launch_vec<Op, 4>(op, n_vec, n_elem, (unsigned)blocks, cfg.hints, st); break;
+    default: launch_vec<Op, 8>(op, n_vec, n_elem, (unsigned)blocks, cfg.hints, st); break;
   }
   return after_launch(name);
 }
@@ -260,12 +310,19 @@ int launch_copy(const void* a, void* out, int64_t nbytes, const DeviceCtx* ctx, 
 }
 
 const char* ew_variant_name(const char* op, int64_t m, int64_t, const DeviceCtx*) {
-  (void)op;
-  switch (ew_cfg(bucket_of(m)).unroll) {
+  const int loads = (op != nullptr && strcmp(op, "copy") == 0) ? 1 : 2;
+  switch (ew_cfg(bucket_of(m), loads).unroll) {
     case 1: return "ew_vec16_unroll1";
     case 2: return "ew_vec16_unroll2";
-    default: return "ew_vec16_unroll4";
+    case 4: return "ew_vec16_unroll4";
+    default: return "ew_vec16_unroll8";
   }
+}
+
+void ew_set_override(int unroll, int ctas_per_sm, int hints) {
+  g_ew_unroll.store(unroll);
+  g_ew_ctas.store(ctas_per_sm);
+  g_ew_hints.store(hints);
 }
 
 }  // namespace dtas

@@ -9,8 +9,7 @@
 // (1, 2, 4 or 8) of a 256-thread CTA; each lane issues UNROLL independent 16-byte loads
 // of W per step with the matching x chunks read through L1 (x is 8-22 KB and hot in
 // L1/L2), accumulates 8 products per chunk in fp32, and the partials meet through warp
-// shuffles and one shared-memory hop.  WPR grows as N shrinks (column-sharded ranks) so
-// that the grid still covers all SMs several times.
+// shuffles and one shared-memory hop.  WPR is chosen from K alone (pick_wpr).
 // Algorithmic bytes: 2*N*K + 2*K + 2*N.  Bound: HBM bandwidth.
 #include "common.cuh"
 
@@ -113,15 +112,38 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
-// Warps per row: aim for at least 4 CTAs per SM.
+std::atomic<int> g_gemv_wpr{0}, g_gemv_unroll{0};
+
+// Warps per row and loads in flight per lane.  Measured on B200 over the Llama-2-7B shapes
+// and their 8-way column shards: the best point is always "one batch of four 16-byte loads
+// per lane and done" - i.e. as many warps per row as it takes to bring a warp's K-slice
+// down to 128 chunks (4 per lane), up to the 8 warps of a CTA.  Short-lived warps with
+// short dependent chains beat fewer warps that loop (w4/u4 vs w1/u8 at 4096 x 4096:
+// 8.0 us vs 9.6 us; at 32000 x 4096: 43.1 us vs 51.8 us).
 inline int pick_wpr(int64_t n, int64_t k, int sm_count) {
+  (void)n;
+  (void)sm_count;
+  const int forced = g_gemv_wpr.load();
+  if (forced == 1 || forced == 2 || forced == 4 || forced == 8) return forced;
+  const int64_t n_chunks = k >> 3;
   int wpr = 1;
-  while (wpr < 8 && (n * wpr) / kWarps < (int64_t)sm_count * 4 && (k >> 3) / (wpr * 2) >= 64)
-    wpr *= 2;
+  while (wpr < 8 && n_chunks / (wpr * 2) >= 128) wpr *= 2;
   return wpr;
 }
 
+inline int pick_unroll(int wpr) {
+  (void)wpr;
+  const int forced = g_gemv_unroll.load();
+  if (forced == 4 || forced == 8) return forced;
+  return 4;
+}
+
 }  // namespace
+
+void gemv_set_override(int wpr, int unroll) {
+  g_gemv_wpr.store(wpr);
+  g_gemv_unroll.store(unroll);
+}
 
 int launch_gemv(const void* x, const void* w, const void* bias, void* y, int64_t n, int64_t k,
                 const DeviceCtx* ctx, cudaStream_t st) {
@@ -139,13 +161,16 @@ int launch_gemv(const void* x, const void* w, const void* bias, void* y, int64_t
   const int wpr = pick_wpr(n, k, ctx->sm_count);
   const int rows_per_cta = kWarps / wpr;
   const unsigned grid = (unsigned)((n + rows_per_cta - 1) / rows_per_cta);
-  switch (wpr) {
-    case 1: gemv_f16_kernel<1, 8><<<grid, kThreads, 0, st>>>(xp, wp, bp, yp, (int)n, (int)k); break;
-    case 2: gemv_f16_kernel<2, 8><<<grid, kThreads, 0, st>>>(xp, wp, bp, yp, (int)n, (int)k); break;
-    case 4: gemv_f16_kernel<4, 4><<<grid, kThreads, 0, st>>>(xp, wp, bp, yp, (int)n, (int)k); break;
-    default: gemv_f16_kernel<8, 4><<<grid, kThreads, 0, st>>>(xp, wp, bp, yp, (int)n, (int)k); break;
+  const int unroll = pick_unroll(wpr);
+#define DTAS_GEMV_CASE(W, U)                                                                  \
+  if (wpr == W && unroll == U) {                                                              \
+    gemv_f16_kernel<W, U><<<grid, kThreads, 0, st>>>(xp, wp, bp, yp, (int)n, (int)k);         \
+    return after_launch("gemv_f16_kernel");                                                   \
   }
-  return after_launch("gemv_f16_kernel");
+  DTAS_GEMV_CASE(1, 4) DTAS_GEMV_CASE(1, 8) DTAS_GEMV_CASE(2, 4) DTAS_GEMV_CASE(2, 8)
+  DTAS_GEMV_CASE(4, 4) DTAS_GEMV_CASE(4, 8) DTAS_GEMV_CASE(8, 4) DTAS_GEMV_CASE(8, 8)
+#undef DTAS_GEMV_CASE
+  DTAS_FAIL(DTAS_EINVAL, "gemv: no kernel for wpr=%d unroll=%d", wpr, unroll);
 }
 
 void gemv_variant_name(int64_t n, int64_t k, const DeviceCtx* ctx, char* buf, int len) {
@@ -154,7 +179,7 @@ void gemv_variant_name(int64_t n, int64_t k, const DeviceCtx* ctx, char* buf, in
     return;
   }
   const int wpr = pick_wpr(n, k, ctx ? ctx->sm_count : 148);
-  snprintf(buf, len, "gemv_vec16_wpr%d_unroll%d", wpr, wpr <= 2 ? 8 : 4);
+  snprintf(buf, len, "gemv_vec16_wpr%d_unroll%d", wpr, pick_unroll(wpr));
 }
 
 }  // namespace dtas

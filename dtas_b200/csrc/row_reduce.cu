@@ -7,7 +7,7 @@
 //
 // Design: a row is owned by TPR threads (a power of two, 32..1024).  Each thread loads
 // its 16-byte chunks (8 fp16, or 2 x 16 B for fp32 input) with all loads in flight at
-// once, keeps the row in registers as fp32, reduces with warp shuffles (+ one shared
+// once, keeps the row in registers as loaded, reduces with warp shuffles (+ one shared
 // memory hop when TPR > 32) and writes 16-byte fp16 vectors.  HBM sees each element
 // once in and once out: algorithmic bytes 4*n_cols per row for fp16 in/out
 // (+ 2*n_cols once for the RMSNorm weight).  Bound: HBM bandwidth.
@@ -26,19 +26,45 @@ __device__ __forceinline__ uint32_t f2h(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// Loads chunk `c` (8 consecutive elements) of a row as fp32.
-__device__ __forceinline__ void load_chunk(const __half* row, int c, float* v) {
-  uint4 r = __ldcs(reinterpret_cast<const uint4*>(row) + c);
-  float2 a = h2f(r.x), b = h2f(r.y), d = h2f(r.z), e = h2f(r.w);
-  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
-  v[4] = d.x; v[5] = d.y; v[6] = e.x; v[7] = e.y;
-}
-__device__ __forceinline__ void load_chunk(const float* row, int c, float* v) {
-  float4 a = __ldcs(reinterpret_cast<const float4*>(row) + 2 * c);
-  float4 b = __ldcs(reinterpret_cast<const float4*>(row) + 2 * c + 1);
-  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-}
+// A chunk is 8 consecutive elements of a row.  Between the reduction and the epilogue a
+// thread keeps its chunks as loaded (16 bytes for fp16 input, 32 bytes for fp32 input) and
+// unpacks to fp32 at each use: half the registers of holding fp32 for the common fp16 case,
+// which is what lets one warp own a whole 4096-element row with every load in flight.
+template <typename InT>
+struct RawChunk;
+template <>
+struct RawChunk<__half> {
+  uint4 r;
+  __device__ __forceinline__ void load(const __half* row, int c) {
+    r = __ldcs(reinterpret_cast<const uint4*>(row) + c);
+  }
+  __device__ __forceinline__ void unpack(float* v) const {
+    float2 a = h2f(r.x), b = h2f(r.y), d = h2f(r.z), e = h2f(r.w);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    v[4] = d.x; v[5] = d.y; v[6] = e.x; v[7] = e.y;
+  }
+  __device__ __forceinline__ void fill(float f) {
+    const uint32_t h = f2h(f, f);
+    r = make_uint4(h, h, h, h);
+  }
+};
+template <>
+struct RawChunk<float> {
+  float4 a, b;
+  __device__ __forceinline__ void load(const float* row, int c) {
+    a = __ldcs(reinterpret_cast<const float4*>(row) + 2 * c);
+    b = __ldcs(reinterpret_cast<const float4*>(row) + 2 * c + 1);
+  }
+  __device__ __forceinline__ void unpack(float* v) const {
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+  __device__ __forceinline__ void fill(float f) {
+    a = make_float4(f, f, f, f);
+    b = a;
+  }
+};
+
 __device__ __forceinline__ void store_chunk(__half* row, int c, const float* v) {
   uint4 w;
   w.x = f2h(v[0], v[1]);
@@ -46,6 +72,13 @@ __device__ __forceinline__ void store_chunk(__half* row, int c, const float* v) 
   w.z = f2h(v[4], v[5]);
   w.w = f2h(v[6], v[7]);
   __stcs(reinterpret_cast<uint4*>(row) + c, w);
+}
+
+// exp(x) for x <= 0 as 2^(x * log2 e) on the special-function unit.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 struct SumOp {
@@ -76,6 +109,9 @@ __device__ __forceinline__ float group_allreduce(float v, F f, float* scratch) {
   return v;
 }
 
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kNegHuge = -3.4028234663852886e+38f;
+
 // One row per TPR threads, up to MAXCH chunks per thread held in registers.
 template <int OP, typename InT, int TPR, int MAXCH>
 __global__ void __launch_bounds__(TPR > kCtaThreads ? TPR : kCtaThreads)
@@ -92,25 +128,27 @@ __global__ void __launch_bounds__(TPR > kCtaThreads ? TPR : kCtaThreads)
   const bool live = row < m;
   const int n_chunks = n_cols >> 3;
   const InT* xr = x + (live ? row : 0) * (int64_t)n_cols;
+  __half* yr = y + (live ? row : 0) * (int64_t)n_cols;
 
-  float v[MAXCH][8];
+  RawChunk<InT> raw[MAXCH];
 #pragma unroll
   for (int c = 0; c < MAXCH; ++c) {
     const int ch = c * TPR + t;
-    if (live && ch < n_chunks) {
-      load_chunk(xr, ch, v[c]);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) v[c][i] = (OP == ROW_SOFTMAX) ? -3.4028234663852886e+38f : 0.f;
-    }
+    if (live && ch < n_chunks)
+      raw[c].load(xr, ch);
+    else
+      raw[c].fill(OP == ROW_SOFTMAX ? -65504.f : 0.f);   // neutral for max (fp16 lowest) / sums
   }
 
   if constexpr (OP == ROW_RMSNORM) {
     float ss = 0.f;
 #pragma unroll
-    for (int c = 0; c < MAXCH; ++c)
+    for (int c = 0; c < MAXCH; ++c) {
+      float v[8];
+      raw[c].unpack(v);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) ss = fmaf(v[c][i], v[c][i], ss);
+      for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+    }
     ss = group_allreduce<TPR>(ss, SumOp(), scratch_a);
     const float r = 1.0f / sqrtf(ss * (1.0f / (float)n_cols) + eps);
     const __half* w = static_cast<const __half*>(p0);
@@ -118,32 +156,44 @@ __global__ void __launch_bounds__(TPR > kCtaThreads ? TPR : kCtaThreads)
     for (int c = 0; c < MAXCH; ++c) {
       const int ch = c * TPR + t;
       if (live && ch < n_chunks) {
-        float wv[8];
-        uint4 wr = __ldg(reinterpret_cast<const uint4*>(w) + ch);
-        float2 a = h2f(wr.x), b = h2f(wr.y), d = h2f(wr.z), e = h2f(wr.w);
-        wv[0] = a.x; wv[1] = a.y; wv[2] = b.x; wv[3] = b.y;
-        wv[4] = d.x; wv[5] = d.y; wv[6] = e.x; wv[7] = e.y;
-        float o[8];
+        float v[8], wv[8], o[8];
+        raw[c].unpack(v);
+        RawChunk<__half> wr;
+        wr.r = __ldg(reinterpret_cast<const uint4*>(w) + ch);
+        wr.unpack(wv);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = __fmul_rn(__fmul_rn(v[c][i], r), wv[i]);
-        store_chunk(y + row * (int64_t)n_cols, ch, o);
+        for (int i = 0; i < 8; ++i) o[i] = __fmul_rn(__fmul_rn(v[i], r), wv[i]);
+        store_chunk(yr, ch, o);
       }
     }
   } else if constexpr (OP == ROW_SOFTMAX) {
-    float mx = -3.4028234663852886e+38f;
+    float mx = kNegHuge;
 #pragma unroll
-    for (int c = 0; c < MAXCH; ++c)
+    for (int c = 0; c < MAXCH; ++c) {
+      const bool on = (c * TPR + t) < n_chunks;
+      float v[8];
+      raw[c].unpack(v);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) mx = fmaxf(mx, v[c][i]);
+      for (int i = 0; i < 8; ++i) mx = on ? fmaxf(mx, v[i]) : mx;
+    }
     mx = group_allreduce<TPR>(mx, MaxOp(), scratch_a);
+    // exp(x - mx) = 2^((x - mx) * log2e); the subtraction comes first so that rows with
+    // large |x| keep full precision in the exponent.  With at most 4 chunks per thread the
+    // 32 exponentials are parked in registers between the sum and the output; with more
+    // they are evaluated twice (a second MUFU pass costs less than the registers).
+    constexpr bool kKeep = MAXCH <= 4;
+    float e[kKeep ? MAXCH : 1][8];
     float sum = 0.f;
 #pragma unroll
     for (int c = 0; c < MAXCH; ++c) {
       const bool on = (c * TPR + t) < n_chunks;
+      float v[8];
+      raw[c].unpack(v);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        v[c][i] = on ? __expf(v[c][i] - mx) : 0.f;
-        sum += v[c][i];
+        const float ev = on ? fast_exp2((v[i] - mx) * kLog2e) : 0.f;
+        if constexpr (kKeep) e[c][i] = ev;
+        sum += ev;
       }
     }
     sum = group_allreduce<TPR>(sum, SumOp(), scratch_b);
@@ -153,20 +203,30 @@ __global__ void __launch_bounds__(TPR > kCtaThreads ? TPR : kCtaThreads)
       const int ch = c * TPR + t;
       if (live && ch < n_chunks) {
         float o[8];
+        if constexpr (kKeep) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = v[c][i] * inv;
-        store_chunk(y + row * (int64_t)n_cols, ch, o);
+          for (int i = 0; i < 8; ++i) o[i] = e[c][i] * inv;
+        } else {
+          float v[8];
+          raw[c].unpack(v);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = fast_exp2((v[i] - mx) * kLog2e) * inv;
+        }
+        store_chunk(yr, ch, o);
       }
     }
   } else {  // ROW_LAYERNORM
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int c = 0; c < MAXCH; ++c)
+    for (int c = 0; c < MAXCH; ++c) {
+      float v[8];
+      raw[c].unpack(v);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        s1 += v[c][i];
-        s2 = fmaf(v[c][i], v[c][i], s2);
+        s1 += v[i];
+        s2 = fmaf(v[i], v[i], s2);
       }
+    }
     s1 = group_allreduce<TPR>(s1, SumOp(), scratch_a);
     s2 = group_allreduce<TPR>(s2, SumOp(), scratch_b);
     const float inv_n = 1.0f / (float)n_cols;
@@ -178,17 +238,19 @@ __global__ void __launch_bounds__(TPR > kCtaThreads ? TPR : kCtaThreads)
     for (int c = 0; c < MAXCH; ++c) {
       const int ch = c * TPR + t;
       if (live && ch < n_chunks) {
-        float4 g0 = __ldg(reinterpret_cast<const float4*>(g) + 2 * ch);
-        float4 g1 = __ldg(reinterpret_cast<const float4*>(g) + 2 * ch + 1);
-        float4 b0 = __ldg(reinterpret_cast<const float4*>(be) + 2 * ch);
-        float4 b1 = __ldg(reinterpret_cast<const float4*>(be) + 2 * ch + 1);
-        const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-        const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-        float o[8];
+        float v[8], gv[8], bv[8], o[8];
+        raw[c].unpack(v);
+        RawChunk<float> gr, br;
+        gr.a = __ldg(reinterpret_cast<const float4*>(g) + 2 * ch);
+        gr.b = __ldg(reinterpret_cast<const float4*>(g) + 2 * ch + 1);
+        br.a = __ldg(reinterpret_cast<const float4*>(be) + 2 * ch);
+        br.b = __ldg(reinterpret_cast<const float4*>(be) + 2 * ch + 1);
+        gr.unpack(gv);
+        br.unpack(bv);
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-          o[i] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v[c][i], mean), r), gv[i]), bv[i]);
-        store_chunk(y + row * (int64_t)n_cols, ch, o);
+          o[i] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v[i], mean), r), gv[i]), bv[i]);
+        store_chunk(yr, ch, o);
       }
     }
   }
@@ -265,14 +327,18 @@ __global__ void __launch_bounds__(kCtaThreads)
 }
 
 // ---- dispatch ------------------------------------------------------------------
-// Threads per row: few rows -> wide groups (short dependent chains, low latency);
-// many rows -> narrower groups (more rows per CTA, fewer barriers).  Always at least
-// enough threads that a row fits in 8 chunks per thread, never more threads than chunks.
+// Threads per row (TPR) and chunks per thread (MAXCH), per m-bucket.  From a sweep on B200
+// at 4096 columns (TPR 32..512, m = 33..8192): 256 threads per row up to m = 1024 (short
+// dependent chains, the latency-bound regime: 2.0 us at m = 33 vs 6.0 us with one warp per
+// row), 128 beyond (5.5 TB/s RMSNorm at m = 4096, 6.2 TB/s at m = 8192; one warp per row
+// reaches 3.4 TB/s, 512 threads 3.5 TB/s).  TPR is raised when a row would not fit the
+// register budget (16 chunks of fp16, 8 of fp32 per thread).
 struct RowCfg {
   int tpr;
-  int maxch;     // 2 or 8
+  int maxch;     // 2, 4, 8 or 16
   bool generic;
 };
+std::atomic<int> g_row_tpr{0};
 
 inline int pow2_ceil(int v) {
   int p = 1;
@@ -280,7 +346,7 @@ inline int pow2_ceil(int v) {
   return p;
 }
 
-inline RowCfg row_cfg(int64_t m, int64_t n_cols, bool vec_ok) {
+inline RowCfg row_cfg(int64_t m, int64_t n_cols, bool vec_ok, int in_dtype) {
   RowCfg c{0, 0, false};
   if (!vec_ok || n_cols > 65536) {
     c.generic = true;
@@ -288,17 +354,27 @@ inline RowCfg row_cfg(int64_t m, int64_t n_cols, bool vec_ok) {
   }
   const int n_chunks = (int)(n_cols >> 3);
   const int bucket = bucket_of(m);
-  int want = bucket == 0 ? 512 : (bucket <= 3 ? 256 : 128);
-  int min_tpr = pow2_ceil((n_chunks + 7) / 8);
-  if (min_tpr < 32) min_tpr = 32;
+  // chunks a thread may hold without spilling: 16 of fp16 / 8 of fp32, half that in a
+  // 1024-thread CTA (64 registers per thread)
+  auto cap_for = [&](int tpr) {
+    const int base = in_dtype == DTAS_F16 ? 16 : 8;
+    return tpr >= 1024 ? base / 2 : base;
+  };
   int max_tpr = pow2_ceil(n_chunks);
   if (max_tpr < 32) max_tpr = 32;
   if (max_tpr > 1024) max_tpr = 1024;
-  int tpr = want;
-  if (tpr < min_tpr) tpr = min_tpr;
+  int tpr = bucket <= 3 ? 256 : 128;
+  const int forced = g_row_tpr.load();
+  if (forced >= 32 && forced <= 1024 && (forced & (forced - 1)) == 0) tpr = forced;
   if (tpr > max_tpr) tpr = max_tpr;
+  while (tpr <= 1024 && (n_chunks + tpr - 1) / tpr > cap_for(tpr)) tpr *= 2;
+  if (tpr > 1024) {
+    c.generic = true;
+    return c;
+  }
   c.tpr = tpr;
-  c.maxch = ((n_chunks + tpr - 1) / tpr) <= 2 ? 2 : 8;
+  const int need = (n_chunks + tpr - 1) / tpr;
+  c.maxch = need <= 2 ? 2 : (need <= 4 ? 4 : (need <= 8 ? 8 : 16));
   return c;
 }
 
@@ -335,8 +411,16 @@ int launch_typed(const RowCfg& c, const InT* x, const void* p0, const void* p1, 
     row_generic_kernel<OP, InT><<<(unsigned)grid, kCtaThreads, 0, st>>>(x, p0, p1, y, m, n_cols, eps);
     return after_launch("row_generic_kernel");
   }
-  if (c.maxch == 2) return launch_tpr<OP, InT, 2>(c.tpr, x, p0, p1, y, m, (int)n_cols, eps, st);
-  return launch_tpr<OP, InT, 8>(c.tpr, x, p0, p1, y, m, (int)n_cols, eps, st);
+  switch (c.maxch) {
+    case 2: return launch_tpr<OP, InT, 2>(c.tpr, x, p0, p1, y, m, (int)n_cols, eps, st);
+    case 4: return launch_tpr<OP, InT, 4>(c.tpr, x, p0, p1, y, m, (int)n_cols, eps, st);
+    case 8: return launch_tpr<OP, InT, 8>(c.tpr, x, p0, p1, y, m, (int)n_cols, eps, st);
+    default:
+      if constexpr (sizeof(InT) == 2)
+        return launch_tpr<OP, InT, 16>(c.tpr, x, p0, p1, y, m, (int)n_cols, eps, st);
+      else
+        DTAS_FAIL(DTAS_EINVAL, "row op: 16 chunks per thread is an fp16-only configuration");
+  }
 }
 
 template <int OP>
@@ -362,7 +446,7 @@ bool row_vec_ok(RowOp op, const void* x, const void* p0, const void* p1, const v
 
 int launch_row_op(RowOp op, const void* x, const void* p0, const void* p1, void* y, int64_t m,
                   int64_t n_cols, float eps, int in_dtype, const DeviceCtx* ctx, cudaStream_t st) {
-  const RowCfg c = row_cfg(m, n_cols, row_vec_ok(op, x, p0, p1, y, n_cols, in_dtype));
+  const RowCfg c = row_cfg(m, n_cols, row_vec_ok(op, x, p0, p1, y, n_cols, in_dtype), in_dtype);
   switch (op) {
     case ROW_RMSNORM: return launch_op<ROW_RMSNORM>(c, x, p0, p1, y, m, n_cols, eps, in_dtype, ctx, st);
     case ROW_SOFTMAX: return launch_op<ROW_SOFTMAX>(c, x, p0, p1, y, m, n_cols, eps, in_dtype, ctx, st);
@@ -371,9 +455,11 @@ int launch_row_op(RowOp op, const void* x, const void* p0, const void* p1, void*
   DTAS_FAIL(DTAS_EINVAL, "row op: unknown op %d", (int)op);
 }
 
+void row_set_override(int tpr) { g_row_tpr.store(tpr); }
+
 void row_variant_name(RowOp op, int64_t m, int64_t n_cols, char* buf, int len) {
   static const char* names[] = {"rms_norm", "softmax", "layer_norm"};
-  const RowCfg c = row_cfg(m, n_cols, n_cols % 8 == 0);
+  const RowCfg c = row_cfg(m, n_cols, n_cols % 8 == 0, DTAS_F16);
   if (c.generic)
     snprintf(buf, len, "%s_generic_cta256", names[op]);
   else

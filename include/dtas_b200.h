@@ -136,6 +136,18 @@ int dtas_variant_of(const char* op, int64_t m, int64_t n, int64_t k, int device,
  * width bn in {64,128,256} (0 = automatic) and split-K factor (0 = automatic). */
 int dtas_gemm_set_override(int bn, int split_k);
 
+/* Same for the elementwise class: vectors in flight per thread (0 = per-bucket default, else
+ * 1, 2, 4 or 8), grid cap in CTAs per SM (0 = default, < 0 = one tile per CTA without a cap)
+ * and streaming cache hints (-1 = default, 0 = off, 1 = on).                                 */
+int dtas_ew_set_override(int unroll, int ctas_per_sm, int stream_hints);
+
+/* Row reductions: threads that own one row (0 = per-bucket default, else a power of two in
+ * [32, 1024]; raised automatically when a row would not fit the register budget).
+ * GEMV: warps per output row (0 = automatic, else 1, 2, 4, 8) and 16-byte loads in flight per
+ * lane (0 = automatic, else 4 or 8).                                                          */
+int dtas_row_set_override(int threads_per_row);
+int dtas_gemv_set_override(int warps_per_row, int unroll);
+
 /* ---- bookkeeping ---------------------------------------------------------
  * dtas_last_error : message of the last failing call on this thread ("" if none).
  * dtas_launch_count: kernels launched by this library since load (all threads).

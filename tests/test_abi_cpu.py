@@ -50,7 +50,9 @@ def test_bucket_index_is_total_monotone_and_clamped(lib):
 
 def test_variant_names(lib):
     assert _abi.variant_of("cast", 1, 4096) == "ew_vec16_unroll1"
-    assert _abi.variant_of("add", 8192, 11008) == "ew_vec16_unroll4"
+    assert _abi.variant_of("add", 8192, 11008) == "ew_vec16_unroll1"     # two loads per vector already
+    assert _abi.variant_of("copy", 8192, 11008) == "ew_vec16_unroll2"
+    assert _abi.variant_of("copy", 1, 11008) == "ew_vec16_unroll1"
     assert "softmax_regs" in _abi.variant_of("softmax", 4096, 4096)
     assert "generic" in _abi.variant_of("rms_norm", 4, 101)
     assert _abi.variant_of("gemv", 1, 4096, 4096).startswith("gemv_vec16")
