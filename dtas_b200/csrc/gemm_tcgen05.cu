@@ -497,6 +497,279 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 }
 
 // ---------------------------------------------------------------------------------------
+// Two-CTA variant for large m: a cluster of two CTAs (the two SMs of a TPC) computes one
+// 256 x 256 tile with tcgen05.mma.cta_group::2.
+//
+// Each CTA loads only its own halves - 128 rows of X and 128 rows of W per k-block, 32 KB
+// per stage instead of 48 KB - so the ring is 7 stages deep (against 4), shared memory
+// feeds the tensor pipe at 2/3 of the single-CTA rate per flop, and L2 sees 2/3 of the
+// operand requests.  The MMA reads X rows from each CTA's own shared memory for that CTA's
+// 128 accumulator rows, and the W rows of both CTAs as the 256 columns of B.
+//
+// Protocol (rank 0 of the pair is the leader):
+//   * every CTA's producer waits on its own empty[s], then issues its two TMA loads with
+//     cta_group::2 so that the bytes are counted on the LEADER's full[s]; only the leader
+//     arms full[s], with the byte count of both CTAs;
+//   * the leader's MMA thread waits full[s], issues the MMAs, and commits with a multicast
+//     arrive to empty[s] of both CTAs; after the last k-block it commits to tmem_full[acc]
+//     of both CTAs;
+//   * the epilogue warps of both CTAs drain their own 128 accumulator rows and arrive on the
+//     leader's tmem_empty[acc] (8 arrivals: 4 warps x 2 CTAs; the peer arrives remotely);
+//   * before leaving, producers wait until every stage's last empty arrival has landed, and
+//     all threads of the pair meet at a cluster barrier, so nobody signals shared memory of
+//     a CTA that has exited; then both CTAs free their tensor memory.
+// No TMA multicast is involved: cta_group::2 only redirects the completion bytes.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1,
+                                                 uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3}], [%4];"
+      :
+      : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(leader_bar)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the barrier at this offset in every CTA of `cta_mask` once the MMAs issued so far retire.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+      "h"(cta_mask)
+      : "memory");
+}
+// Arrive on the barrier at the same offset in CTA `cta` of the cluster.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t cta) {
+  asm volatile(
+      "{\n\t"
+      ".reg .b32 remote;\n\t"
+      "mapa.shared::cluster.u32 remote, %0, %1;\n\t"
+      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [remote];\n\t"
+      "}" ::"r"(bar),
+      "r"(cta)
+      : "memory");
+}
+
+constexpr int kPairBN = 256;                 // columns of the pair's tile
+constexpr int kPairHalfBytes = BM * BK * 2;  // one 128 x 64 fp16 operand half: 16 KB
+constexpr int kPairStageBytes = 2 * kPairHalfBytes;
+constexpr int kPairStages = 7;
+constexpr int kPairTmemCols = 2 * kPairBN;
+constexpr int kPairBarBytes = (2 * kPairStages + 4) * 8 + 16;
+constexpr int kPairSmemBytes = 1024 + kPairStages * kPairStageBytes + kPairBarBytes;
+static_assert(kPairSmemBytes <= 227 * 1024, "smem");
+constexpr int kPairGroupM = 8;               // 256-row tiles per rasterisation band
+constexpr int ERR_PAIR_TAIL = 0x105;
+
+__device__ __forceinline__ void decode_pair_work(int w, int m_tiles, int n_tiles, int& mt, int& nt) {
+  const int band_tiles = kPairGroupM * n_tiles;
+  const int band = w / band_tiles;
+  const int in_band = w - band * band_tiles;
+  const int band_rows = min(kPairGroupM, m_tiles - band * kPairGroupM);
+  mt = band * kPairGroupM + in_band % band_rows;
+  nt = in_band / band_rows;
+}
+
+// a.m_tiles / a.n_tiles count 256 x 256 tiles here; a.splits must be 1.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+    gemm_f16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                                 const __grid_constant__ CUtensorMap tmap_w, const GemmArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bars = base + kPairStages * kPairStageBytes;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (kPairStages + s); };
+  auto tfull_bar = [&](int i) { return bars + 8u * (2 * kPairStages + i); };
+  auto tempty_bar = [&](int i) { return bars + 8u * (2 * kPairStages + 2 + i); };
+  const uint32_t tmem_slot = bars + 8u * (2 * kPairStages + 4);
+  uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(
+      gen_base + kPairStages * kPairStageBytes + 8 * (2 * kPairStages + 4));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();          // 0 = leader
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int total_work = a.m_tiles * a.n_tiles;
+  constexpr uint32_t kPeerMask = 0xFEFFFFFFu;       // clears the CTA-rank bit of a shared::cluster address
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(tfull_bar(i), 1);
+      mbar_init(tempty_bar(i), 2 * (kEpilogueThreads / 32));
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, kPairTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();      // barriers of both CTAs are initialised before anyone signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_x)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w)) : "memory");
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = pair; w < total_work && ok; w += n_pairs) {
+        int mt, nt;
+        decode_pair_work(w, a.m_tiles, a.n_tiles, mt, nt);
+        const int row0 = mt * 2 * BM + (int)rank * BM;          // this CTA's 128 rows of X
+        const int col0 = nt * kPairBN + (int)rank * (kPairBN / 2);  // this CTA's 128 rows of W
+        for (int kb = 0; kb < a.num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, a.status, ERR_PRODUCER)) { ok = false; break; }
+          if (leader) mbar_expect_tx(full_bar(stage), 2 * kPairStageBytes);
+          const uint32_t sa = base + stage * kPairStageBytes;
+          const uint32_t lbar = full_bar(stage) & kPeerMask;
+          tma_load_2d_pair(sa, &tmap_x, kb * BK, row0, lbar);
+          tma_load_2d_pair(sa + kPairHalfBytes, &tmap_w, kb * BK, col0, lbar);
+          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      // Tail: every stage's last release by the leader's MMA thread must have landed here
+      // before this CTA may exit.
+      for (int s = 0; s < kPairStages && ok; ++s) {
+        if (!mbar_wait(empty_bar(stage), phase ^ 1u, a.status, ERR_PAIR_TAIL)) ok = false;
+        if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader only)
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(kPairBN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      int iter = 0;
+      bool ok = true;
+      for (int w = pair; w < total_work && ok; w += n_pairs, ++iter) {
+        const int acc = iter & 1;
+        const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, a.status, ERR_MMA_TMEM)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kPairBN);
+        for (int kb = 0; kb < a.num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, a.status, ERR_MMA_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = base + stage * kPairStageBytes;
+          const uint64_t da = make_kmajor_sw128_desc(sa);
+          const uint64_t db = make_kmajor_sw128_desc(sa + kPairHalfBytes);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk)
+            umma_f16_pair(d_tmem, da + 2u * kk, db + 2u * kk, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          umma_commit_pair(empty_bar(stage), 0x3);
+          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit_pair(tfull_bar(acc), 0x3);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue (both CTAs)
+    const int quarter = warp & 3;
+    int iter = 0;
+    bool ok = true;
+    for (int w = pair; w < total_work && ok; w += n_pairs, ++iter) {
+      int mt, nt;
+      decode_pair_work(w, a.m_tiles, a.n_tiles, mt, nt);
+      const int acc = iter & 1;
+      const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
+      if (!mbar_wait(tfull_bar(acc), acc_phase, a.status, ERR_EPILOGUE)) { ok = false; break; }
+      tc_fence_after();
+      const int row = mt * 2 * BM + (int)rank * BM + quarter * 32 + lane;
+      const bool row_ok = row < a.m;
+      const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kPairBN);
+      const int col_base = nt * kPairBN;
+      __half* yrow = a.y + (int64_t)row * a.ldy;
+#pragma unroll 1
+      for (int c = 0; c < kPairBN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(t_addr + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = col_base + c * 32;
+        if (row_ok && col0 < a.n) {
+          if (a.bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < a.n) r[j] = __float_as_uint(__uint_as_float(r[j]) + __half2float(a.bias[col0 + j]));
+          }
+          if (a.vec_store && col0 + 32 <= a.n) {
+            uint4* dst = reinterpret_cast<uint4*>(yrow + col0);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 v;
+              __half2 h0 = __floats2half2_rn(__uint_as_float(r[8 * q + 0]), __uint_as_float(r[8 * q + 1]));
+              __half2 h1 = __floats2half2_rn(__uint_as_float(r[8 * q + 2]), __uint_as_float(r[8 * q + 3]));
+              __half2 h2 = __floats2half2_rn(__uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5]));
+              __half2 h3 = __floats2half2_rn(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7]));
+              v.x = *reinterpret_cast<uint32_t*>(&h0);
+              v.y = *reinterpret_cast<uint32_t*>(&h1);
+              v.z = *reinterpret_cast<uint32_t*>(&h2);
+              v.w = *reinterpret_cast<uint32_t*>(&h3);
+              dst[q] = v;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < a.n) yrow[col0 + j] = __float2half_rn(__uint_as_float(r[j]));
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty_bar(acc), 0);   // the leader's barrier, from either CTA
+    }
+  }
+
+  tc_fence_before();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kPairTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // SIMT fallback for shapes TMA cannot describe (k % 8 != 0 or unaligned bases): one thread
 // per output element, fp32 accumulation.  Correct for every shape, not a performance path.
 // ---------------------------------------------------------------------------------------
@@ -558,11 +831,14 @@ struct GemmPlan {
   int splits;
   int kb_per_split;
   bool simt;
+  bool pair = false;   // two-CTA 256 x 256 tiles (gemm_f16_tcgen05_pair_kernel)
 };
 
 std::atomic<int> g_override_bn{0};
 std::atomic<int> g_override_split{0};
 
+constexpr bool kPairByDefault = true;    // consider two-CTA tiles
+constexpr int kPairMinM = 257;           // below that a 256-row tile is mostly padding
 constexpr size_t kSplitKWorkspaceBytes = 64ull << 20;
 constexpr int kTileCounters = 4096;
 
@@ -627,6 +903,31 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
   }
   int bn = best_bn, splits = best_splits;
   const int obn = g_override_bn.load(), osp = g_override_split.load();
+  // The two-CTA kernel as one more candidate: 256 x 256 tiles on SM pairs.  Measured per
+  // k-block it runs at about 0.9x the time of two single-CTA 128 x 256 tiles (1.40-1.50
+  // PFLOP/s against 1.30-1.33 at m >= 4096), and its ring is deeper.
+  bool pair = false;
+  if (kPairByDefault && m >= kPairMinM) {
+    const int64_t pm = (m + 2 * BM - 1) / (2 * BM), pn = (n + kPairBN - 1) / kPairBN;
+    const int64_t work = pm * pn, slots = sm_count / 2 > 0 ? sm_count / 2 : 1;
+    const int64_t rounds = (work + slots - 1) / slots;
+    const double active = (double)(work < slots ? work : slots);
+    const double t_core = 0.9 * 512.0 / kClockGHz;
+    const double am = (double)(pm < kPairGroupM ? pm : kPairGroupM);
+    const double an = active / am < 1.0 ? 1.0 : active / am;
+    const double t_hbm = 128.0 * (an * kPairBN + am * 2 * BM) / kHbmGBs;
+    const double cost = (double)rounds * (num_kb * (t_core > t_hbm ? t_core : t_hbm) + kItemFixedNs);
+    pair = cost < best;
+  }
+  if (obn == 512) pair = true;
+  if (obn == 64 || obn == 128 || obn == 256) pair = false;
+  if (pair) {
+    p.bn = 256;
+    p.splits = 1;
+    p.kb_per_split = num_kb;
+    p.pair = true;
+    return p;
+  }
   if (obn == 64 || obn == 128 || obn == 256) {
     bn = obn;
     if (osp <= 0 && !ws_ok(bn, splits)) splits = 1;
@@ -659,6 +960,41 @@ int launch_tc(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a, i
   const int grid = total < sm_count ? total : sm_count;
   gemm_f16_tcgen05_kernel<BN><<<grid, kGemmThreads, C::kSmemBytes, st>>>(tx, tw, a);
   return after_launch("gemm_f16_tcgen05_kernel");
+}
+
+int launch_pair(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a, int sm_count, cudaStream_t st) {
+  static bool attr_set[64] = {false};
+  static int max_pairs[64] = {0};
+  int dev = 0;
+  DTAS_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_set[dev]) {
+    DTAS_CUDA(cudaFuncSetAttribute(gemm_f16_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   kPairSmemBytes));
+    // how many CTA pairs the device can hold at once (one CTA per SM, pairs share a TPC)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (unsigned)(sm_count / 2));
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = kPairSmemBytes;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_f16_tcgen05_pair_kernel, &cfg) != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      n = sm_count / 2;
+    }
+    max_pairs[dev] = n;
+    attr_set[dev] = true;
+  }
+  const int total = a.m_tiles * a.n_tiles;
+  int pairs = dev < 64 ? max_pairs[dev] : sm_count / 2;
+  if (pairs > total) pairs = total;
+  gemm_f16_tcgen05_pair_kernel<<<2 * pairs, kGemmThreads, kPairSmemBytes, st>>>(tx, tw, a);
+  return after_launch("gemm_f16_tcgen05_pair_kernel");
 }
 
 bool gemm_tma_ok(const void* x, const void* w, int64_t k) {
@@ -701,7 +1037,7 @@ int launch_gemm(const void* x, const void* w, const void* bias, void* y, int64_t
   CUtensorMap tx, tw;
   int rc = make_tmap(&tx, x, m, k, BM);
   if (rc != DTAS_OK) return rc;
-  rc = make_tmap(&tw, w, n, k, p.bn);
+  rc = make_tmap(&tw, w, n, k, p.pair ? kPairBN / 2 : p.bn);
   if (rc != DTAS_OK) return rc;
 
   GemmArgs a;
@@ -722,6 +1058,11 @@ int launch_gemm(const void* x, const void* w, const void* bias, void* y, int64_t
   a.vec_store = (aligned16(y) && (ldy % 8 == 0)) ? 1 : 0;
   if ((int64_t)a.m_tiles * a.n_tiles * a.splits > 0x7fffffffLL)
     DTAS_FAIL(DTAS_EINVAL, "gemm: too many tiles");
+  if (p.pair) {
+    a.m_tiles = (int)((m + 2 * BM - 1) / (2 * BM));
+    a.n_tiles = (int)((n + kPairBN - 1) / kPairBN);
+    return launch_pair(tx, tw, a, ctx->sm_count, st);
+  }
   switch (p.bn) {
     case 256: return launch_tc<256>(tx, tw, a, ctx->sm_count, st);
     case 128: return launch_tc<128>(tx, tw, a, ctx->sm_count, st);
@@ -733,6 +1074,10 @@ void gemm_variant_name(int64_t m, int64_t n, int64_t k, const DeviceCtx* ctx, ch
   const GemmPlan p = plan_gemm(m, n, k, ctx ? ctx->sm_count : 148, k % 8 == 0);
   if (p.simt) {
     snprintf(buf, len, "gemm_simt_fallback");
+    return;
+  }
+  if (p.pair) {
+    snprintf(buf, len, "gemm_tcgen05_2cta_bm256_bn256_bk64_s%d", kPairStages);
     return;
   }
   const int stages = p.bn == 256 ? Cfg<256>::kStages : (p.bn == 128 ? Cfg<128>::kStages : Cfg<64>::kStages);

@@ -255,7 +255,7 @@ def test_gemm_small_m_full_oracle(cuda_device):
         util.assert_matmul_close(np_of(y), oracle.gemm_nt(x.numpy(), w.numpy()).astype(np.float32), f"gemm m={m} full")
 
 
-@pytest.mark.parametrize("bn,split", [(64, 1), (128, 1), (256, 1), (64, 4), (128, 3), (256, 2), (128, 16)])
+@pytest.mark.parametrize("bn,split", [(64, 1), (128, 1), (256, 1), (64, 4), (128, 3), (256, 2), (128, 16), (512, 1)])
 def test_gemm_every_tile_width_and_split(cuda_device, bn, split):
     """Forces each kernel instantiation and split factor on ragged shapes (m, n, k not
     multiples of the tile), with a bias, writing into a column slab of a wider buffer."""
@@ -276,6 +276,31 @@ def test_gemm_every_tile_width_and_split(cuda_device, bn, split):
     want = x.float().numpy() @ w.float().numpy().T + b.float().numpy()
     util.assert_matmul_close(np_of(y), want, f"gemm bn={bn} split={split}")
     assert bool((wide[:, :8] == 5.0).all()) and bool((wide[:, 8 + n:] == 5.0).all()), "wrote outside its column slab"
+
+
+@pytest.mark.parametrize("m,n,k", [(1024, 4096, 4096), (4096, 12288, 4096), (1000, 2752, 11008), (300, 520, 72)])
+def test_gemm_two_cta_kernel(cuda_device, m, n, k):
+    """The cta_group::2 kernel (256 x 256 tiles on CTA pairs), forced, on full and ragged shapes."""
+    x = seeded_normal((m, k), 97, "float16")
+    w = seeded_normal((n, k), 98, "float16", scale=0.02)
+    xd, wd = x.to(cuda_device), w.to(cuda_device)
+    big, y = guarded((m, n), torch.float16, cuda_device, 5.0)
+    _abi.check(_abi.lib().dtas_gemm_set_override(512, 0))
+    try:
+        assert "2cta" in _abi.variant_of("gemm", m, n, k)
+        ops.gemm_nt(xd, wd, y)
+        ops.poll_status()
+        y2 = torch.empty_like(y)
+        ops.gemm_nt(xd, wd, y2)
+        ops.poll_status()
+    finally:
+        _abi.check(_abi.lib().dtas_gemm_set_override(0, 0))
+    assert_guards(big, m * n, 5.0, f"2cta gemm m={m} n={n} k={k}")
+    assert torch.equal(y, y2), "two runs differ"
+    _check_gemm_tiles(np_of(y), x, w, m, n, k, f"2cta gemm m={m} n={n} k={k}")
+    ref = (xd @ wd.T).float()
+    err = (y.float() - ref).abs().max().item()
+    assert err <= 2e-2 * ref.abs().max().item()
 
 
 def test_gemm_unaligned_k_uses_fallback(cuda_device):
