@@ -217,8 +217,8 @@ int dtas_variant_of(const char* op, int64_t m, int64_t n, int64_t k, int device,
 }
 
 int dtas_gemm_set_override(int bn, int split_k) {
-  if (!(bn == 0 || bn == 64 || bn == 128 || bn == 256 || bn == 512))
-    DTAS_FAIL(DTAS_EINVAL, "gemm override: bn must be 0, 64, 128, 256, or 512 for the two-CTA 256 x 256 tile");
+  if (!(bn == 0 || bn == 64 || bn == 128 || bn == 256 || bn == 512 || bn == 1024))
+    DTAS_FAIL(DTAS_EINVAL, "gemm override: bn must be 0, 64, 128, 256, 512 (two-CTA 256 x 256 tile) or 1024 (swapped operands, m <= 256)");
   if (split_k < 0 || split_k > 64) DTAS_FAIL(DTAS_EINVAL, "gemm override: split_k must be in [0, 64]");
   gemm_set_override(bn, split_k);
   return DTAS_OK;

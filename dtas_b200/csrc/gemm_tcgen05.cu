@@ -497,6 +497,261 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 }
 
 // ---------------------------------------------------------------------------------------
+// Small-m variant (m <= 256): the operands trade places.
+//
+// With few rows the GEMM is a stream over W, and what limits a CTA is how many bytes of W it
+// keeps in flight.  In the kernel above a stage always carries a 128-row X tile (16 KB, mostly
+// zero fill when m is small) next to the W tile, so at BN = 64 only a third of the ring is W.
+// Here the MMA computes Y^T: the 128 rows of the A operand are 128 rows of W (output columns),
+// the B operand is the X tile with MN = m rounded up to 16/32/64/128/256 rows.  A stage is
+// 16 KB of W plus MN*128 bytes of X, so at m = 16 the ring holds ten 16 KB W tiles.  The
+// accumulator is 128 (n) x MN (m) in tensor memory: an epilogue thread owns one output column
+// n and writes it row by row, so that a warp's store covers 32 consecutive columns of Y.
+//
+// Split-K partials are float4s of four consecutive rows, laid out [split][row group][column],
+// so that warps write and read 512 contiguous bytes; the last CTA to arrive at a tile
+// reduces in split order with eight independent loads in flight per thread.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+template <int MN>
+struct SwapCfg {
+  static constexpr int kWBytes = BM * BK * 2;            // 128 rows of W
+  static constexpr int kXBytes = MN * BK * 2;            // MN rows of X
+  static constexpr int kXPad = (kXBytes + 1023) / 1024 * 1024;
+  static constexpr int kStageBytes = kWBytes + kXPad;
+  static constexpr int kStages = kStageBudget / kStageBytes > 12 ? 12 : kStageBudget / kStageBytes;
+  static constexpr int kTmemCols = 2 * MN < 32 ? 32 : 2 * MN;
+  static constexpr int kBarBytes = (2 * kStages + 4) * 8 + 16;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kBarBytes;
+  static_assert(kSmemBytes <= 227 * 1024, "smem");
+  static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "tmem");
+};
+
+// a.n_tiles counts 128-column tiles of Y (128-row tiles of W); a.m_tiles is 1.
+template <int MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    gemm_f16_tcgen05_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                                 const __grid_constant__ CUtensorMap tmap_x, const GemmArgs a) {
+  using C = SwapCfg<MN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bars = base + C::kStages * C::kStageBytes;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (C::kStages + s); };
+  auto tfull_bar = [&](int i) { return bars + 8u * (2 * C::kStages + i); };
+  auto tempty_bar = [&](int i) { return bars + 8u * (2 * C::kStages + 2 + i); };
+  const uint32_t tmem_slot = bars + 8u * (2 * C::kStages + 4);
+  uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(gen_base + C::kStages * C::kStageBytes + 8 * (2 * C::kStages + 4));
+  volatile uint32_t* last_flag_ptr = tmem_slot_ptr + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_work = a.n_tiles * a.splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(tfull_bar(i), 1);
+      mbar_init(tempty_bar(i), kEpilogueThreads / 32);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_x)) : "memory");
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        const int nt = w / a.splits, sp = w - nt * a.splits;
+        const int kb0 = sp * a.kb_per_split;
+        const int kb1 = min(kb0 + a.kb_per_split, a.num_kb);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, a.status, ERR_PRODUCER)) { ok = false; break; }
+          mbar_expect_tx(full_bar(stage), C::kWBytes + C::kXBytes);
+          const uint32_t sa = base + stage * C::kStageBytes;
+          tma_load_2d(sa, &tmap_w, kb * BK, nt * BM, full_bar(stage));
+          tma_load_2d(sa + C::kWBytes, &tmap_x, kb * BK, 0, full_bar(stage));
+          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16_f32(MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int iter = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++iter) {
+        const int nt = w / a.splits, sp = w - nt * a.splits;
+        const int kb0 = sp * a.kb_per_split;
+        const int kb1 = min(kb0 + a.kb_per_split, a.num_kb);
+        const int acc = iter & 1;
+        const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, a.status, ERR_MMA_TMEM)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * MN);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, a.status, ERR_MMA_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = base + stage * C::kStageBytes;
+          const uint64_t da = make_kmajor_sw128_desc(sa);                // W rows: the M side
+          const uint64_t db = make_kmajor_sw128_desc(sa + C::kWBytes);   // X rows: the N side
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk)
+            umma_f16(d_tmem, da + 2u * kk, db + 2u * kk, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
+          umma_commit(empty_bar(stage));
+          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(tfull_bar(acc));
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quarter = warp & 3;
+    const int epi_tid = threadIdx.x - 64;
+    constexpr int kChunk = MN < 32 ? 16 : 32;     // columns per tcgen05.ld
+    int iter = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++iter) {
+      const int nt = w / a.splits, sp = w - nt * a.splits;
+      const int acc = iter & 1;
+      const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
+      if (!mbar_wait(tfull_bar(acc), acc_phase, a.status, ERR_EPILOGUE)) { ok = false; break; }
+      tc_fence_after();
+      const int col = nt * BM + quarter * 32 + lane;        // output column owned by this thread
+      const bool col_ok = col < a.n;
+      const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * MN);
+
+      if (a.splits == 1) {
+        const float bias = (a.bias != nullptr && col_ok) ? __half2float(a.bias[col]) : 0.f;
+#pragma unroll 1
+        for (int c = 0; c < MN / kChunk; ++c) {
+          uint32_t r[kChunk];
+          if constexpr (kChunk == 16) tmem_ld16(t_addr + c * kChunk, r);
+          else tmem_ld32(t_addr + c * kChunk, r);
+          tmem_ld_wait();
+          if (col_ok) {
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j) {
+              const int row = c * kChunk + j;
+              if (row < a.m) a.y[(int64_t)row * a.ldy + col] = __float2half_rn(__uint_as_float(r[j]) + bias);
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
+      } else {
+        // Partials as float4 = four consecutive rows (m) of one output column, laid out
+        // [split][row group][column]: a warp's store covers 32 consecutive columns (512 B).
+        // Row groups at or beyond m are never written or read.
+        const int64_t ncols_pad = (int64_t)a.n_tiles * BM;
+        const int groups = (a.m + 3) >> 2;                   // live row groups
+        float4* ws4 = reinterpret_cast<float4*>(a.ws);
+#pragma unroll 1
+        for (int c = 0; c < MN / kChunk; ++c) {
+          uint32_t r[kChunk];
+          if constexpr (kChunk == 16) tmem_ld16(t_addr + c * kChunk, r);
+          else tmem_ld32(t_addr + c * kChunk, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < kChunk / 4; ++q) {
+            const int g = c * (kChunk / 4) + q;
+            if (g < groups)
+              ws4[((int64_t)sp * (MN / 4) + g) * ncols_pad + col] =
+                  make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                              __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
+
+        __threadfence();
+        epilogue_bar_sync();
+        if (epi_tid == 0) {
+          const int old = atomicAdd(&a.counters[nt], 1);
+          const uint32_t last = (old == a.splits - 1) ? 1u : 0u;
+          if (last) a.counters[nt] = 0;
+          *last_flag_ptr = last;
+        }
+        epilogue_bar_sync();
+        const bool is_last = *last_flag_ptr != 0;
+        epilogue_bar_sync();
+        if (is_last) {
+          __threadfence();
+          const float bias = (a.bias != nullptr && col_ok) ? __half2float(a.bias[col]) : 0.f;
+          // two row groups per step, four splits per batch: up to 8 independent 16-byte loads in flight
+#pragma unroll 1
+          for (int g = 0; g < groups; g += 2) {
+            float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
+            const bool two = g + 1 < groups;
+#pragma unroll 1
+            for (int sb = 0; sb < a.splits; sb += 4) {
+              float4 v0[4], v1[4];
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const bool on = sb + u < a.splits;
+                const int64_t off = ((int64_t)(on ? sb + u : 0) * (MN / 4) + g) * ncols_pad + col;
+                v0[u] = on ? __ldcg(ws4 + off) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v1[u] = (on && two) ? __ldcg(ws4 + off + ncols_pad) : make_float4(0.f, 0.f, 0.f, 0.f);
+              }
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {     // fixed split order: deterministic
+                s0.x += v0[u].x; s0.y += v0[u].y; s0.z += v0[u].z; s0.w += v0[u].w;
+                s1.x += v1[u].x; s1.y += v1[u].y; s1.z += v1[u].z; s1.w += v1[u].w;
+              }
+            }
+            if (col_ok) {
+              const float o[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const int row = g * 4 + j;
+                if (row < a.m) a.y[(int64_t)row * a.ldy + col] = __float2half_rn(o[j] + bias);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // Two-CTA variant for large m: a cluster of two CTAs (the two SMs of a TPC) computes one
 // 256 x 256 tile with tcgen05.mma.cta_group::2.
 //
@@ -832,11 +1087,14 @@ struct GemmPlan {
   int kb_per_split;
   bool simt;
   bool pair = false;   // two-CTA 256 x 256 tiles (gemm_f16_tcgen05_pair_kernel)
+  int swap_mn = 0;     // > 0: swapped-operand kernel with the X tile padded to this many rows
 };
 
 std::atomic<int> g_override_bn{0};
 std::atomic<int> g_override_split{0};
 
+constexpr bool kSwapByDefault = true;    // swapped-operand kernel for small m
+constexpr int kSwapMaxM = 64;            // beyond that the X tile crowds W out of the ring
 constexpr bool kPairByDefault = true;    // consider two-CTA tiles
 constexpr int kPairMinM = 257;           // below that a 256-row tile is mostly padding
 constexpr size_t kSplitKWorkspaceBytes = 64ull << 20;
@@ -856,6 +1114,49 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
   const int num_kb = (int)((k + BK - 1) / BK);
   p.kb_per_split = num_kb;
   if (p.simt) return p;
+  const int obn0 = g_override_bn.load(), osp0 = g_override_split.load();
+  if ((m <= 256 && obn0 == 1024) || (m <= kSwapMaxM && obn0 == 0 && kSwapByDefault)) {
+    // Swapped-operand kernel: 128-row W tiles, split K until the work items fill the SMs.
+    const int mn = m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256)));
+    const int stage_bytes = BM * BK * 2 + ((mn * BK * 2 + 1023) / 1024) * 1024;
+    int stages = kStageBudget / stage_bytes;
+    if (stages > 12) stages = 12;
+    const int64_t t = (n + BM - 1) / BM;
+    constexpr double kClock = 1.7, kHbm = 6500.0;
+    double best_cost = 1e30;
+    int best_s = 1;
+    for (int want = 1; want <= 32; ++want) {
+      const int kb_per = (num_kb + want - 1) / want;
+      const int sp = (num_kb + kb_per - 1) / kb_per;
+      if (sp != want) continue;
+      if (want > 1 && (kb_per < 2 || t > kTileCounters || (int64_t)sp * (t * BM) * mn * 4 > (int64_t)kSplitKWorkspaceBytes)) continue;
+      if (osp0 > 0 && want != osp0 && !(want == 1 && osp0 > num_kb)) continue;
+      const int64_t work = t * sp;
+      const int64_t rounds = (work + sm_count - 1) / sm_count;
+      const double active = (double)(work < sm_count ? work : sm_count);
+      const double smem_clk = (double)stage_bytes / 128.0, mma_clk = 2.0 * mn;
+      const double t_core = (mma_clk > smem_clk ? mma_clk : smem_clk) / kClock;
+      const double t_hbm = (active * BM * BK * 2 + mn * BK * 2) / kHbm;
+      // A CTA alone pulls one stage per (ring round trip / stages); the round trip measured
+      // 2.6 us on B200 (TMA issue -> data -> MMA -> commit -> producer wake-up).
+      const double t_lat = 2600.0 / stages;
+      double t_kb = t_core > t_hbm ? t_core : t_hbm;
+      if (t_lat > t_kb) t_kb = t_lat;
+      double cost = (double)rounds * (kb_per * t_kb + 3000.0);
+      // the last CTA of a tile sums the partials in batches of 2 row groups x 4 splits, one L2
+      // round trip (~0.7 us) per batch
+      if (sp > 1) cost += 1500.0 + 700.0 * (double)((((m + 3) / 4) + 1) / 2) * (double)((sp + 3) / 4);
+      if (cost < best_cost * 0.999) {
+        best_cost = cost;
+        best_s = sp;
+      }
+    }
+    p.swap_mn = mn;
+    p.bn = BM;
+    p.splits = best_s;
+    p.kb_per_split = (num_kb + best_s - 1) / best_s;
+    return p;
+  }
   const int64_t m_tiles = (m + BM - 1) / BM;
   auto tiles = [&](int bn) { return m_tiles * ((n + bn - 1) / bn); };
   auto ws_ok = [&](int bn, int splits) {
@@ -893,7 +1194,9 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
       const double an = active / am < 1.0 ? 1.0 : active / am;
       const double t_hbm = 128.0 * (an * bn + am * rows_x) / kHbmGBs;
       double cost = (double)rounds * (kb_per * (t_core > t_hbm ? t_core : t_hbm) + kItemFixedNs);
-      if (s > 1) cost += 2.0 * s * (double)m * (double)n * 4.0 / kHbmGBs + 1000.0;
+      // split-K tail: partial traffic, plus the last CTA summing chunk by chunk and split by
+      // split, one L2 round trip (~0.7 us) each
+      if (s > 1) cost += 2.0 * s * (double)m * (double)n * 4.0 / kHbmGBs + 1500.0 + 700.0 * (bn / 32) * s;
       if (cost < best * 0.999) {
         best = cost;
         best_bn = bn;
@@ -997,6 +1300,23 @@ int launch_pair(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a,
   return after_launch("gemm_f16_tcgen05_pair_kernel");
 }
 
+template <int MN>
+int launch_swap(const CUtensorMap& tw, const CUtensorMap& tx, const GemmArgs& a, int sm_count, cudaStream_t st) {
+  using C = SwapCfg<MN>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  DTAS_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_set[dev]) {
+    DTAS_CUDA(cudaFuncSetAttribute(gemm_f16_tcgen05_swap_kernel<MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   C::kSmemBytes));
+    attr_set[dev] = true;
+  }
+  const int total = a.n_tiles * a.splits;
+  const int grid = total < sm_count ? total : sm_count;
+  gemm_f16_tcgen05_swap_kernel<MN><<<grid, kGemmThreads, C::kSmemBytes, st>>>(tw, tx, a);
+  return after_launch("gemm_f16_tcgen05_swap_kernel");
+}
+
 bool gemm_tma_ok(const void* x, const void* w, int64_t k) {
   return (k % 8 == 0) && aligned16(x) && aligned16(w);
 }
@@ -1035,7 +1355,7 @@ int launch_gemm(const void* x, const void* w, const void* bias, void* y, int64_t
     if (rc != DTAS_OK) return rc;
   }
   CUtensorMap tx, tw;
-  int rc = make_tmap(&tx, x, m, k, BM);
+  int rc = make_tmap(&tx, x, m, k, p.swap_mn > 0 ? p.swap_mn : BM);
   if (rc != DTAS_OK) return rc;
   rc = make_tmap(&tw, w, n, k, p.pair ? kPairBN / 2 : p.bn);
   if (rc != DTAS_OK) return rc;
@@ -1063,6 +1383,17 @@ int launch_gemm(const void* x, const void* w, const void* bias, void* y, int64_t
     a.n_tiles = (int)((n + kPairBN - 1) / kPairBN);
     return launch_pair(tx, tw, a, ctx->sm_count, st);
   }
+  if (p.swap_mn > 0) {
+    a.m_tiles = 1;
+    a.n_tiles = (int)((n + BM - 1) / BM);
+    switch (p.swap_mn) {
+      case 16: return launch_swap<16>(tw, tx, a, ctx->sm_count, st);
+      case 32: return launch_swap<32>(tw, tx, a, ctx->sm_count, st);
+      case 64: return launch_swap<64>(tw, tx, a, ctx->sm_count, st);
+      case 128: return launch_swap<128>(tw, tx, a, ctx->sm_count, st);
+      default: return launch_swap<256>(tw, tx, a, ctx->sm_count, st);
+    }
+  }
   switch (p.bn) {
     case 256: return launch_tc<256>(tx, tw, a, ctx->sm_count, st);
     case 128: return launch_tc<128>(tx, tw, a, ctx->sm_count, st);
@@ -1078,6 +1409,10 @@ void gemm_variant_name(int64_t m, int64_t n, int64_t k, const DeviceCtx* ctx, ch
   }
   if (p.pair) {
     snprintf(buf, len, "gemm_tcgen05_2cta_bm256_bn256_bk64_s%d", kPairStages);
+    return;
+  }
+  if (p.swap_mn > 0) {
+    snprintf(buf, len, "gemm_tcgen05_swap_n128_m%d_bk64_splitk%d", p.swap_mn, p.splits);
     return;
   }
   const int stages = p.bn == 256 ? Cfg<256>::kStages : (p.bn == 128 ? Cfg<128>::kStages : Cfg<64>::kStages);

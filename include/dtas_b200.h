@@ -133,8 +133,9 @@ int dtas_variant_of(const char* op, int64_t m, int64_t n, int64_t k, int device,
                     char* buf, int buf_len);
 
 /* Overrides the GEMM dispatch for testing and offline re-tuning: block-tile
- * width bn in {64,128,256} (0 = automatic; 512 = the two-CTA kernel with 256 x 256 tiles)
- * and split-K factor (0 = automatic). */
+ * width bn in {64,128,256} (0 = automatic; 512 = the two-CTA kernel with 256 x 256 tiles;
+ * 1024 = the swapped-operand kernel, which applies to m <= 256) and split-K factor
+ * (0 = automatic). */
 int dtas_gemm_set_override(int bn, int split_k);
 
 /* Same for the elementwise class: vectors in flight per thread (0 = per-bucket default, else

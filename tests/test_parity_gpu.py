@@ -255,7 +255,8 @@ def test_gemm_small_m_full_oracle(cuda_device):
         util.assert_matmul_close(np_of(y), oracle.gemm_nt(x.numpy(), w.numpy()).astype(np.float32), f"gemm m={m} full")
 
 
-@pytest.mark.parametrize("bn,split", [(64, 1), (128, 1), (256, 1), (64, 4), (128, 3), (256, 2), (128, 16), (512, 1)])
+@pytest.mark.parametrize("bn,split", [(64, 1), (128, 1), (256, 1), (64, 4), (128, 3), (256, 2), (128, 16), (512, 1),
+                                      (1024, 1), (1024, 4), (1024, 7)])
 def test_gemm_every_tile_width_and_split(cuda_device, bn, split):
     """Forces each kernel instantiation and split factor on ragged shapes (m, n, k not
     multiples of the tile), with a bias, writing into a column slab of a wider buffer."""
@@ -301,6 +302,29 @@ def test_gemm_two_cta_kernel(cuda_device, m, n, k):
     ref = (xd @ wd.T).float()
     err = (y.float() - ref).abs().max().item()
     assert err <= 2e-2 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("m", [1, 15, 16, 17, 33, 100, 129, 256])
+@pytest.mark.parametrize("split", [0, 1, 5])
+def test_gemm_swapped_operand_kernel(cuda_device, m, split):
+    """The m <= 256 kernel at every padded X-tile height, ragged n and k, bias, strided output."""
+    n, k = 1000, 1096
+    x = seeded_normal((m, k), 99, "float16")
+    w = seeded_normal((n, k), 100, "float16", scale=0.02)
+    b = seeded_normal((n,), 101, "float16", scale=0.1)
+    wide = torch.full((m, n + 16), 5.0, dtype=torch.float16, device=cuda_device)
+    y = wide[:, 8:8 + n]
+    _abi.check(_abi.lib().dtas_gemm_set_override(1024, split))
+    try:
+        assert "swap" in _abi.variant_of("gemm", m, n, k)
+        for _ in range(2):
+            ops.gemm_nt(x.to(cuda_device), w.to(cuda_device), y, bias=b.to(cuda_device))
+            ops.poll_status()
+    finally:
+        _abi.check(_abi.lib().dtas_gemm_set_override(0, 0))
+    want = x.float().numpy() @ w.float().numpy().T + b.float().numpy()
+    util.assert_matmul_close(np_of(y), want, f"swap gemm m={m} split={split}")
+    assert bool((wide[:, :8] == 5.0).all()) and bool((wide[:, 8 + n:] == 5.0).all()), "wrote outside its column slab"
 
 
 def test_gemm_unaligned_k_uses_fallback(cuda_device):
