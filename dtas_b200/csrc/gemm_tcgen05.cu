@@ -1066,8 +1066,29 @@ EncodeTiledFn get_encode_fn() {
 }
 
 // 2-D fp16 row-major [rows, cols] tensor, box = [box_rows, 64 cols], 128-byte swizzle,
-// out-of-bounds elements read as zero.
+// out-of-bounds elements read as zero.  Encoding costs a driver call; a descriptor depends
+// only on (base, rows, cols, box rows), so each host thread keeps its last few.
+struct TmapKey {
+  const void* ptr;
+  int64_t rows, cols;
+  int box_rows;
+};
+struct TmapSlot {
+  TmapKey key{nullptr, 0, 0, 0};
+  CUtensorMap map;
+};
+constexpr int kTmapCacheSlots = 16;
+thread_local TmapSlot tl_tmap_cache[kTmapCacheSlots];
+thread_local int tl_tmap_next = 0;
+
 int make_tmap(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int box_rows) {
+  for (int i = 0; i < kTmapCacheSlots; ++i) {
+    const TmapKey& k = tl_tmap_cache[i].key;
+    if (k.ptr == ptr && k.rows == rows && k.cols == cols && k.box_rows == box_rows) {
+      *map = tl_tmap_cache[i].map;
+      return DTAS_OK;
+    }
+  }
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) DTAS_FAIL(DTAS_ECUDA, "gemm: cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -1078,6 +1099,10 @@ int make_tmap(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int
                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) DTAS_FAIL(DTAS_ECUDA, "gemm: cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  TmapSlot& slot = tl_tmap_cache[tl_tmap_next];
+  tl_tmap_next = (tl_tmap_next + 1) % kTmapCacheSlots;
+  slot.key = TmapKey{ptr, rows, cols, box_rows};
+  slot.map = *map;
   return DTAS_OK;
 }
 

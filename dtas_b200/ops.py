@@ -11,7 +11,21 @@ import torch
 
 from . import _abi
 
+_L = None
+
+
+def _lib():
+    global _L
+    if _L is None:
+        _L = _abi.lib()
+    return _L
+
 _DTYPE_CODE = {torch.float16: _abi.F16, torch.float32: _abi.F32, torch.int8: _abi.I8}
+
+
+def _chk(status):
+    if status:
+        _abi.check(status)
 
 
 def _code(t):
@@ -30,17 +44,26 @@ def _rows_cols(t, name):
     raise _abi.DtasError(_abi.EINVAL, f"{name}: expected [m, H] or [1, m, H], got {tuple(t.shape)}")
 
 
+try:   # raw handle of the current stream without building a torch.cuda.Stream object
+    _raw_stream = torch._C._cuda_getCurrentRawStream
+except AttributeError:   # older / stripped builds
+    def _raw_stream(index):
+        return torch.cuda.current_stream(index).cuda_stream
+
+
 def _check(name, *tensors):
-    dev = tensors[0].device
-    if dev.type != "cuda":
-        raise _abi.DtasError(_abi.EINVAL, f"{name}: tensors must live on a CUDA device, got {dev}")
+    """Device index and current raw stream; rejects CPU, mixed-device and strided tensors."""
+    first = tensors[0]
+    if not first.is_cuda:
+        raise _abi.DtasError(_abi.EINVAL, f"{name}: tensors must live on a CUDA device, got {first.device}")
+    dev = first.device
     for t in tensors:
-        if t.device != dev:
-            raise _abi.DtasError(_abi.EINVAL, f"{name}: tensors on different devices")
         if not t.is_contiguous():
             raise _abi.DtasError(_abi.EINVAL, f"{name}: tensors must be contiguous")
-    index = dev.index if dev.index is not None else torch.cuda.current_device()
-    return index, torch.cuda.current_stream(index).cuda_stream
+        if t.device != dev:
+            raise _abi.DtasError(_abi.EINVAL, f"{name}: tensors on different devices")
+    index = dev.index
+    return index, _raw_stream(index)
 
 
 def _same_shape(name, a, b):
@@ -53,7 +76,7 @@ def cast(a, out):
     dev, st = _check("cast", a, out)
     _same_shape("cast", a, out)
     m, h = _rows_cols(a, "cast")
-    _abi.check(_abi.lib().dtas_cast(a.data_ptr(), out.data_ptr(), m, h, _code(a), _code(out), dev, st))
+    _chk(_lib().dtas_cast(a.data_ptr(), out.data_ptr(), m, h, _code(a), _code(out), dev, st))
     return out
 
 
@@ -65,7 +88,7 @@ def add(a, b, out):
     if not (a.dtype == b.dtype == out.dtype):
         raise _abi.DtasError(_abi.EINVAL, "add: dtypes differ")
     m, h = _rows_cols(a, "add")
-    _abi.check(_abi.lib().dtas_add(a.data_ptr(), b.data_ptr(), out.data_ptr(), m, h, _code(a), dev, st))
+    _chk(_lib().dtas_add(a.data_ptr(), b.data_ptr(), out.data_ptr(), m, h, _code(a), dev, st))
     return out
 
 
@@ -76,7 +99,7 @@ def copy(a, out):
     if a.dtype != out.dtype:
         raise _abi.DtasError(_abi.EINVAL, "copy: dtypes differ")
     m, h = _rows_cols(a, "copy")
-    _abi.check(_abi.lib().dtas_copy(a.data_ptr(), out.data_ptr(), m, h, _code(a), dev, st))
+    _chk(_lib().dtas_copy(a.data_ptr(), out.data_ptr(), m, h, _code(a), dev, st))
     return out
 
 
@@ -87,7 +110,7 @@ def rms_norm(x, weight, out, eps=1e-6):
     m, h = _rows_cols(x, "rms_norm")
     if weight.dtype != torch.float16 or weight.numel() != h or out.dtype != torch.float16:
         raise _abi.DtasError(_abi.EINVAL, "rms_norm: weight must be fp16 [H] and out fp16")
-    _abi.check(_abi.lib().dtas_rms_norm(x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, h,
+    _chk(_lib().dtas_rms_norm(x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, h,
                                         float(eps), _code(x), dev, st))
     return out
 
@@ -99,7 +122,7 @@ def softmax(x, out):
     if out.dtype != torch.float16:
         raise _abi.DtasError(_abi.EINVAL, "softmax: out must be fp16")
     m, h = _rows_cols(x, "softmax")
-    _abi.check(_abi.lib().dtas_softmax(x.data_ptr(), out.data_ptr(), m, h, _code(x), dev, st))
+    _chk(_lib().dtas_softmax(x.data_ptr(), out.data_ptr(), m, h, _code(x), dev, st))
     return out
 
 
@@ -112,7 +135,7 @@ def layer_norm(x, gamma, beta, out, eps=1e-5):
         raise _abi.DtasError(_abi.EINVAL, "layer_norm: gamma and beta must be fp32 [H]")
     if out.dtype != torch.float16:
         raise _abi.DtasError(_abi.EINVAL, "layer_norm: out must be fp16")
-    _abi.check(_abi.lib().dtas_layer_norm(x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), out.data_ptr(),
+    _chk(_lib().dtas_layer_norm(x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), out.data_ptr(),
                                           m, h, float(eps), _code(x), dev, st))
     return out
 
@@ -128,7 +151,7 @@ def gemv(x, w, out, bias=None):
         raise _abi.DtasError(_abi.EUNSUPPORTED, "gemv: only fp16 is implemented")
     if bias is not None and bias.numel() != n:
         raise _abi.DtasError(_abi.EINVAL, "gemv: bias must have N elements")
-    _abi.check(_abi.lib().dtas_gemv(x.data_ptr(), w.data_ptr(), bias.data_ptr() if bias is not None else None,
+    _chk(_lib().dtas_gemv(x.data_ptr(), w.data_ptr(), bias.data_ptr() if bias is not None else None,
                                     out.data_ptr(), n, k, _abi.F16, dev, st))
     return out
 
@@ -159,8 +182,8 @@ def gemm_nt(x, w, out, bias=None):
     if bias is not None and bias.numel() != n:
         raise _abi.DtasError(_abi.EINVAL, "gemm: bias must have N elements")
     dev = dev_t.index if dev_t.index is not None else torch.cuda.current_device()
-    st = torch.cuda.current_stream(dev).cuda_stream
-    _abi.check(_abi.lib().dtas_gemm_nt(x.data_ptr(), w.data_ptr(), bias.data_ptr() if bias is not None else None,
+    st = _raw_stream(dev)
+    _chk(_lib().dtas_gemm_nt(x.data_ptr(), w.data_ptr(), bias.data_ptr() if bias is not None else None,
                                        out.data_ptr(), m, n, k, ldy, _abi.F16, dev, st))
     return out
 
@@ -169,4 +192,4 @@ def poll_status(device=None):
     """Synchronises `device` and raises DtasError(ETIMEOUT) if a bounded device-side wait gave up."""
     if device is None:
         device = torch.cuda.current_device()
-    _abi.check(_abi.lib().dtas_poll_status(int(device)))
+    _chk(_lib().dtas_poll_status(int(device)))

@@ -57,7 +57,8 @@ def test_variant_names(lib):
     assert "generic" in _abi.variant_of("rms_norm", 4, 101)
     assert _abi.variant_of("gemv", 1, 4096, 4096).startswith("gemv_vec16")
     assert _abi.variant_of("gemm", 8192, 22016, 4096) == "gemm_tcgen05_2cta_bm256_bn256_bk64_s7"
-    assert _abi.variant_of("gemm", 16, 22016, 4096).startswith("gemm_tcgen05_bm128_bn")
+    assert _abi.variant_of("gemm", 16, 22016, 4096).startswith("gemm_tcgen05_swap_n128_m16")
+    assert _abi.variant_of("gemm", 255, 22016, 4096).startswith("gemm_tcgen05_bm128_bn")
     assert _abi.variant_of("gemm", 33, 70, 101) == "gemm_simt_fallback"
     with pytest.raises(_abi.DtasError):
         _abi.variant_of("nope", 1, 1)
