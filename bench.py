@@ -384,8 +384,11 @@ def run_gpu(args):
         (op, m, n, k), t = dominant
         achieved = algorithmic(op, m, n, k)["flops"] / t["mean_us"] / 1e6
         roofline = {"bound": "tensor", "achieved": round(achieved, 1), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                    "frac": round(achieved / peaks["bf16_tflops"], 3), "traffic": GEMM_NCU_TRAFFIC_BYTES,
-                    "kernel": f"gemm_f16_tcgen05_kernel<256> m={m} n={n} k={k}", "peak_source": f"{peak_src}, burst",
+                    "frac": round(achieved / peaks["bf16_tflops"], 3),
+                    "traffic": GEMM_NCU_TRAFFIC_BYTES if (m, n, k) == (8192, 22016, 4096) else None,
+                    "kernel": f"{_abi.variant_of(op, m, n, k, local)} m={m} n={n} k={k}", "peak_source": f"{peak_src}, burst",
+                    "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of this launch at N=1 "
+                                    "(profiles/gemm_pair_kernel_m8192_n22016_k4096.md); null when sharded",
                     "frac_of_sustained": round(achieved / peaks["bf16_tflops_sustained"], 3),
                     "launch_us": round(t["mean_us"], 1)}
 
@@ -420,9 +423,10 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant GEMM, from the ncu
-# capture summarised under profiles/ (None until a capture of that kernel has been taken).
-GEMM_NCU_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant GEMM
+# (m=8192, n=22016, k=4096, two-CTA kernel), from the ncu capture summarised in
+# profiles/gemm_pair_kernel_m8192_n22016_k4096.md (1032.2 MB read + 346.1 MB written).
+GEMM_NCU_TRAFFIC_BYTES = 1378254592
 
 
 # -----------------------------------------------------------------------------------------
