@@ -46,6 +46,8 @@ PROTOTYPES = {
     "dtas_bucket_count": (_i, [ctypes.c_char_p]),
     "dtas_variant_of": (_i, [ctypes.c_char_p, _i64, _i64, _i64, _i, ctypes.c_char_p, _i]),
     "dtas_gemm_set_override": (_i, [_i, _i]),
+    "dtas_gemm_table_set": (_i, [_i64, _i64, _i64, _i64, _i, _i]),
+    "dtas_gemm_table_clear": (_i, []),
     "dtas_ew_set_override": (_i, [_i, _i, _i]),
     "dtas_row_set_override": (_i, [_i]),
     "dtas_gemv_set_override": (_i, [_i, _i]),

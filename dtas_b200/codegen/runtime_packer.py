@@ -94,6 +94,11 @@ class RuntimeModule:
         _abi.lib()   # fail here, loudly, if the kernel library is missing
         self.record = record
         self._funcs = {name: PackedOp(name, e) for name, e in record["functions"].items()}
+        # measured GEMM choices travel with the module: (re-)install them in the library
+        for e in record["functions"].values():
+            for row in e.get("measured_table", []):
+                _abi.check(_abi.lib().dtas_gemm_table_set(e["spec"]["cols"], e["spec"]["k"], row["m_lo"], row["m_hi"],
+                                                          row["bn"], row["split"]))
 
     def __getitem__(self, name):
         return self._funcs[name]

@@ -119,5 +119,7 @@ int launch_gemm(const void* x, const void* w, const void* bias, void* y, int64_t
                 int64_t k, int64_t ldy, DeviceCtx* ctx, cudaStream_t st);
 void gemm_variant_name(int64_t m, int64_t n, int64_t k, const DeviceCtx* ctx, char* buf, int len);
 void gemm_set_override(int bn, int split_k);
+int gemm_table_set(int64_t n, int64_t k, int64_t m_lo, int64_t m_hi, int bn, int split_k);
+void gemm_table_clear();
 
 }  // namespace dtas

@@ -224,6 +224,18 @@ int dtas_gemm_set_override(int bn, int split_k) {
   return DTAS_OK;
 }
 
+int dtas_gemm_table_set(int64_t n, int64_t k, int64_t m_lo, int64_t m_hi, int bn, int split_k) {
+  if (n <= 0 || k <= 0 || m_lo < 1 || m_hi < m_lo) DTAS_FAIL(DTAS_EINVAL, "gemm table: bad key n=%lld k=%lld m=[%lld,%lld]", (long long)n, (long long)k, (long long)m_lo, (long long)m_hi);
+  if (!(bn == 0 || bn == 64 || bn == 128 || bn == 256 || bn == 512 || bn == 1024)) DTAS_FAIL(DTAS_EINVAL, "gemm table: bad tile code %d", bn);
+  if (split_k < 0 || split_k > 64) DTAS_FAIL(DTAS_EINVAL, "gemm table: split_k must be in [0, 64]");
+  return gemm_table_set(n, k, m_lo, m_hi, bn, split_k);
+}
+
+int dtas_gemm_table_clear(void) {
+  gemm_table_clear();
+  return DTAS_OK;
+}
+
 int dtas_ew_set_override(int unroll, int ctas_per_sm, int stream_hints) {
   if (!(unroll == 0 || unroll == 1 || unroll == 2 || unroll == 4 || unroll == 8))
     DTAS_FAIL(DTAS_EINVAL, "elementwise override: unroll must be 0, 1, 2, 4 or 8");

@@ -38,6 +38,7 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -1118,6 +1119,42 @@ struct GemmPlan {
 std::atomic<int> g_override_bn{0};
 std::atomic<int> g_override_split{0};
 
+// Measured dispatch table: (n, k, [m_lo, m_hi]) -> (tile code, split).  This is the counterpart of
+// the reference's per-range best configs (python/dtas/engine/tuner.py:103-133): Engine.tune_module
+// with search=True times the candidates on the device and installs the winners here; without
+// entries the cost model below decides.
+struct TableEntry {
+  int64_t n, k, m_lo, m_hi;
+  int bn, split;
+};
+std::vector<TableEntry> g_table;
+std::mutex g_table_mutex;
+
+bool table_lookup(int64_t m, int64_t n, int64_t k, int* bn, int* split) {
+  std::lock_guard<std::mutex> lock(g_table_mutex);
+  for (const TableEntry& e : g_table)
+    if (e.n == n && e.k == k && m >= e.m_lo && m <= e.m_hi) {
+      *bn = e.bn;
+      *split = e.split;
+      return true;
+    }
+  return false;
+}
+
+// Global override first, then the table, else 0 / 0 (cost model).
+void effective_choice(int64_t m, int64_t n, int64_t k, int* bn, int* split) {
+  *bn = g_override_bn.load();
+  *split = g_override_split.load();
+  if (*bn == 0 && *split == 0) {
+    int tb = 0, ts = 0;
+    if (table_lookup(m, n, k, &tb, &ts)) {
+      *bn = tb;
+      *split = ts;
+    }
+  }
+  if (*bn == 1024 && m > 256) *bn = 0;   // the swapped kernel only exists for m <= 256
+}
+
 constexpr bool kSwapByDefault = true;    // swapped-operand kernel for small m
 constexpr int kSwapMaxM = 64;            // beyond that the X tile crowds W out of the ring
 constexpr bool kPairByDefault = true;    // consider two-CTA tiles
@@ -1139,7 +1176,8 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
   const int num_kb = (int)((k + BK - 1) / BK);
   p.kb_per_split = num_kb;
   if (p.simt) return p;
-  const int obn0 = g_override_bn.load(), osp0 = g_override_split.load();
+  int obn0 = 0, osp0 = 0;
+  effective_choice(m, n, k, &obn0, &osp0);
   if ((m <= 256 && obn0 == 1024) || (m <= kSwapMaxM && obn0 == 0 && kSwapByDefault)) {
     // Swapped-operand kernel: 128-row W tiles, split K until the work items fill the SMs.
     const int mn = m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256)));
@@ -1230,7 +1268,7 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
     }
   }
   int bn = best_bn, splits = best_splits;
-  const int obn = g_override_bn.load(), osp = g_override_split.load();
+  const int obn = obn0, osp = osp0;
   // The two-CTA kernel as one more candidate: 256 x 256 tiles on SM pairs.  Measured per
   // k-block it runs at about 0.9x the time of two single-CTA 128 x 256 tiles (1.40-1.50
   // PFLOP/s against 1.30-1.33 at m >= 4096), and its ring is deeper.
@@ -1347,6 +1385,23 @@ bool gemm_tma_ok(const void* x, const void* w, int64_t k) {
 }
 
 }  // namespace
+
+int gemm_table_set(int64_t n, int64_t k, int64_t m_lo, int64_t m_hi, int bn, int split_k) {
+  std::lock_guard<std::mutex> lock(g_table_mutex);
+  for (TableEntry& e : g_table)
+    if (e.n == n && e.k == k && e.m_lo == m_lo && e.m_hi == m_hi) {
+      e.bn = bn;
+      e.split = split_k;
+      return DTAS_OK;
+    }
+  g_table.push_back(TableEntry{n, k, m_lo, m_hi, bn, split_k});
+  return DTAS_OK;
+}
+
+void gemm_table_clear() {
+  std::lock_guard<std::mutex> lock(g_table_mutex);
+  g_table.clear();
+}
 
 void gemm_set_override(int bn, int split_k) {
   g_override_bn.store(bn);

@@ -120,12 +120,83 @@ class Engine:
         table, stmt = self.get_index_table(merged, range_div_factor)
         return info, merged, table, stmt
 
-    def tune_module(self, mod, arch, range_div_factor: int = 256):
+    # -- on-device search (GEMM) -------------------------------------------------------------
+    @staticmethod
+    def gemm_candidates(m_hi: int):
+        """(tile code, split) candidates for row counts up to m_hi; tile codes as in
+        dtas_gemm_set_override (64/128/256 single-CTA widths, 512 two-CTA, 1024 swapped operands)."""
+        cands = []
+        if m_hi <= 256:
+            cands += [(1024, s) for s in (1, 2, 3, 4, 6, 8, 12, 16)]
+            cands += [(bn, s) for bn in (64, 128, 256) for s in (1, 2, 4)]
+        elif m_hi <= 1024:
+            cands += [(bn, s) for bn in (128, 256) for s in (1, 2)] + [(512, 1)]
+        else:
+            cands += [(256, 1), (512, 1)]
+        return cands
+
+    def search_gemm(self, info: FuncInfo, ranges, device, samples=2, min_repeat_ms=5.0):
+        """The reference's inner loop (python/dtas/schedule/tir_base.py:181-241: build each
+        candidate, time it at sample shapes spread over the range, keep the fastest), with
+        hand-written kernel variants as the candidates and CUDA-graph replay as the timer.
+        Returns {range tuple: (GEMMConfig, tile code, split, mean us)}."""
+        import torch
+        from ..profiling import time_op
+        from .. import ops
+        lib = _abi.lib()
+        spec = info.spec
+        n, k = spec.cols, spec.k
+        w = (torch.randn((n, k), device=device, dtype=torch.float32) * 0.02).to(torch.float16)
+        best = {}
+        try:
+            for rt in ranges:
+                r = rt[0]
+                ms = sorted({max(r.start, (r.start + r.end) // 2), r.end}) if samples >= 2 else [r.end]
+                xs = [torch.randn((m, k), device=device, dtype=torch.float16) for m in ms]
+                ys = [torch.empty((m, n), device=device, dtype=torch.float16) for m in ms]
+                results = []
+                for bn, split in self.gemm_candidates(r.end):
+                    _abi.check(lib.dtas_gemm_set_override(bn, split))
+                    variant = _abi.variant_of("gemm", r.end, n, k, device.index or 0)
+                    total = 0.0
+                    for x, y in zip(xs, ys):
+                        t = time_op(lambda i: ops.gemm_nt(x, w, y), warmup=2, number=2, min_repeat_ms=min_repeat_ms, graph=True)
+                        total += t["mean_us"]
+                    results.append((total / len(xs), bn, split, variant))
+                    if get_log_level() >= 2:
+                        debug_info(f"{info.name} {r}: {variant} {total / len(xs):.2f} us")
+                results.sort()
+                us, bn, split, variant = results[0]
+                best[rt] = (config_for("gemm", variant), bn, split, us)
+                ops.poll_status(device.index or 0)
+        finally:
+            _abi.check(lib.dtas_gemm_set_override(0, 0))
+        return best
+
+    def tune_module(self, mod, arch, range_div_factor: int = 256, search: bool = False):
+        """search=True (needs a GPU): GEMM functions are tuned on the device - every candidate
+        kernel variant is timed per range, the winners are installed in the library's dispatch
+        table and stored in work_dir, so `load_module_from_file` restores them."""
         self._collect_upper_bounds(mod)
         entries = {}
         for name, func in self._functions(mod):
             try:
                 info, merged, table, stmt = self.tune_func(func, name, arch, range_div_factor)
+                measured = None
+                if search and info.spec.op == "gemm":
+                    device = getattr(arch, "device", None)
+                    if device is None:
+                        raise RuntimeError("tune_module(search=True) needs a CUDA device")
+                    ranges = self.gen_range_tuples(info, range_div_factor)
+                    found = self.search_gemm(info, ranges, device)
+                    merged = self.merge_same_configs({rt: cfg for rt, (cfg, _, _, _) in found.items()})
+                    table, stmt = self.get_index_table(merged, range_div_factor)
+                    measured = []
+                    for rt, cfg in merged.items():
+                        # tile code / split of any member range with this config
+                        bn, split = next((b, s) for r2, (c2, b, s, _) in found.items() if c2 == cfg and r2[0].start >= rt[0].start and r2[0].end <= rt[0].end)
+                        measured.append({"m_lo": rt[0].start, "m_hi": rt[0].end, "bn": bn, "split": split})
+                        _abi.check(_abi.lib().dtas_gemm_table_set(info.spec.cols, info.spec.k, rt[0].start, rt[0].end, bn, split))
             except UnsupportedWorkload as e:
                 if get_log_level() >= 1:
                     debug_info(f"skipping {name}: {e}")
@@ -141,6 +212,8 @@ class Engine:
                 "index_table": table,
                 "index_stmt": stmt,
             }
+            if measured is not None:
+                entries[name]["measured_table"] = measured
             if get_log_level() >= 1:
                 debug_info(f"{name}: {info.kind.name}, {len(merged)} merged range(s)")
         record = {"library": _abi.lib().dtas_version().decode(), "arch": type(arch).__name__, "functions": entries}

@@ -138,6 +138,14 @@ int dtas_variant_of(const char* op, int64_t m, int64_t n, int64_t k, int device,
  * (0 = automatic). */
 int dtas_gemm_set_override(int bn, int split_k);
 
+/* Measured dispatch table for the GEMM: for weight shape (n, k) and row counts m_lo..m_hi use
+ * tile code bn (as in dtas_gemm_set_override) and split_k.  The counterpart of the per-range
+ * best configs the reference's search records (python/dtas/engine/tuner.py:103-133,211-299);
+ * Engine.tune_module(..., search=True) fills it from on-device timings.  Calls whose shape has
+ * no entry are planned by the built-in cost model.  dtas_gemm_set_override wins over the table. */
+int dtas_gemm_table_set(int64_t n, int64_t k, int64_t m_lo, int64_t m_hi, int bn, int split_k);
+int dtas_gemm_table_clear(void);
+
 /* Same for the elementwise class: vectors in flight per thread (0 = per-bucket default, else
  * 1, 2, 4 or 8), grid cap in CTAs per SM (0 = default, < 0 = one tile per CTA without a cap)
  * and streaming cache hints (-1 = default, 0 = off, 1 = on).                                 */

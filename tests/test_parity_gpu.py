@@ -401,3 +401,37 @@ def test_against_tvm_golden(cuda_device, name):
         util.assert_matmul_close(got, want.astype(np.float32), name)
     else:
         util.assert_reduction_close(got, want, name, abs_floor=1e-6 if op == "layer_norm" else 0.0)
+
+
+def test_engine_search_installs_measured_table(cuda_device, tmp_path):
+    """Engine.tune_module(search=True): candidates are timed on the device, the winners land in
+    the library's dispatch table, survive a reload from work_dir, and results stay correct."""
+    import dtas_b200
+    from dtas_b200 import Engine, arch, load_module_from_file
+    from dtas_b200.workloads import OpSpec
+    dtas_b200.set_log_level(0)
+    n, k = 1024, 1024
+    spec = OpSpec("proj", "gemm", cols=n, k=k, upper=512)
+    lib = _abi.lib()
+    try:
+        rt = Engine(1, True, str(tmp_path)).tune_module([spec], arch=arch.B200(0), range_div_factor=128, search=True)
+        rows = rt.record["functions"]["proj"]["measured_table"]
+        assert rows and rows[0]["m_lo"] == 1 and rows[-1]["m_hi"] == 512
+        for r in rows:
+            want = _abi.variant_of("gemm", r["m_hi"], n, k)
+            lib.dtas_gemm_set_override(r["bn"], r["split"])
+            assert _abi.variant_of("gemm", r["m_hi"], n, k) == want, "table entry is not what dispatch uses"
+            lib.dtas_gemm_set_override(0, 0)
+        x = seeded_normal((200, k), 1, "float16")
+        w = seeded_normal((n, k), 2, "float16", scale=0.02)
+        y = torch.empty((200, n), dtype=torch.float16, device=cuda_device)
+        rt["proj"](x.to(cuda_device), w.to(cuda_device), y)
+        ops.poll_status()
+        util.assert_matmul_close(np_of(y), x.float().numpy() @ w.float().numpy().T, "gemm after search")
+        lib.dtas_gemm_table_clear()
+        rt2 = load_module_from_file(str(tmp_path))
+        assert rt2.record["functions"]["proj"]["measured_table"] == rows
+        assert _abi.variant_of("gemm", rows[0]["m_hi"], n, k) == rt.record["functions"]["proj"]["ranges"][0]["config"]["variant"]
+    finally:
+        lib.dtas_gemm_set_override(0, 0)
+        lib.dtas_gemm_table_clear()
