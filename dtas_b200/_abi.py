@@ -75,7 +75,27 @@ def lib():
             fn.restype = restype
             fn.argtypes = argtypes
         _lib = handle
+        _install_default_tables(handle)
     return _lib
+
+
+DEFAULT_GEMM_TABLE = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tables", "b200_gemm.json")
+
+
+def _install_default_tables(handle):
+    """Installs the shipped measured GEMM table (written by `python -m dtas_b200.retune`) unless
+    DTAS_B200_NO_TABLE is set.  Shapes it does not cover fall back to the cost model."""
+    if os.environ.get("DTAS_B200_NO_TABLE") or not os.path.exists(DEFAULT_GEMM_TABLE):
+        return 0
+    import json
+    with open(DEFAULT_GEMM_TABLE) as f:
+        rec = json.load(f)
+    count = 0
+    for shape in rec.get("gemm", []):
+        for r in shape["rows"]:
+            if handle.dtas_gemm_table_set(shape["n"], shape["k"], r["m_lo"], r["m_hi"], r["bn"], r["split"]) == OK:
+                count += 1
+    return count
 
 
 def check(status):

@@ -141,12 +141,14 @@ class Engine:
         hand-written kernel variants as the candidates and CUDA-graph replay as the timer.
         Returns {range tuple: (GEMMConfig, tile code, split, mean us)}."""
         import torch
-        from ..profiling import time_op
+        from ..profiling import rotation_for, time_op
         from .. import ops
         lib = _abi.lib()
         spec = info.spec
         n, k = spec.cols, spec.k
-        w = (torch.randn((n, k), device=device, dtype=torch.float32) * 0.02).to(torch.float16)
+        # enough copies of W that consecutive launches cannot be served from L2
+        copies = rotation_for(2 * n * k, max_copies=8)
+        ws = [(torch.randn((n, k), device=device, dtype=torch.float32) * 0.02).to(torch.float16) for _ in range(copies)]
         best = {}
         try:
             for rt in ranges:
@@ -160,7 +162,7 @@ class Engine:
                     variant = _abi.variant_of("gemm", r.end, n, k, device.index or 0)
                     total = 0.0
                     for x, y in zip(xs, ys):
-                        t = time_op(lambda i: ops.gemm_nt(x, w, y), warmup=2, number=2, min_repeat_ms=min_repeat_ms, graph=True)
+                        t = time_op(lambda i: ops.gemm_nt(x, ws[i % copies], y), warmup=2, number=2, min_repeat_ms=min_repeat_ms, graph=True)
                         total += t["mean_us"]
                     results.append((total / len(xs), bn, split, variant))
                     if get_log_level() >= 2:

@@ -49,6 +49,7 @@ def test_bucket_index_is_total_monotone_and_clamped(lib):
 
 
 def test_variant_names(lib):
+    lib.dtas_gemm_table_clear()          # the cost model's own choices, not a shipped table's
     assert _abi.variant_of("cast", 1, 4096) == "ew_vec16_unroll1"
     assert _abi.variant_of("add", 8192, 11008) == "ew_vec16_unroll1"     # two loads per vector already
     assert _abi.variant_of("copy", 8192, 11008) == "ew_vec16_unroll2"
@@ -62,6 +63,28 @@ def test_variant_names(lib):
     assert _abi.variant_of("gemm", 33, 70, 101) == "gemm_simt_fallback"
     with pytest.raises(_abi.DtasError):
         _abi.variant_of("nope", 1, 1)
+    _abi._install_default_tables(lib)
+
+
+def test_gemm_table_overrides_cost_model(lib):
+    lib.dtas_gemm_table_clear()
+    try:
+        base = _abi.variant_of("gemm", 16, 4096, 4096)
+        assert lib.dtas_gemm_table_set(4096, 4096, 1, 32, 128, 2) == _abi.OK
+        assert _abi.variant_of("gemm", 16, 4096, 4096) == "gemm_tcgen05_bm128_bn128_bk64_s6_splitk2"
+        assert _abi.variant_of("gemm", 33, 4096, 4096) == _abi.variant_of("gemm", 33, 4096, 4096)
+        assert _abi.variant_of("gemm", 16, 4096, 11008) != "gemm_tcgen05_bm128_bn128_bk64_s6_splitk2"   # other shape untouched
+        assert lib.dtas_gemm_set_override(256, 1) == _abi.OK                       # the global override wins
+        assert _abi.variant_of("gemm", 16, 4096, 4096) == "gemm_tcgen05_bm128_bn256_bk64_s4_splitk1"
+        lib.dtas_gemm_set_override(0, 0)
+        assert lib.dtas_gemm_table_set(4096, 4096, 0, 32, 128, 2) == _abi.EINVAL
+        assert lib.dtas_gemm_table_set(4096, 4096, 1, 32, 100, 2) == _abi.EINVAL
+        lib.dtas_gemm_table_clear()
+        assert _abi.variant_of("gemm", 16, 4096, 4096) == base
+    finally:
+        lib.dtas_gemm_set_override(0, 0)
+        lib.dtas_gemm_table_clear()
+        _abi._install_default_tables(lib)
 
 
 def test_argument_validation_needs_no_device(lib):

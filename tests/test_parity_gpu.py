@@ -435,3 +435,4 @@ def test_engine_search_installs_measured_table(cuda_device, tmp_path):
     finally:
         lib.dtas_gemm_set_override(0, 0)
         lib.dtas_gemm_table_clear()
+        _abi._install_default_tables(lib)
