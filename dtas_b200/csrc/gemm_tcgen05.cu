@@ -201,6 +201,9 @@ struct GemmArgs {
   int m, n, k;
   int m_tiles, n_tiles, splits, kb_per_split, num_kb;
   int vec_store;      // 1 when 16-byte stores into Y are aligned
+  // swapped-operand kernel only
+  int sk_per = 0;     // > 0: stream-K, every CTA owns sk_per consecutive (tile, k-block) units
+  int slots_cap = 0;  // partial-tile slots reserved per output tile in the workspace
 };
 
 template <int BN>
@@ -509,9 +512,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 // accumulator is 128 (n) x MN (m) in tensor memory: an epilogue thread owns one output column
 // n and writes it row by row, so that a warp's store covers 32 consecutive columns of Y.
 //
-// Split-K partials are float4s of four consecutive rows, laid out [split][row group][column],
-// so that warps write and read 512 contiguous bytes; the last CTA to arrive at a tile
-// reduces in split order with eight independent loads in flight per thread.
+// K is cut either into a fixed number of slices per tile, or stream-K fashion: the (tile,
+// k-block) units are dealt out in equal consecutive runs, so the CTAs finish together even
+// when the tile count is no multiple of the SM count.  Partial tiles are float4s of four
+// consecutive rows, laid out [tile][slot][row group][column], so that warps write and read
+// 512 contiguous bytes; the last CTA to arrive at a tile sums the slots in K order with
+// eight independent loads in flight per thread.
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
   asm volatile(
@@ -537,6 +543,51 @@ struct SwapCfg {
   static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "tmem");
 };
 
+// The work of a CTA of the swapped-operand kernel as a sequence of segments: k-blocks
+// [kb0, kb1) of output tile nt, being contribution `slot` of `count` to that tile.
+//   * fixed split (a.sk_per == 0): items w = (tile, split) dealt round-robin to the CTAs;
+//   * stream-K (a.sk_per > 0): the (tile, k-block) units are numbered tile-major and CTA c owns
+//     units [c*per, (c+1)*per); a tile is finished by whichever CTAs its units fall to, so every
+//     CTA streams the same number of k-blocks whatever the tile count.
+// The three roles walk the same sequence, each with its own copy of the iterator.
+struct SwapSeg {
+  int nt, kb0, kb1, slot, count;
+};
+struct SwapIter {
+  int pos, end;
+  __device__ __forceinline__ void init(const GemmArgs& a) {
+    if (a.sk_per > 0) {
+      const int total = a.n_tiles * a.num_kb;
+      pos = min((int)blockIdx.x * a.sk_per, total);
+      end = min(pos + a.sk_per, total);
+    } else {
+      pos = blockIdx.x;
+      end = a.n_tiles * a.splits;
+    }
+  }
+  __device__ __forceinline__ bool next(const GemmArgs& a, SwapSeg& s) {
+    if (pos >= end) return false;
+    if (a.sk_per > 0) {
+      s.nt = pos / a.num_kb;
+      s.kb0 = pos - s.nt * a.num_kb;
+      s.kb1 = min(a.num_kb, s.kb0 + (end - pos));
+      const int u0 = s.nt * a.num_kb;
+      const int first = u0 / a.sk_per, last = (u0 + a.num_kb - 1) / a.sk_per;
+      s.count = last - first + 1;
+      s.slot = (int)blockIdx.x - first;
+      pos += s.kb1 - s.kb0;
+    } else {
+      s.nt = pos / a.splits;
+      s.slot = pos - s.nt * a.splits;
+      s.count = a.splits;
+      s.kb0 = s.slot * a.kb_per_split;
+      s.kb1 = min(s.kb0 + a.kb_per_split, a.num_kb);
+      pos += gridDim.x;
+    }
+    return true;
+  }
+};
+
 // a.n_tiles counts 128-column tiles of Y (128-row tiles of W); a.m_tiles is 1.
 template <int MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -557,7 +608,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   volatile uint32_t* last_flag_ptr = tmem_slot_ptr + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int total_work = a.n_tiles * a.splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
@@ -587,11 +637,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-        const int nt = w / a.splits, sp = w - nt * a.splits;
-        const int kb0 = sp * a.kb_per_split;
-        const int kb1 = min(kb0 + a.kb_per_split, a.num_kb);
-        for (int kb = kb0; kb < kb1; ++kb) {
+      SwapIter it;
+      SwapSeg sg;
+      it.init(a);
+      while (ok && it.next(a, sg)) {
+        const int nt = sg.nt;
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, a.status, ERR_PRODUCER)) { ok = false; break; }
           mbar_expect_tx(full_bar(stage), C::kWBytes + C::kXBytes);
           const uint32_t sa = base + stage * C::kStageBytes;
@@ -609,10 +660,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       uint32_t phase = 0;
       int iter = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++iter) {
-        const int nt = w / a.splits, sp = w - nt * a.splits;
-        const int kb0 = sp * a.kb_per_split;
-        const int kb1 = min(kb0 + a.kb_per_split, a.num_kb);
+      SwapIter it;
+      SwapSeg sg;
+      it.init(a);
+      for (; ok && it.next(a, sg); ++iter) {
+        const int kb0 = sg.kb0, kb1 = sg.kb1;
         const int acc = iter & 1;
         const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, a.status, ERR_MMA_TMEM)) { ok = false; break; }
@@ -640,8 +692,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     constexpr int kChunk = MN < 32 ? 16 : 32;     // columns per tcgen05.ld
     int iter = 0;
     bool ok = true;
-    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++iter) {
-      const int nt = w / a.splits, sp = w - nt * a.splits;
+    SwapIter it;
+    SwapSeg sg;
+    it.init(a);
+    for (; ok && it.next(a, sg); ++iter) {
+      const int nt = sg.nt, sp = sg.slot, n_parts = sg.count;
       const int acc = iter & 1;
       const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
       if (!mbar_wait(tfull_bar(acc), acc_phase, a.status, ERR_EPILOGUE)) { ok = false; break; }
@@ -650,7 +705,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const bool col_ok = col < a.n;
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * MN);
 
-      if (a.splits == 1) {
+      if (n_parts == 1) {
         const float bias = (a.bias != nullptr && col_ok) ? __half2float(a.bias[col]) : 0.f;
 #pragma unroll 1
         for (int c = 0; c < MN / kChunk; ++c) {
@@ -671,11 +726,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (lane == 0) mbar_arrive(tempty_bar(acc));
       } else {
         // Partials as float4 = four consecutive rows (m) of one output column, laid out
-        // [split][row group][column]: a warp's store covers 32 consecutive columns (512 B).
-        // Row groups at or beyond m are never written or read.
-        const int64_t ncols_pad = (int64_t)a.n_tiles * BM;
+        // [tile][slot][row group][column in tile]: a warp's store covers 32 consecutive columns
+        // (512 B).  Row groups at or beyond m are never written or read.
         const int groups = (a.m + 3) >> 2;                   // live row groups
-        float4* ws4 = reinterpret_cast<float4*>(a.ws);
+        float4* ws4 = reinterpret_cast<float4*>(a.ws) + (int64_t)nt * a.slots_cap * (MN / 4) * BM + (quarter * 32 + lane);
+        auto ws_off = [&](int slot, int g) { return ((int64_t)slot * (MN / 4) + g) * BM; };
 #pragma unroll 1
         for (int c = 0; c < MN / kChunk; ++c) {
           uint32_t r[kChunk];
@@ -686,7 +741,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           for (int q = 0; q < kChunk / 4; ++q) {
             const int g = c * (kChunk / 4) + q;
             if (g < groups)
-              ws4[((int64_t)sp * (MN / 4) + g) * ncols_pad + col] =
+              ws4[ws_off(sp, g)] =
                   make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
                               __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
           }
@@ -699,7 +754,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         epilogue_bar_sync();
         if (epi_tid == 0) {
           const int old = atomicAdd(&a.counters[nt], 1);
-          const uint32_t last = (old == a.splits - 1) ? 1u : 0u;
+          const uint32_t last = (old == n_parts - 1) ? 1u : 0u;
           if (last) a.counters[nt] = 0;
           *last_flag_ptr = last;
         }
@@ -709,20 +764,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (is_last) {
           __threadfence();
           const float bias = (a.bias != nullptr && col_ok) ? __half2float(a.bias[col]) : 0.f;
-          // two row groups per step, four splits per batch: up to 8 independent 16-byte loads in flight
+          // two row groups per step, four slots per batch: up to 8 independent 16-byte loads in flight;
+          // slots are summed in slot order = K order, whatever the arrival order
 #pragma unroll 1
           for (int g = 0; g < groups; g += 2) {
             float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
             const bool two = g + 1 < groups;
 #pragma unroll 1
-            for (int sb = 0; sb < a.splits; sb += 4) {
+            for (int sb = 0; sb < n_parts; sb += 4) {
               float4 v0[4], v1[4];
 #pragma unroll
               for (int u = 0; u < 4; ++u) {
-                const bool on = sb + u < a.splits;
-                const int64_t off = ((int64_t)(on ? sb + u : 0) * (MN / 4) + g) * ncols_pad + col;
+                const bool on = sb + u < n_parts;
+                const int64_t off = ws_off(on ? sb + u : 0, g);
                 v0[u] = on ? __ldcg(ws4 + off) : make_float4(0.f, 0.f, 0.f, 0.f);
-                v1[u] = (on && two) ? __ldcg(ws4 + off + ncols_pad) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v1[u] = (on && two) ? __ldcg(ws4 + off + BM) : make_float4(0.f, 0.f, 0.f, 0.f);
               }
 #pragma unroll
               for (int u = 0; u < 4; ++u) {     // fixed split order: deterministic
@@ -1114,6 +1170,9 @@ struct GemmPlan {
   bool simt;
   bool pair = false;   // two-CTA 256 x 256 tiles (gemm_f16_tcgen05_pair_kernel)
   int swap_mn = 0;     // > 0: swapped-operand kernel with the X tile padded to this many rows
+  int sk_per = 0;      // swapped kernel, stream-K: (tile, k-block) units per CTA (0 = fixed split)
+  int sk_grid = 0;     //   CTAs launched
+  int slots_cap = 0;   //   partial slots reserved per tile
 };
 
 std::atomic<int> g_override_bn{0};
@@ -1152,7 +1211,7 @@ void effective_choice(int64_t m, int64_t n, int64_t k, int* bn, int* split) {
       *split = ts;
     }
   }
-  if (*bn == 1024 && m > 256) *bn = 0;   // the swapped kernel only exists for m <= 256
+  if ((*bn == 1024 || *bn == 2048) && m > 256) *bn = 0;   // the swapped kernel only exists for m <= 256
 }
 
 constexpr bool kSwapByDefault = true;    // swapped-operand kernel for small m
@@ -1178,7 +1237,7 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
   if (p.simt) return p;
   int obn0 = 0, osp0 = 0;
   effective_choice(m, n, k, &obn0, &osp0);
-  if ((m <= 256 && obn0 == 1024) || (m <= kSwapMaxM && obn0 == 0 && kSwapByDefault)) {
+  if ((m <= 256 && (obn0 == 1024 || obn0 == 2048)) || (m <= kSwapMaxM && obn0 == 0 && kSwapByDefault)) {
     // Swapped-operand kernel: 128-row W tiles, split K until the work items fill the SMs.
     const int mn = m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256)));
     const int stage_bytes = BM * BK * 2 + ((mn * BK * 2 + 1023) / 1024) * 1024;
@@ -1218,6 +1277,36 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
     p.bn = BM;
     p.splits = best_s;
     p.kb_per_split = (num_kb + best_s - 1) / best_s;
+    p.slots_cap = best_s;
+    // Stream-K: every CTA streams the same number of k-blocks whatever the tile count; only
+    // tiles that straddle two CTAs' ranges go through the workspace.
+    if (obn0 == 2048 || (obn0 == 0 && osp0 == 0)) {
+      const int64_t total = t * num_kb;
+      int64_t grid = total / 2 < sm_count ? total / 2 : sm_count;
+      if (grid < 1) grid = 1;
+      const int64_t per = (total + grid - 1) / grid;
+      grid = (total + per - 1) / per;
+      const int slots = (int)((num_kb - 1) / per) + 2;
+      const bool fits = t <= kTileCounters && t * slots * (int64_t)mn * BM * 4 <= (int64_t)kSplitKWorkspaceBytes;
+      if (fits && total < 0x7fffffffLL) {
+        const double smem_clk = (double)stage_bytes / 128.0, mma_clk = 2.0 * mn;
+        const double t_core = (mma_clk > smem_clk ? mma_clk : smem_clk) / kClock;
+        const double t_hbm = ((double)grid * BM * BK * 2 + mn * BK * 2) / kHbm;
+        const double t_lat = 2600.0 / stages;
+        double t_kb = t_core > t_hbm ? t_core : t_hbm;
+        if (t_lat > t_kb) t_kb = t_lat;
+        double cost = (double)per * t_kb + 3000.0;
+        if (per % num_kb != 0)   // some tile is shared between CTAs
+          cost += 1500.0 + 700.0 * (double)((((m + 3) / 4) + 1) / 2) * (double)((slots + 3) / 4);
+        if (obn0 == 2048 || cost < best_cost) {
+          p.sk_per = (int)per;
+          p.sk_grid = (int)grid;
+          p.slots_cap = slots;
+          p.splits = 1;
+          p.kb_per_split = num_kb;
+        }
+      }
+    }
     return p;
   }
   const int64_t m_tiles = (m + BM - 1) / BM;
@@ -1375,7 +1464,8 @@ int launch_swap(const CUtensorMap& tw, const CUtensorMap& tx, const GemmArgs& a,
     attr_set[dev] = true;
   }
   const int total = a.n_tiles * a.splits;
-  const int grid = total < sm_count ? total : sm_count;
+  int grid = total < sm_count ? total : sm_count;
+  if (a.sk_per > 0) grid = (a.n_tiles * a.num_kb + a.sk_per - 1) / a.sk_per;
   gemm_f16_tcgen05_swap_kernel<MN><<<grid, kGemmThreads, C::kSmemBytes, st>>>(tw, tx, a);
   return after_launch("gemm_f16_tcgen05_swap_kernel");
 }
@@ -1466,6 +1556,14 @@ int launch_gemm(const void* x, const void* w, const void* bias, void* y, int64_t
   if (p.swap_mn > 0) {
     a.m_tiles = 1;
     a.n_tiles = (int)((n + BM - 1) / BM);
+    a.sk_per = p.sk_per;
+    a.slots_cap = p.slots_cap;
+    if (p.sk_per > 0) {
+      rc = ensure_splitk_scratch(ctx);
+      if (rc != DTAS_OK) return rc;
+      a.ws = ctx->splitk_ws;
+      a.counters = ctx->tile_counters;
+    }
     switch (p.swap_mn) {
       case 16: return launch_swap<16>(tw, tx, a, ctx->sm_count, st);
       case 32: return launch_swap<32>(tw, tx, a, ctx->sm_count, st);
@@ -1492,7 +1590,10 @@ void gemm_variant_name(int64_t m, int64_t n, int64_t k, const DeviceCtx* ctx, ch
     return;
   }
   if (p.swap_mn > 0) {
-    snprintf(buf, len, "gemm_tcgen05_swap_n128_m%d_bk64_splitk%d", p.swap_mn, p.splits);
+    if (p.sk_per > 0)
+      snprintf(buf, len, "gemm_tcgen05_swap_n128_m%d_bk64_streamk%d", p.swap_mn, p.sk_grid);
+    else
+      snprintf(buf, len, "gemm_tcgen05_swap_n128_m%d_bk64_splitk%d", p.swap_mn, p.splits);
     return;
   }
   const int stages = p.bn == 256 ? Cfg<256>::kStages : (p.bn == 128 ? Cfg<128>::kStages : Cfg<64>::kStages);

@@ -124,10 +124,11 @@ class Engine:
     @staticmethod
     def gemm_candidates(m_hi: int):
         """(tile code, split) candidates for row counts up to m_hi; tile codes as in
-        dtas_gemm_set_override (64/128/256 single-CTA widths, 512 two-CTA, 1024 swapped operands)."""
+        dtas_gemm_set_override (64/128/256 single-CTA widths, 512 two-CTA, 1024 swapped operands with a
+        fixed split, 2048 swapped operands with stream-K)."""
         cands = []
         if m_hi <= 256:
-            cands += [(1024, s) for s in (1, 2, 3, 4, 6, 8, 12, 16)]
+            cands += [(1024, s) for s in (1, 2, 3, 4, 6, 8, 12, 16)] + [(2048, 0)]
             cands += [(bn, s) for bn in (64, 128, 256) for s in (1, 2, 4)]
         elif m_hi <= 1024:
             cands += [(bn, s) for bn in (128, 256) for s in (1, 2)] + [(512, 1)]

@@ -134,8 +134,8 @@ int dtas_variant_of(const char* op, int64_t m, int64_t n, int64_t k, int device,
 
 /* Overrides the GEMM dispatch for testing and offline re-tuning: block-tile
  * width bn in {64,128,256} (0 = automatic; 512 = the two-CTA kernel with 256 x 256 tiles;
- * 1024 = the swapped-operand kernel, which applies to m <= 256) and split-K factor
- * (0 = automatic). */
+ * 1024 = the swapped-operand kernel, which applies to m <= 256; 2048 = the same kernel with
+ * stream-K work distribution, where split_k is ignored) and split-K factor (0 = automatic). */
 int dtas_gemm_set_override(int bn, int split_k);
 
 /* Measured dispatch table for the GEMM: for weight shape (n, k) and row counts m_lo..m_hi use

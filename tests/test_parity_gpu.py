@@ -305,18 +305,21 @@ def test_gemm_two_cta_kernel(cuda_device, m, n, k):
 
 
 @pytest.mark.parametrize("m", [1, 15, 16, 17, 33, 100, 129, 256])
-@pytest.mark.parametrize("split", [0, 1, 5])
+@pytest.mark.parametrize("split", [0, 1, 5, "streamk"])
 def test_gemm_swapped_operand_kernel(cuda_device, m, split):
-    """The m <= 256 kernel at every padded X-tile height, ragged n and k, bias, strided output."""
+    """The m <= 256 kernel at every padded X-tile height, ragged n and k, bias, strided output;
+    K cut into fixed slices or dealt out stream-K fashion."""
     n, k = 1000, 1096
     x = seeded_normal((m, k), 99, "float16")
     w = seeded_normal((n, k), 100, "float16", scale=0.02)
     b = seeded_normal((n,), 101, "float16", scale=0.1)
     wide = torch.full((m, n + 16), 5.0, dtype=torch.float16, device=cuda_device)
     y = wide[:, 8:8 + n]
-    _abi.check(_abi.lib().dtas_gemm_set_override(1024, split))
+    code, split = (2048, 0) if split == "streamk" else (1024, split)
+    _abi.check(_abi.lib().dtas_gemm_set_override(code, split))
     try:
         assert "swap" in _abi.variant_of("gemm", m, n, k)
+        assert ("streamk" in _abi.variant_of("gemm", m, n, k)) == (code == 2048)
         for _ in range(2):
             ops.gemm_nt(x.to(cuda_device), w.to(cuda_device), y, bias=b.to(cuda_device))
             ops.poll_status()
