@@ -194,14 +194,13 @@ __host__ __device__ constexpr uint32_t make_idesc_f16_f32(int n) {
 struct GemmArgs {
   __half* y;
   const __half* bias;
-  float* ws;          // split-K partials: [splits][m][n] fp32
+  float* ws;          // partial tiles of shared output tiles (layout: see the epilogues)
   int* counters;      // one arrival counter per output tile (zero between launches)
   int* status;
   int64_t ldy;
   int m, n, k;
   int m_tiles, n_tiles, splits, kb_per_split, num_kb;
   int vec_store;      // 1 when 16-byte stores into Y are aligned
-  // swapped-operand kernel only
   int sk_per = 0;     // > 0: stream-K, every CTA owns sk_per consecutive (tile, k-block) units
   int slots_cap = 0;  // partial-tile slots reserved per output tile in the workspace
 };
@@ -219,12 +218,10 @@ struct Cfg {
   static_assert(kSmemBytes <= 227 * 1024, "smem");
 };
 
-// Work item -> (m_tile, n_tile, split).  Tiles are visited band by band (kGroupM m-tiles
-// per band); inside a band the m index runs fastest, so CTAs that run side by side read
-// the same W tile and a small set of X tiles.
-__device__ __forceinline__ void decode_work(const GemmArgs& a, int w, int& mt, int& nt, int& sp) {
-  sp = w % a.splits;
-  const int tile = w / a.splits;
+// Tile index -> (m_tile, n_tile).  Tiles are visited band by band (kGroupM m-tiles per band);
+// inside a band the m index runs fastest, so CTAs that run side by side read the same W tile
+// and a small set of X tiles.
+__device__ __forceinline__ void decode_tile(const GemmArgs& a, int tile, int& mt, int& nt) {
   const int band_tiles = kGroupM * a.n_tiles;
   const int band = tile / band_tiles;
   const int in_band = tile - band * band_tiles;
@@ -232,6 +229,52 @@ __device__ __forceinline__ void decode_work(const GemmArgs& a, int w, int& mt, i
   mt = band * kGroupM + in_band % band_rows;
   nt = in_band / band_rows;
 }
+
+// The work of a CTA as a sequence of segments: k-blocks [kb0, kb1) of output tile (mt, nt),
+// being contribution `slot` of `count` to that tile.
+//   * fixed split (a.sk_per == 0): items (tile, split) dealt round-robin to the CTAs;
+//   * stream-K (a.sk_per > 0): the (tile, k-block) units are numbered tile-major and CTA c owns
+//     units [c*per, (c+1)*per), so all CTAs stream the same number of k-blocks whatever the
+//     tile count; a tile whose units fall to several CTAs is finished through the workspace.
+// Producer, MMA issuer and epilogue each walk the same sequence with their own iterator.
+struct TileSeg {
+  int mt, nt, tile, kb0, kb1, slot, count;
+};
+struct TileIter {
+  int pos, end;
+  __device__ __forceinline__ void init(const GemmArgs& a) {
+    if (a.sk_per > 0) {
+      const int total = a.m_tiles * a.n_tiles * a.num_kb;
+      pos = min((int)blockIdx.x * a.sk_per, total);
+      end = min(pos + a.sk_per, total);
+    } else {
+      pos = blockIdx.x;
+      end = a.m_tiles * a.n_tiles * a.splits;
+    }
+  }
+  __device__ __forceinline__ bool next(const GemmArgs& a, TileSeg& s) {
+    if (pos >= end) return false;
+    if (a.sk_per > 0) {
+      s.tile = pos / a.num_kb;
+      s.kb0 = pos - s.tile * a.num_kb;
+      s.kb1 = min(a.num_kb, s.kb0 + (end - pos));
+      const int u0 = s.tile * a.num_kb;
+      const int first = u0 / a.sk_per, last = (u0 + a.num_kb - 1) / a.sk_per;
+      s.count = last - first + 1;
+      s.slot = (int)blockIdx.x - first;
+      pos += s.kb1 - s.kb0;
+    } else {
+      s.tile = pos / a.splits;
+      s.slot = pos - s.tile * a.splits;
+      s.count = a.splits;
+      s.kb0 = s.slot * a.kb_per_split;
+      s.kb1 = min(s.kb0 + a.kb_per_split, a.num_kb);
+      pos += gridDim.x;
+    }
+    decode_tile(a, s.tile, s.mt, s.nt);
+    return true;
+  }
+};
 
 template <int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -254,7 +297,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   (void)last_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int total_work = a.m_tiles * a.n_tiles * a.splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
@@ -285,12 +327,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-        int mt, nt, sp;
-        decode_work(a, w, mt, nt, sp);
-        const int kb0 = sp * a.kb_per_split;
-        const int kb1 = min(kb0 + a.kb_per_split, a.num_kb);
-        for (int kb = kb0; kb < kb1; ++kb) {
+      TileIter it;
+      TileSeg sg;
+      it.init(a);
+      while (ok && it.next(a, sg)) {
+        const int mt = sg.mt, nt = sg.nt;
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, a.status, ERR_PRODUCER)) { ok = false; break; }
           mbar_expect_tx(full_bar(stage), C::kStageBytes);
           const uint32_t sa = base + stage * C::kStageBytes;
@@ -309,11 +351,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       uint32_t phase = 0;
       int iter = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++iter) {
-        int mt, nt, sp;
-        decode_work(a, w, mt, nt, sp);
-        const int kb0 = sp * a.kb_per_split;
-        const int kb1 = min(kb0 + a.kb_per_split, a.num_kb);
+      TileIter it;
+      TileSeg sg;
+      it.init(a);
+      for (; ok && it.next(a, sg); ++iter) {
+        const int kb0 = sg.kb0, kb1 = sg.kb1;
         const int acc = iter & 1;
         const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, a.status, ERR_MMA_TMEM)) { ok = false; break; }
@@ -343,9 +385,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int epi_tid = threadIdx.x - 64;
     int iter = 0;
     bool ok = true;
-    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++iter) {
-      int mt, nt, sp;
-      decode_work(a, w, mt, nt, sp);
+    TileIter it;
+    TileSeg sg;
+    it.init(a);
+    for (; ok && it.next(a, sg); ++iter) {
+      const int mt = sg.mt, nt = sg.nt, sp = sg.slot, n_parts = sg.count;
       const int acc = iter & 1;
       const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
       if (!mbar_wait(tfull_bar(acc), acc_phase, a.status, ERR_EPILOGUE)) { ok = false; break; }
@@ -355,7 +399,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
       const int col_base = nt * BN;
 
-      if (a.splits == 1) {
+      if (n_parts == 1) {
         __half* yrow = a.y + (int64_t)row * a.ldy;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
@@ -395,26 +439,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar(acc));
       } else {
-        // split-K: park the fp32 partial, then the last slice to arrive reduces.
-        float* wrow = a.ws + ((int64_t)sp * a.m + row) * a.n;
+        // Shared tile: park the fp32 partial, then the last contributor to arrive reduces.
+        // Partials are float4s of four consecutive columns, laid out
+        // [n tile][slot][column group][row]: the 32 lanes of a warp (32 consecutive rows) write
+        // and read 512 contiguous bytes; rows at or beyond m are never touched.
+        float4* ws4 = reinterpret_cast<float4*>(a.ws) + (int64_t)nt * a.slots_cap * (BN / 4) * a.m + row;
+        auto ws_off = [&](int slot, int c4) { return ((int64_t)slot * (BN / 4) + c4) * a.m; };
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
           tmem_ld32(t_addr + c * 32, r);
           tmem_ld_wait();
-          const int col0 = col_base + c * 32;
-          if (row_ok && col0 < a.n) {
-            if (col0 + 32 <= a.n && (a.n & 3) == 0) {
-              float4* dst = reinterpret_cast<float4*>(wrow + col0);
+          if (row_ok && col_base + c * 32 < a.n) {
 #pragma unroll
-              for (int q = 0; q < 8; ++q)
-                dst[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                     __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < a.n) wrow[col0 + j] = __uint_as_float(r[j]);
-            }
+            for (int q = 0; q < 8; ++q)
+              ws4[ws_off(sp, c * 8 + q)] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                       __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
           }
         }
         tc_fence_before();
@@ -424,10 +464,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         __threadfence();
         epilogue_bar_sync();
         if (epi_tid == 0) {
-          const int tile = mt * a.n_tiles + nt;
-          const int old = atomicAdd(&a.counters[tile], 1);
-          const uint32_t last = (old == a.splits - 1) ? 1u : 0u;
-          if (last) a.counters[tile] = 0;   // every slice has arrived: re-arm for the next launch
+          const int old = atomicAdd(&a.counters[sg.tile], 1);
+          const uint32_t last = (old == n_parts - 1) ? 1u : 0u;
+          if (last) a.counters[sg.tile] = 0;   // every contributor has arrived: re-arm for the next launch
           *last_flag_ptr = last;
         }
         epilogue_bar_sync();
@@ -444,20 +483,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               float acc32[32];
 #pragma unroll
               for (int j = 0; j < 32; ++j) acc32[j] = 0.f;
-              const bool full = (col0 + 32 <= a.n) && ((a.n & 3) == 0);
-              for (int s = 0; s < a.splits; ++s) {
-                const float* src = a.ws + ((int64_t)s * a.m + row) * a.n + col0;
-                if (full) {
+              // two slots per batch: 16 independent 16-byte loads in flight; slots are added in
+              // slot order = K order, whatever the arrival order
+#pragma unroll 1
+              for (int sb = 0; sb < n_parts; sb += 2) {
+                float4 v0[8], v1[8];
+                const bool two = sb + 1 < n_parts;
 #pragma unroll
-                  for (int q = 0; q < 8; ++q) {
-                    float4 v = __ldcg(reinterpret_cast<const float4*>(src) + q);
-                    acc32[4 * q] += v.x; acc32[4 * q + 1] += v.y;
-                    acc32[4 * q + 2] += v.z; acc32[4 * q + 3] += v.w;
-                  }
-                } else {
+                for (int q = 0; q < 8; ++q) {
+                  v0[q] = __ldcg(ws4 + ws_off(sb, c * 8 + q));
+                  v1[q] = two ? __ldcg(ws4 + ws_off(sb + 1, c * 8 + q)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
 #pragma unroll
-                  for (int j = 0; j < 32; ++j)
-                    if (col0 + j < a.n) acc32[j] += __ldcg(src + j);
+                for (int q = 0; q < 8; ++q) {
+                  acc32[4 * q] += v0[q].x; acc32[4 * q + 1] += v0[q].y; acc32[4 * q + 2] += v0[q].z; acc32[4 * q + 3] += v0[q].w;
+                }
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  acc32[4 * q] += v1[q].x; acc32[4 * q + 1] += v1[q].y; acc32[4 * q + 2] += v1[q].z; acc32[4 * q + 3] += v1[q].w;
                 }
               }
               if (a.bias != nullptr) {
@@ -1214,6 +1257,8 @@ void effective_choice(int64_t m, int64_t n, int64_t k, int* bn, int* split) {
   if ((*bn == 1024 || *bn == 2048) && m > 256) *bn = 0;   // the swapped kernel only exists for m <= 256
 }
 
+constexpr bool kStreamKByDefault = true; // stream-K candidates of the tiled kernel for mid m
+constexpr int kStreamKMaxM = 1024;
 constexpr bool kSwapByDefault = true;    // swapped-operand kernel for small m
 constexpr int kSwapMaxM = 64;            // beyond that the X tile crowds W out of the ring
 constexpr bool kPairByDefault = true;    // consider two-CTA tiles
@@ -1311,8 +1356,9 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
   }
   const int64_t m_tiles = (m + BM - 1) / BM;
   auto tiles = [&](int bn) { return m_tiles * ((n + bn - 1) / bn); };
-  auto ws_ok = [&](int bn, int splits) {
-    return tiles(bn) <= kTileCounters && (int64_t)splits * m * n * 4 <= (int64_t)kSplitKWorkspaceBytes;
+  auto ws_ok = [&](int bn, int slots) {   // partial tiles: [n tile][slot][BN/4][m] float4
+    const int64_t n_pad = ((n + bn - 1) / bn) * bn;
+    return tiles(bn) <= kTileCounters && (int64_t)slots * m * n_pad * 4 <= (int64_t)kSplitKWorkspaceBytes;
   };
 
   constexpr double kClockGHz = 1.7, kHbmGBs = 6500.0, kItemFixedNs = 1500.0;
@@ -1348,7 +1394,7 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
       double cost = (double)rounds * (kb_per * (t_core > t_hbm ? t_core : t_hbm) + kItemFixedNs);
       // split-K tail: partial traffic, plus the last CTA summing chunk by chunk and split by
       // split, one L2 round trip (~0.7 us) each
-      if (s > 1) cost += 2.0 * s * (double)m * (double)n * 4.0 / kHbmGBs + 1500.0 + 700.0 * (bn / 32) * s;
+      if (s > 1) cost += 2.0 * s * (double)m * (double)n * 4.0 / kHbmGBs + 1500.0 + 700.0 * (bn / 32) * ((s + 1) / 2);
       if (cost < best * 0.999) {
         best = cost;
         best_bn = bn;
@@ -1356,8 +1402,57 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
       }
     }
   }
+  // Stream-K candidates (tile codes 4096 + BN): the (tile, k-block) units are dealt out in equal
+  // consecutive runs, one per CTA; tiles shared between CTAs are finished through the workspace.
+  struct SkPlan {
+    int per = 0, grid = 0, slots = 0;
+    double cost = 1e30;
+  };
+  auto sk_plan = [&](int bn) {
+    SkPlan q;
+    const int64_t n_tiles = (n + bn - 1) / bn;
+    const int64_t total = m_tiles * n_tiles * num_kb;
+    if (total >= 0x7fffffffLL) return q;
+    int64_t grid = total / 2 < sm_count ? total / 2 : sm_count;
+    if (grid < 1) grid = 1;
+    const int64_t per = (total + grid - 1) / grid;
+    grid = (total + per - 1) / per;
+    const int slots = (int)((num_kb - 1) / per) + 2;
+    if (!ws_ok(bn, slots)) return q;
+    const double smem_clk = (double)(BM * BK * 2 + bn * BK * 2) / 128.0, mma_clk = 2.0 * bn;
+    const double narrow = bn == 256 ? 1.0 : (bn == 128 ? 1.4 : 2.2);
+    const double t_core = narrow * (mma_clk > smem_clk ? mma_clk : smem_clk) / kClockGHz;
+    const double rows_x = (double)(m < BM ? m : BM);
+    const double am = (double)(m_tiles < kGroupM ? m_tiles : kGroupM);
+    const double an = (double)grid / am < 1.0 ? 1.0 : (double)grid / am;
+    const double t_hbm = 128.0 * (an * bn + am * rows_x) / kHbmGBs;
+    q.cost = (double)per * (t_core > t_hbm ? t_core : t_hbm) + 2.0 * kItemFixedNs;
+    if (per % num_kb != 0)
+      q.cost += 2.0 * (double)grid * BM * bn * 4.0 * 2.0 / kHbmGBs / 4.0 + 1500.0 + 700.0 * (bn / 32) * ((slots + 1) / 2);
+    q.per = (int)per;
+    q.grid = (int)grid;
+    q.slots = slots;
+    return q;
+  };
+  SkPlan sk;
+  int sk_bn = 0;
+  if (obn0 >= 4096) {
+    sk_bn = obn0 - 4096;
+    sk = sk_plan(sk_bn);
+    if (sk.per == 0) sk_bn = 0;   // does not fit the workspace: fall through to the fixed plan
+  } else if (obn0 == 0 && osp0 == 0 && kStreamKByDefault && m <= kStreamKMaxM) {
+    for (int bi = 0; bi < 3; ++bi) {
+      const SkPlan q = sk_plan(kBn[bi]);
+      if (q.per > 0 && q.cost < sk.cost * 0.999) {
+        sk = q;
+        sk_bn = kBn[bi];
+      }
+    }
+    if (!(sk.cost < best)) sk_bn = 0;
+    else best = sk.cost;
+  }
   int bn = best_bn, splits = best_splits;
-  const int obn = obn0, osp = osp0;
+  const int obn = obn0 >= 4096 ? 0 : obn0, osp = osp0;
   // The two-CTA kernel as one more candidate: 256 x 256 tiles on SM pairs.  Measured per
   // k-block it runs at about 0.9x the time of two single-CTA 128 x 256 tiles (1.40-1.50
   // PFLOP/s against 1.30-1.33 at m >= 4096), and its ring is deeper.
@@ -1376,11 +1471,20 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
   }
   if (obn == 512) pair = true;
   if (obn == 64 || obn == 128 || obn == 256) pair = false;
-  if (pair) {
+  if (pair && obn0 < 4096) {
     p.bn = 256;
     p.splits = 1;
     p.kb_per_split = num_kb;
     p.pair = true;
+    return p;
+  }
+  if (sk_bn > 0) {
+    p.bn = sk_bn;
+    p.splits = 1;
+    p.kb_per_split = num_kb;
+    p.sk_per = sk.per;
+    p.sk_grid = sk.grid;
+    p.slots_cap = sk.slots;
     return p;
   }
   if (obn == 64 || obn == 128 || obn == 256) {
@@ -1396,6 +1500,7 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
   p.bn = bn;
   p.splits = splits;
   p.kb_per_split = kb_per;
+  p.slots_cap = splits;
   return p;
 }
 
@@ -1412,7 +1517,8 @@ int launch_tc(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a, i
     attr_set[dev] = true;
   }
   const int total = a.m_tiles * a.n_tiles * a.splits;
-  const int grid = total < sm_count ? total : sm_count;
+  int grid = total < sm_count ? total : sm_count;
+  if (a.sk_per > 0) grid = (a.m_tiles * a.n_tiles * a.num_kb + a.sk_per - 1) / a.sk_per;
   gemm_f16_tcgen05_kernel<BN><<<grid, kGemmThreads, C::kSmemBytes, st>>>(tx, tw, a);
   return after_launch("gemm_f16_tcgen05_kernel");
 }
@@ -1520,7 +1626,7 @@ int launch_gemm(const void* x, const void* w, const void* bias, void* y, int64_t
                                                (__half*)y, (int)m, (int)n, (int)k, ldy);
     return after_launch("gemm_f16_simt_kernel");
   }
-  if (p.splits > 1) {
+  if (p.splits > 1 || p.sk_per > 0) {
     int rc = ensure_splitk_scratch(ctx);
     if (rc != DTAS_OK) return rc;
   }
@@ -1543,6 +1649,8 @@ int launch_gemm(const void* x, const void* w, const void* bias, void* y, int64_t
   a.m_tiles = (int)((m + BM - 1) / BM);
   a.n_tiles = (int)((n + p.bn - 1) / p.bn);
   a.splits = p.splits;
+  a.sk_per = p.swap_mn > 0 ? 0 : p.sk_per;
+  a.slots_cap = p.slots_cap > 0 ? p.slots_cap : p.splits;
   a.kb_per_split = p.kb_per_split;
   a.num_kb = (int)((k + BK - 1) / BK);
   a.vec_store = (aligned16(y) && (ldy % 8 == 0)) ? 1 : 0;
@@ -1594,6 +1702,10 @@ void gemm_variant_name(int64_t m, int64_t n, int64_t k, const DeviceCtx* ctx, ch
       snprintf(buf, len, "gemm_tcgen05_swap_n128_m%d_bk64_streamk%d", p.swap_mn, p.sk_grid);
     else
       snprintf(buf, len, "gemm_tcgen05_swap_n128_m%d_bk64_splitk%d", p.swap_mn, p.splits);
+    return;
+  }
+  if (p.sk_per > 0) {
+    snprintf(buf, len, "gemm_tcgen05_bm128_bn%d_bk64_streamk%d", p.bn, p.sk_grid);
     return;
   }
   const int stages = p.bn == 256 ? Cfg<256>::kStages : (p.bn == 128 ? Cfg<128>::kStages : Cfg<64>::kStages);
@@ -1675,7 +1787,7 @@ extern "C" int dtas_gemm_nt_static_scratch(const void* x, const void* w, const v
   splits = (num_kb + kb_per - 1) / kb_per;
   const int64_t m_tiles = (m + BM - 1) / BM, n_tiles = (n + p.bn - 1) / p.bn;
   if (splits > 1) {
-    const int64_t need = (int64_t)splits * m * n * 4;
+    const int64_t need = (int64_t)splits * m * (n_tiles * p.bn) * 4;   // partials cover whole column tiles
     if (need > (int64_t)kStaticPartialBytes)
       DTAS_FAIL(DTAS_EINVAL,
                 "gemm (static scratch): split_k=%d at m=%lld n=%lld needs %lld bytes of partial sums; the built-in "
@@ -1712,6 +1824,7 @@ extern "C" int dtas_gemm_nt_static_scratch(const void* x, const void* w, const v
   a.m_tiles = (int)m_tiles;
   a.n_tiles = (int)n_tiles;
   a.splits = splits;
+  a.slots_cap = splits;
   a.kb_per_split = kb_per;
   a.num_kb = num_kb;
   a.vec_store = (aligned16(y) && (ldy % 8 == 0)) ? 1 : 0;

@@ -106,8 +106,8 @@ int dtas_gemm_nt(const void* x, const void* w, const void* bias, void* y,
  * of the library image (8 MiB of fp32 partials + 1024 tile counters per GPU that loads the
  * library, held until the process exits) and calls no allocating routine at all.
  *   split_k     : K slices per output tile; 0 lets the planner choose.  The call is rejected with
- *                 DTAS_EINVAL when split_k * m * n * 4 bytes exceed 8 MiB or the output has more
- *                 than 1024 tiles; with one slice no scratch is used and any size is accepted.
+ *                 DTAS_EINVAL when split_k * m * n * 4 bytes (n rounded up to the tile width) exceed
+ *                 8 MiB or the output has more than 1024 tiles; with one slice no scratch is used and any size is accepted.
  *                 x and w must be 16-byte aligned and k a multiple of 8 (DTAS_EALIGN otherwise).
  *   status_word : optional device int32 that receives a non-zero code if a bounded wait inside
  *                 the kernel gives up; NULL keeps the code in the library's own scratch.
@@ -135,7 +135,8 @@ int dtas_variant_of(const char* op, int64_t m, int64_t n, int64_t k, int device,
 /* Overrides the GEMM dispatch for testing and offline re-tuning: block-tile
  * width bn in {64,128,256} (0 = automatic; 512 = the two-CTA kernel with 256 x 256 tiles;
  * 1024 = the swapped-operand kernel, which applies to m <= 256; 2048 = the same kernel with
- * stream-K work distribution, where split_k is ignored) and split-K factor (0 = automatic). */
+ * stream-K work distribution; 4096 + 64/128/256 = single-CTA tiles of that width with stream-K;
+ * split_k is ignored by the stream-K codes) and split-K factor (0 = automatic). */
 int dtas_gemm_set_override(int bn, int split_k);
 
 /* Measured dispatch table for the GEMM: for weight shape (n, k) and row counts m_lo..m_hi use

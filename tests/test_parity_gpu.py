@@ -256,7 +256,7 @@ def test_gemm_small_m_full_oracle(cuda_device):
 
 
 @pytest.mark.parametrize("bn,split", [(64, 1), (128, 1), (256, 1), (64, 4), (128, 3), (256, 2), (128, 16), (512, 1),
-                                      (1024, 1), (1024, 4), (1024, 7)])
+                                      (1024, 1), (1024, 4), (1024, 7), (2048, 0), (4160, 0), (4224, 0), (4352, 0)])
 def test_gemm_every_tile_width_and_split(cuda_device, bn, split):
     """Forces each kernel instantiation and split factor on ragged shapes (m, n, k not
     multiples of the tile), with a bias, writing into a column slab of a wider buffer."""
