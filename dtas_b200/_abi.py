@@ -51,6 +51,7 @@ PROTOTYPES = {
     "dtas_ew_set_override": (_i, [_i, _i, _i]),
     "dtas_row_set_override": (_i, [_i]),
     "dtas_gemv_set_override": (_i, [_i, _i]),
+    "dtas_set_pdl": (_i, [_i]),
     "dtas_last_error": (ctypes.c_char_p, []),
     "dtas_launch_count": (_i64, []),
     "dtas_poll_status": (_i, [_i]),

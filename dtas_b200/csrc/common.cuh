@@ -47,6 +47,42 @@ inline int after_launch(const char* what) {
   return DTAS_OK;
 }
 
+// ---- programmatic dependent launch ---------------------------------------------
+// Every kernel of the library is launched with the programmatic-stream-serialization attribute
+// and runs pdl_wait() before its first access to global memory.  The wait returns once the
+// kernel launched before it on the stream has finished and its writes are visible, so stream
+// order is what the caller sees; what comes before the wait (barrier and tensor-memory set-up,
+// descriptor prefetch, index arithmetic) overlaps the tail of the previous kernel.
+// pdl_launch_dependents() right after the wait lets the next kernel start its own preamble.
+// A kernel that has no predecessor, or whose predecessor is not a kernel, passes the wait at
+// once.  DTAS_B200_PDL=0 in the environment launches without the attribute.
+bool pdl_enabled();
+int pdl_mode();
+int set_pdl_mode(int mode);
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 // ---- per-device context ------------------------------------------------------
 struct DeviceCtx {
   bool ready = false;

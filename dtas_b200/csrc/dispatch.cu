@@ -8,6 +8,7 @@
 // launch.  The bucket -> kernel-variant tables live next to the kernels they select
 // (ew_cfg, row_cfg, pick_wpr, plan_gemm).
 #include <mutex>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -15,6 +16,24 @@ namespace dtas {
 
 static thread_local char tl_error[512] = {0};
 std::atomic<int64_t> g_launches{0};
+
+// 0 = plain launches, 1 = programmatic dependent launch.  Initialised from DTAS_B200_PDL (default 1).
+static std::atomic<int> g_pdl_mode{-1};
+int pdl_mode() {
+  int m = g_pdl_mode.load(std::memory_order_relaxed);
+  if (m < 0) {
+    const char* e = getenv("DTAS_B200_PDL");
+    m = (e && e[0] == '0') ? 0 : 1;
+    g_pdl_mode.store(m, std::memory_order_relaxed);
+  }
+  return m;
+}
+bool pdl_enabled() { return pdl_mode() != 0; }
+int set_pdl_mode(int mode) {
+  const int prev = pdl_mode();
+  g_pdl_mode.store(mode, std::memory_order_relaxed);
+  return prev;
+}
 
 void set_error(const char* fmt, ...) {
   va_list ap;
@@ -259,6 +278,11 @@ int dtas_gemv_set_override(int warps_per_row, int unroll) {
 }
 
 const char* dtas_last_error(void) { return tl_error; }
+
+int dtas_set_pdl(int mode) {
+  if (mode < 0 || mode > 1) DTAS_FAIL(-1, "dtas_set_pdl: mode %d is not 0 or 1", mode);
+  return set_pdl_mode(mode);
+}
 
 int64_t dtas_launch_count(void) { return g_launches.load(); }
 

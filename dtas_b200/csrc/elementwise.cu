@@ -180,6 +180,8 @@ template <typename Op, int UNROLL, bool HINT>
 __global__ void __launch_bounds__(kThreads) ew_vec_kernel(const Op op, int64_t n_vec,
                                                           int64_t n_elem) {
   constexpr int64_t kTile = (int64_t)kThreads * UNROLL;
+  pdl_wait();
+  pdl_launch_dependents();
   for (int64_t base = (int64_t)blockIdx.x * kTile; base < n_vec;
        base += (int64_t)gridDim.x * kTile) {
     typename Op::Reg r[UNROLL];
@@ -203,6 +205,8 @@ __global__ void __launch_bounds__(kThreads) ew_vec_kernel(const Op op, int64_t n
 // Scalar path for buffers that are not 16-byte aligned.
 template <typename Op>
 __global__ void __launch_bounds__(kThreads) ew_scalar_kernel(const Op op, int64_t n_elem) {
+  pdl_wait();
+  pdl_launch_dependents();
   for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n_elem;
        i += (int64_t)gridDim.x * kThreads)
     op.scalar(i);
@@ -238,9 +242,9 @@ inline EwCfg ew_cfg(int bucket, int loads_per_vec) {
 template <typename Op, int UNROLL>
 void launch_vec(const Op& op, int64_t n_vec, int64_t n_elem, unsigned blocks, bool hints, cudaStream_t st) {
   if (hints)
-    ew_vec_kernel<Op, UNROLL, true><<<blocks, kThreads, 0, st>>>(op, n_vec, n_elem);
+    launch_kernel(ew_vec_kernel<Op, UNROLL, true>, blocks, kThreads, 0, st, op, n_vec, n_elem);
   else
-    ew_vec_kernel<Op, UNROLL, false><<<blocks, kThreads, 0, st>>>(op, n_vec, n_elem);
+    launch_kernel(ew_vec_kernel<Op, UNROLL, false>, blocks, kThreads, 0, st, op, n_vec, n_elem);
 }
 
 template <typename Op>
@@ -249,7 +253,7 @@ int launch_ew(const Op& op, int64_t n_elem, bool aligned, const DeviceCtx* ctx, 
   if (!aligned) {
     int64_t blocks = (n_elem + kThreads - 1) / kThreads;
     int64_t cap = (int64_t)ctx->sm_count * 8;
-    ew_scalar_kernel<Op><<<(unsigned)(blocks < cap ? blocks : cap), kThreads, 0, st>>>(op, n_elem);
+    launch_kernel(ew_scalar_kernel<Op>, (unsigned)(blocks < cap ? blocks : cap), kThreads, 0, st, op, n_elem);
     return after_launch(name);
   }
   const int64_t n_vec = n_elem / Op::kVec;

@@ -318,6 +318,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  pdl_wait();                 // the previous kernel on the stream is complete from here on
+  pdl_launch_dependents();    // the next one may run its own set-up while this one works
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -672,6 +674,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  pdl_wait();                 // the previous kernel on the stream is complete from here on
+  pdl_launch_dependents();    // the next one may run its own set-up while this one works
 
   if (warp == 0) {
     if (lane == 0) {
@@ -997,6 +1001,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   cluster_sync_all();      // barriers of both CTAs are initialised before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  pdl_wait();                 // the previous kernel on the stream is complete from here on
+  pdl_launch_dependents();    // the next one may run its own set-up while this one works
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -1134,6 +1140,8 @@ __global__ void __launch_bounds__(256)
                          int k, int64_t ldy) {
   const int col = blockIdx.x * 16 + (threadIdx.x & 15);
   const int row = blockIdx.y * 16 + (threadIdx.x >> 4);
+  pdl_wait();
+  pdl_launch_dependents();
   if (row >= m || col >= n) return;
   const __half* xr = x + (int64_t)row * k;
   const __half* wr = w + (int64_t)col * k;
@@ -1519,7 +1527,7 @@ int launch_tc(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a, i
   const int total = a.m_tiles * a.n_tiles * a.splits;
   int grid = total < sm_count ? total : sm_count;
   if (a.sk_per > 0) grid = (a.m_tiles * a.n_tiles * a.num_kb + a.sk_per - 1) / a.sk_per;
-  gemm_f16_tcgen05_kernel<BN><<<grid, kGemmThreads, C::kSmemBytes, st>>>(tx, tw, a);
+  launch_kernel(gemm_f16_tcgen05_kernel<BN>, grid, kGemmThreads, C::kSmemBytes, st, tx, tw, a);
   return after_launch("gemm_f16_tcgen05_kernel");
 }
 
@@ -1554,7 +1562,7 @@ int launch_pair(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a,
   const int total = a.m_tiles * a.n_tiles;
   int pairs = dev < 64 ? max_pairs[dev] : sm_count / 2;
   if (pairs > total) pairs = total;
-  gemm_f16_tcgen05_pair_kernel<<<2 * pairs, kGemmThreads, kPairSmemBytes, st>>>(tx, tw, a);
+  launch_kernel(gemm_f16_tcgen05_pair_kernel, 2 * pairs, kGemmThreads, kPairSmemBytes, st, tx, tw, a);
   return after_launch("gemm_f16_tcgen05_pair_kernel");
 }
 
@@ -1572,7 +1580,7 @@ int launch_swap(const CUtensorMap& tw, const CUtensorMap& tx, const GemmArgs& a,
   const int total = a.n_tiles * a.splits;
   int grid = total < sm_count ? total : sm_count;
   if (a.sk_per > 0) grid = (a.n_tiles * a.num_kb + a.sk_per - 1) / a.sk_per;
-  gemm_f16_tcgen05_swap_kernel<MN><<<grid, kGemmThreads, C::kSmemBytes, st>>>(tw, tx, a);
+  launch_kernel(gemm_f16_tcgen05_swap_kernel<MN>, grid, kGemmThreads, C::kSmemBytes, st, tw, tx, a);
   return after_launch("gemm_f16_tcgen05_swap_kernel");
 }
 
@@ -1622,8 +1630,8 @@ int launch_gemm(const void* x, const void* w, const void* bias, void* y, int64_t
   if (p.simt) {
     dim3 grid((unsigned)((n + 15) / 16), (unsigned)((m + 15) / 16));
     if (grid.y > 65535) DTAS_FAIL(DTAS_EUNSUPPORTED, "gemm: unaligned operands with m > 1048560");
-    gemm_f16_simt_kernel<<<grid, 256, 0, st>>>((const __half*)x, (const __half*)w, (const __half*)bias,
-                                               (__half*)y, (int)m, (int)n, (int)k, ldy);
+    launch_kernel(gemm_f16_simt_kernel, grid, 256, 0, st, (const __half*)x, (const __half*)w,
+                  (const __half*)bias, (__half*)y, (int)m, (int)n, (int)k, ldy);
     return after_launch("gemm_f16_simt_kernel");
   }
   if (p.splits > 1 || p.sk_per > 0) {

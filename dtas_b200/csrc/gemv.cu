@@ -56,6 +56,8 @@ __global__ void __launch_bounds__(kThreads)
 #pragma unroll
   for (int u = 0; u < UNROLL; ++u) acc[u] = 0.f;
 
+  pdl_wait();
+  pdl_launch_dependents();
   if (live) {
     int c = c0 + lane;
     // Full steps: UNROLL independent 16-byte loads of W per lane before any use.
@@ -100,6 +102,8 @@ __global__ void __launch_bounds__(kThreads)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * kWarps + warp;
   float s = 0.f;
+  pdl_wait();
+  pdl_launch_dependents();
   if (row < n) {
     const __half* wr = w + (int64_t)row * k;
     for (int i = lane; i < k; i += 32) s = fmaf(__half2float(wr[i]), __half2float(x[i]), s);
@@ -155,7 +159,7 @@ int launch_gemv(const void* x, const void* w, const void* bias, void* y, int64_t
   const bool vec_ok = (k % 8 == 0) && aligned16(x) && aligned16(w);
   if (!vec_ok) {
     const unsigned grid = (unsigned)((n + kWarps - 1) / kWarps);
-    gemv_f16_scalar_kernel<<<grid, kThreads, 0, st>>>(xp, wp, bp, yp, (int)n, (int)k);
+    launch_kernel(gemv_f16_scalar_kernel, grid, kThreads, 0, st, xp, wp, bp, yp, (int)n, (int)k);
     return after_launch("gemv_f16_scalar_kernel");
   }
   const int wpr = pick_wpr(n, k, ctx->sm_count);
@@ -164,7 +168,7 @@ int launch_gemv(const void* x, const void* w, const void* bias, void* y, int64_t
   const int unroll = pick_unroll(wpr);
 #define DTAS_GEMV_CASE(W, U)                                                                  \
   if (wpr == W && unroll == U) {                                                              \
-    gemv_f16_kernel<W, U><<<grid, kThreads, 0, st>>>(xp, wp, bp, yp, (int)n, (int)k);         \
+    launch_kernel(gemv_f16_kernel<W, U>, grid, kThreads, 0, st, xp, wp, bp, yp, (int)n, (int)k); \
     return after_launch("gemv_f16_kernel");                                                   \
   }
   DTAS_GEMV_CASE(1, 4) DTAS_GEMV_CASE(1, 8) DTAS_GEMV_CASE(2, 4) DTAS_GEMV_CASE(2, 8)

@@ -130,6 +130,8 @@ __global__ void __launch_bounds__(TPR > kCtaThreads ? TPR : kCtaThreads)
   const InT* xr = x + (live ? row : 0) * (int64_t)n_cols;
   __half* yr = y + (live ? row : 0) * (int64_t)n_cols;
 
+  pdl_wait();
+  pdl_launch_dependents();
   RawChunk<InT> raw[MAXCH];
 #pragma unroll
   for (int c = 0; c < MAXCH; ++c) {
@@ -280,6 +282,8 @@ __global__ void __launch_bounds__(kCtaThreads)
                        const void* __restrict__ p1, __half* __restrict__ y, int64_t m,
                        int64_t n_cols, float eps) {
   __shared__ float scratch[kCtaThreads / 32];
+  pdl_wait();
+  pdl_launch_dependents();
   for (int64_t row = blockIdx.x; row < m; row += gridDim.x) {
     const InT* xr = x + row * n_cols;
     __half* yr = y + row * n_cols;
@@ -385,7 +389,7 @@ int launch_regs(const InT* x, const void* p0, const void* p1, __half* y, int64_t
   constexpr int kRowsPerCta = kThreads / TPR;
   const int64_t grid = (m + kRowsPerCta - 1) / kRowsPerCta;
   if (grid > 0x7fffffffLL) DTAS_FAIL(DTAS_EINVAL, "row op: too many rows (%lld)", (long long)m);
-  row_regs_kernel<OP, InT, TPR, MAXCH><<<(unsigned)grid, kThreads, 0, st>>>(x, p0, p1, y, m, n_cols, eps);
+  launch_kernel(row_regs_kernel<OP, InT, TPR, MAXCH>, (unsigned)grid, kThreads, 0, st, x, p0, p1, y, m, n_cols, eps);
   return after_launch("row_regs_kernel");
 }
 
@@ -408,7 +412,7 @@ int launch_typed(const RowCfg& c, const InT* x, const void* p0, const void* p1, 
                  int64_t m, int64_t n_cols, float eps, const DeviceCtx* ctx, cudaStream_t st) {
   if (c.generic) {
     int64_t grid = m < (int64_t)ctx->sm_count * 8 ? m : (int64_t)ctx->sm_count * 8;
-    row_generic_kernel<OP, InT><<<(unsigned)grid, kCtaThreads, 0, st>>>(x, p0, p1, y, m, n_cols, eps);
+    launch_kernel(row_generic_kernel<OP, InT>, (unsigned)grid, kCtaThreads, 0, st, x, p0, p1, y, m, n_cols, eps);
     return after_launch("row_generic_kernel");
   }
   switch (c.maxch) {

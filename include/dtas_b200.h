@@ -159,6 +159,16 @@ int dtas_ew_set_override(int unroll, int ctas_per_sm, int stream_hints);
 int dtas_row_set_override(int threads_per_row);
 int dtas_gemv_set_override(int warps_per_row, int unroll);
 
+/* Launch mode of every kernel of the library.  No counterpart in the reference.
+ *   1 (default): programmatic dependent launch - a kernel may be scheduled, and run the set-up it
+ *      does before touching global memory, while the kernel before it on the stream drains; it
+ *      waits for that kernel's results before its first global access, so callers see plain
+ *      stream order;
+ *   0: plain launches.
+ * The initial mode comes from the environment variable DTAS_B200_PDL (0 or 1).  Returns the
+ * previous mode, or -1 for any other value.                                                  */
+int dtas_set_pdl(int mode);
+
 /* ---- bookkeeping ---------------------------------------------------------
  * dtas_last_error : message of the last failing call on this thread ("" if none).
  * dtas_launch_count: kernels launched by this library since load (all threads).
