@@ -53,6 +53,23 @@ constexpr int kEpilogueThreads = 128;
 constexpr int kStageBudget = 192 * 1024;   // bytes of operand ring per CTA
 constexpr int kGroupM = 16;     // m-tiles per rasterisation band
 
+// Optional timeline of one launch (compile with -DDTAS_TRACE; not part of the shipped build):
+// each CTA stamps its SM clock at a few milestones into a device array that
+// dtas_trace_read() copies out.  Slots 14 / 15 hold the global timer at entry / exit.
+#ifdef DTAS_TRACE
+__device__ unsigned long long g_trace[1024][16];
+#define DTAS_TRACE_AT(slot) do { g_trace[blockIdx.x & 1023][slot] = (unsigned long long)clock64(); } while (0)
+#define DTAS_TRACE_G(slot)                                              \
+  do {                                                                  \
+    unsigned long long t_;                                              \
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));              \
+    g_trace[blockIdx.x & 1023][slot] = t_;                              \
+  } while (0)
+#else
+#define DTAS_TRACE_AT(slot) do { } while (0)
+#define DTAS_TRACE_G(slot) do { } while (0)
+#endif
+
 constexpr int ERR_PRODUCER = 0x101, ERR_MMA_FULL = 0x102, ERR_MMA_TMEM = 0x103, ERR_EPILOGUE = 0x104;
 
 // ---------------------------------------------------------------------------------------
@@ -171,6 +188,36 @@ __device__ __forceinline__ void tmem_ld_wait() {
 }
 __device__ __forceinline__ void epilogue_bar_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
+}
+
+// Finishes 32 consecutive output columns of one row: bias, round to fp16, store.
+__device__ __forceinline__ void store_row32(__half* yrow, int col0, int n, const __half* bias, int vec_store,
+                                            float* acc32) {
+  if (bias != nullptr) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < n) acc32[j] += __half2float(bias[col0 + j]);
+  }
+  if (vec_store && col0 + 32 <= n) {
+    uint4* dst = reinterpret_cast<uint4*>(yrow + col0);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint4 v;
+      __half2 h0 = __floats2half2_rn(acc32[8 * q + 0], acc32[8 * q + 1]);
+      __half2 h1 = __floats2half2_rn(acc32[8 * q + 2], acc32[8 * q + 3]);
+      __half2 h2 = __floats2half2_rn(acc32[8 * q + 4], acc32[8 * q + 5]);
+      __half2 h3 = __floats2half2_rn(acc32[8 * q + 6], acc32[8 * q + 7]);
+      v.x = *reinterpret_cast<uint32_t*>(&h0);
+      v.y = *reinterpret_cast<uint32_t*>(&h1);
+      v.z = *reinterpret_cast<uint32_t*>(&h2);
+      v.w = *reinterpret_cast<uint32_t*>(&h3);
+      dst[q] = v;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < n) yrow[col0 + j] = __float2half_rn(acc32[j]);
+  }
 }
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 fp16)
@@ -297,8 +344,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   (void)last_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) { DTAS_TRACE_G(14); DTAS_TRACE_AT(0); }
 
   if (threadIdx.x == 0) {
+    // descriptor fetch overlaps the set-up below and the wait for the previous kernel
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_x)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w)) : "memory");
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -318,14 +369,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  if (threadIdx.x == 0) DTAS_TRACE_AT(1);
   pdl_wait();                 // the previous kernel on the stream is complete from here on
   pdl_launch_dependents();    // the next one may run its own set-up while this one works
+  if (threadIdx.x == 0) DTAS_TRACE_AT(2);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_x)) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w)) : "memory");
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -340,9 +391,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           const uint32_t sa = base + stage * C::kStageBytes;
           tma_load_2d(sa, &tmap_x, kb * BK, mt * BM, full_bar(stage));
           tma_load_2d(sa + C::kABytes, &tmap_w, kb * BK, nt * BN, full_bar(stage));
+          if (kb == sg.kb0) DTAS_TRACE_AT(3);
           if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
         }
       }
+      DTAS_TRACE_AT(4);
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -366,6 +419,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, a.status, ERR_MMA_FULL)) { ok = false; break; }
           tc_fence_after();
+          if (kb == kb0) DTAS_TRACE_AT(5);
           const uint32_t sa = base + stage * C::kStageBytes;
           const uint64_t da = make_kmajor_sw128_desc(sa);
           const uint64_t db = make_kmajor_sw128_desc(sa + C::kABytes);
@@ -378,6 +432,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
         }
         if (ok) umma_commit(tfull_bar(acc));  // accumulator complete
+        DTAS_TRACE_AT(6);
       }
     }
     __syncwarp();
@@ -396,6 +451,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
       if (!mbar_wait(tfull_bar(acc), acc_phase, a.status, ERR_EPILOGUE)) { ok = false; break; }
       tc_fence_after();
+      if (epi_tid == 0) DTAS_TRACE_AT(7);
       const int row = mt * BM + quarter * 32 + lane;
       const bool row_ok = row < a.m;
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
@@ -465,6 +521,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
         __threadfence();
         epilogue_bar_sync();
+        if (epi_tid == 0) DTAS_TRACE_AT(8);
         if (epi_tid == 0) {
           const int old = atomicAdd(&a.counters[sg.tile], 1);
           const uint32_t last = (old == n_parts - 1) ? 1u : 0u;
@@ -474,62 +531,45 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         epilogue_bar_sync();
         const bool is_last = *last_flag_ptr != 0;
         epilogue_bar_sync();                 // flag consumed before a later tile rewrites it
+        if (epi_tid == 0) DTAS_TRACE_AT(9);
         if (is_last) {
           __threadfence();
           if (row_ok) {
             __half* yrow = a.y + (int64_t)row * a.ldy;
+            // 64 columns and two slots per batch: 32 independent 16-byte loads in flight per
+            // thread, one L2 round trip per 64 columns and slot pair; slots are added in slot
+            // order = K order, whatever the arrival order
+            constexpr int W = 64;
+            const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-              const int col0 = col_base + c * 32;
+            for (int c = 0; c < BN / W; ++c) {
+              const int col0 = col_base + c * W;
               if (col0 >= a.n) break;
-              float acc32[32];
+              const int live4 = min(W / 4, (a.n - col0 + 3) >> 2);   // column groups holding data
+              float acc[W];
 #pragma unroll
-              for (int j = 0; j < 32; ++j) acc32[j] = 0.f;
-              // two slots per batch: 16 independent 16-byte loads in flight; slots are added in
-              // slot order = K order, whatever the arrival order
+              for (int j = 0; j < W; ++j) acc[j] = 0.f;
 #pragma unroll 1
               for (int sb = 0; sb < n_parts; sb += 2) {
-                float4 v0[8], v1[8];
+                float4 v0[W / 4], v1[W / 4];
                 const bool two = sb + 1 < n_parts;
 #pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                  v0[q] = __ldcg(ws4 + ws_off(sb, c * 8 + q));
-                  v1[q] = two ? __ldcg(ws4 + ws_off(sb + 1, c * 8 + q)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int q = 0; q < W / 4; ++q) {
+                  const bool on = q < live4;
+                  v0[q] = on ? __ldcg(ws4 + ws_off(sb, c * (W / 4) + q)) : zero4;
+                  v1[q] = (on && two) ? __ldcg(ws4 + ws_off(sb + 1, c * (W / 4) + q)) : zero4;
                 }
 #pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                  acc32[4 * q] += v0[q].x; acc32[4 * q + 1] += v0[q].y; acc32[4 * q + 2] += v0[q].z; acc32[4 * q + 3] += v0[q].w;
+                for (int q = 0; q < W / 4; ++q) {
+                  acc[4 * q] += v0[q].x; acc[4 * q + 1] += v0[q].y; acc[4 * q + 2] += v0[q].z; acc[4 * q + 3] += v0[q].w;
                 }
 #pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                  acc32[4 * q] += v1[q].x; acc32[4 * q + 1] += v1[q].y; acc32[4 * q + 2] += v1[q].z; acc32[4 * q + 3] += v1[q].w;
+                for (int q = 0; q < W / 4; ++q) {
+                  acc[4 * q] += v1[q].x; acc[4 * q + 1] += v1[q].y; acc[4 * q + 2] += v1[q].z; acc[4 * q + 3] += v1[q].w;
                 }
               }
-              if (a.bias != nullptr) {
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  if (col0 + j < a.n) acc32[j] += __half2float(a.bias[col0 + j]);
-              }
-              if (a.vec_store && col0 + 32 <= a.n) {
-                uint4* dst = reinterpret_cast<uint4*>(yrow + col0);
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  uint4 v;
-                  __half2 h0 = __floats2half2_rn(acc32[8 * q + 0], acc32[8 * q + 1]);
-                  __half2 h1 = __floats2half2_rn(acc32[8 * q + 2], acc32[8 * q + 3]);
-                  __half2 h2 = __floats2half2_rn(acc32[8 * q + 4], acc32[8 * q + 5]);
-                  __half2 h3 = __floats2half2_rn(acc32[8 * q + 6], acc32[8 * q + 7]);
-                  v.x = *reinterpret_cast<uint32_t*>(&h0);
-                  v.y = *reinterpret_cast<uint32_t*>(&h1);
-                  v.z = *reinterpret_cast<uint32_t*>(&h2);
-                  v.w = *reinterpret_cast<uint32_t*>(&h3);
-                  dst[q] = v;
-                }
-              } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  if (col0 + j < a.n) yrow[col0 + j] = __float2half_rn(acc32[j]);
-              }
+              store_row32(yrow, col0, a.n, a.bias, a.vec_store, acc);
+              if (col0 + 32 < a.n) store_row32(yrow, col0 + 32, a.n, a.bias, a.vec_store, acc + 32);
             }
           }
         }
@@ -537,11 +577,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
   }
 
+  if (threadIdx.x == 64) DTAS_TRACE_AT(10);
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) DTAS_TRACE_AT(11);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);
+    if (lane == 0) { DTAS_TRACE_AT(12); DTAS_TRACE_G(15); }
   }
 }
 
@@ -653,8 +696,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   volatile uint32_t* last_flag_ptr = tmem_slot_ptr + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) { DTAS_TRACE_G(14); DTAS_TRACE_AT(0); }
 
   if (threadIdx.x == 0) {
+    // descriptor fetch overlaps the set-up below and the wait for the previous kernel
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_x)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w)) : "memory");
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -674,13 +721,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  if (threadIdx.x == 0) DTAS_TRACE_AT(1);
   pdl_wait();                 // the previous kernel on the stream is complete from here on
   pdl_launch_dependents();    // the next one may run its own set-up while this one works
+  if (threadIdx.x == 0) DTAS_TRACE_AT(2);
 
   if (warp == 0) {
     if (lane == 0) {
-      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w)) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_x)) : "memory");
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -695,9 +742,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           const uint32_t sa = base + stage * C::kStageBytes;
           tma_load_2d(sa, &tmap_w, kb * BK, nt * BM, full_bar(stage));
           tma_load_2d(sa + C::kWBytes, &tmap_x, kb * BK, 0, full_bar(stage));
+          if (kb == sg.kb0) DTAS_TRACE_AT(3);
           if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
         }
       }
+      DTAS_TRACE_AT(4);
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -720,6 +769,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, a.status, ERR_MMA_FULL)) { ok = false; break; }
           tc_fence_after();
+          if (kb == kb0) DTAS_TRACE_AT(5);
           const uint32_t sa = base + stage * C::kStageBytes;
           const uint64_t da = make_kmajor_sw128_desc(sa);                // W rows: the M side
           const uint64_t db = make_kmajor_sw128_desc(sa + C::kWBytes);   // X rows: the N side
@@ -730,6 +780,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
         }
         if (ok) umma_commit(tfull_bar(acc));
+        DTAS_TRACE_AT(6);
       }
     }
     __syncwarp();
@@ -748,6 +799,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
       if (!mbar_wait(tfull_bar(acc), acc_phase, a.status, ERR_EPILOGUE)) { ok = false; break; }
       tc_fence_after();
+      if (epi_tid == 0) DTAS_TRACE_AT(7);
       const int col = nt * BM + quarter * 32 + lane;        // output column owned by this thread
       const bool col_ok = col < a.n;
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * MN);
@@ -787,10 +839,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
           for (int q = 0; q < kChunk / 4; ++q) {
             const int g = c * (kChunk / 4) + q;
-            if (g < groups)
-              ws4[ws_off(sp, g)] =
-                  make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                              __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+            if (g < groups) {
+              const float4 v = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                           __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+              ws4[ws_off(sp, g)] = v;
+            }
           }
         }
         tc_fence_before();
@@ -799,6 +852,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
         __threadfence();
         epilogue_bar_sync();
+        if (epi_tid == 0) DTAS_TRACE_AT(8);
         if (epi_tid == 0) {
           const int old = atomicAdd(&a.counters[nt], 1);
           const uint32_t last = (old == n_parts - 1) ? 1u : 0u;
@@ -808,37 +862,48 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         epilogue_bar_sync();
         const bool is_last = *last_flag_ptr != 0;
         epilogue_bar_sync();
+        if (epi_tid == 0) DTAS_TRACE_AT(9);
         if (is_last) {
           __threadfence();
           const float bias = (a.bias != nullptr && col_ok) ? __half2float(a.bias[col]) : 0.f;
-          // two row groups per step, four slots per batch: up to 8 independent 16-byte loads in flight;
-          // slots are summed in slot order = K order, whatever the arrival order
+          // Up to eight row groups and four slots per batch: 16-32 independent 16-byte loads in
+          // flight per thread, so that a tile of up to 32 rows costs one L2 round trip per four
+          // slots.  Slots are summed in slot order = K order, whatever the arrival order.
+          constexpr int G = MN / 4 < 8 ? MN / 4 : 8;
+          const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 1
-          for (int g = 0; g < groups; g += 2) {
-            float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
-            const bool two = g + 1 < groups;
+          for (int g0 = 0; g0 < groups; g0 += G) {
+            float4 sum4[G];
+#pragma unroll
+            for (int j = 0; j < G; ++j) sum4[j] = zero4;
 #pragma unroll 1
             for (int sb = 0; sb < n_parts; sb += 4) {
-              float4 v0[4], v1[4];
+              float4 v[4][G];
 #pragma unroll
               for (int u = 0; u < 4; ++u) {
                 const bool on = sb + u < n_parts;
-                const int64_t off = ws_off(on ? sb + u : 0, g);
-                v0[u] = on ? __ldcg(ws4 + off) : make_float4(0.f, 0.f, 0.f, 0.f);
-                v1[u] = (on && two) ? __ldcg(ws4 + off + BM) : make_float4(0.f, 0.f, 0.f, 0.f);
+                const float4* src = ws4 + ws_off(on ? sb + u : 0, g0);
+#pragma unroll
+                for (int j = 0; j < G; ++j)
+                  v[u][j] = (on && g0 + j < groups) ? __ldcg(src + (int64_t)j * BM) : zero4;
               }
 #pragma unroll
               for (int u = 0; u < 4; ++u) {     // fixed split order: deterministic
-                s0.x += v0[u].x; s0.y += v0[u].y; s0.z += v0[u].z; s0.w += v0[u].w;
-                s1.x += v1[u].x; s1.y += v1[u].y; s1.z += v1[u].z; s1.w += v1[u].w;
+#pragma unroll
+                for (int j = 0; j < G; ++j) {
+                  sum4[j].x += v[u][j].x; sum4[j].y += v[u][j].y; sum4[j].z += v[u][j].z; sum4[j].w += v[u][j].w;
+                }
               }
             }
             if (col_ok) {
-              const float o[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const int row = g * 4 + j;
-                if (row < a.m) a.y[(int64_t)row * a.ldy + col] = __float2half_rn(o[j] + bias);
+              for (int j = 0; j < G; ++j) {
+                const float o[4] = {sum4[j].x, sum4[j].y, sum4[j].z, sum4[j].w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const int row = (g0 + j) * 4 + i;
+                  if (row < a.m) a.y[(int64_t)row * a.ldy + col] = __float2half_rn(o[i] + bias);
+                }
               }
             }
           }
@@ -847,11 +912,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
   }
 
+  if (threadIdx.x == 64) DTAS_TRACE_AT(10);
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) DTAS_TRACE_AT(11);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);
+    if (lane == 0) { DTAS_TRACE_AT(12); DTAS_TRACE_G(15); }
   }
 }
 
@@ -982,6 +1050,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   constexpr uint32_t kPeerMask = 0xFEFFFFFFu;       // clears the CTA-rank bit of a shared::cluster address
 
   if (threadIdx.x == 0) {
+    // descriptor fetch overlaps the set-up below and the wait for the previous kernel
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_x)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w)) : "memory");
     for (int s = 0; s < kPairStages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -1007,8 +1078,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
-      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_x)) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w)) : "memory");
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -1842,3 +1911,11 @@ extern "C" int dtas_gemm_nt_static_scratch(const void* x, const void* w, const v
     default: return launch_tc<64>(tx, tw, a, sd->sm_count, st);
   }
 }
+
+#ifdef DTAS_TRACE
+// Trace build only: copies the per-CTA timeline of the last GEMM launch (1024 x 16 x u64) to `dst`.
+extern "C" int dtas_trace_read(void* dst) {
+  cudaError_t e = cudaMemcpyFromSymbol(dst, dtas::g_trace, sizeof(unsigned long long) * 1024 * 16);
+  return e == cudaSuccess ? DTAS_OK : DTAS_ECUDA;
+}
+#endif
