@@ -245,6 +245,48 @@ def point_runner(op, m, n, k, dev):
     return (lambda i: ops.gemm_nt(x, ws[i % copies], y)), copies
 
 
+POINT_IDLE_S = 0.2   # idle time before each per-point measurement
+
+
+def fused_points(dev, peaks):
+    """The fused matmul forms of the reference's model workloads at their own sizes (dolly-v2-3b:
+    hidden 2560, FFN 10240): device time of the fused call, and of the same result from the plain
+    GEMM followed by separate add kernels.  Not part of the step; reported beside it."""
+    import torch
+    from dtas_b200 import ops
+    from dtas_b200.profiling import rotation_for, time_op
+    f16 = dict(dtype=torch.float16, device=dev)
+    out = []
+    for m in (16, 1024, 4096):
+        for label, n, k, n_res, act in (("gemm+bias+res+res", 2560, 2560, 2, None), ("gemm+bias+gelu", 10240, 2560, 0, "gelu")):
+            nbytes = 2 * (m * k + n * k + m * n) + 2 * n + 2 * n_res * m * n
+            flops = 2 * m * n * k
+            copies = rotation_for(nbytes, max_copies=16)
+            ws = [torch.randn(n, k, **f16) * 0.02 for _ in range(copies)]
+            x, b, y, tmp = torch.randn(m, k, **f16), torch.randn(n, **f16), torch.empty(m, n, **f16), torch.empty(m, n, **f16)
+            res = [torch.randn(m, n, **f16) for _ in range(n_res)] + [None, None]
+
+            def fused(i):
+                ops.gemm_nt(x, ws[i % copies], y, bias=b, res1=res[0], res2=res[1], act=act)
+
+            def unfused(i):
+                ops.gemm_nt(x, ws[i % copies], y, bias=b)
+                if n_res:
+                    ops.add(res[0], y, tmp)
+                    ops.add(tmp, res[1], y)
+
+            torch.cuda.synchronize()
+            time.sleep(POINT_IDLE_S)
+            tf = time_op(fused, warmup=3, number=3, min_repeat_ms=10.0, graph=True)["mean_us"]
+            tu = time_op(unfused, warmup=3, number=3, min_repeat_ms=10.0, graph=True)["mean_us"]
+            ideal_us = max(nbytes / (peaks["hbm_gbs"] * 1e3), flops / (peaks["bf16_tflops"] * 1e6))
+            out.append({"op": label, "m": m, "n": n, "k": k, "us": round(tf, 2),
+                        "us_unfused" if n_res else "us_plain_gemm": round(tu, 2), "frac": round(ideal_us / tf, 3)})
+            del ws
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
@@ -367,6 +409,10 @@ def run_gpu(args):
             if m_local == 0 or n_local == 0:
                 continue
             fn, copies = point_runner(op, m_local, n_local, k, dev)
+            # A point is timed on its own: after the m = 8192 GEMMs the SM clock stays under the power
+            # cap for a while, which reads as +10-25 % on the small points that follow them.
+            torch.cuda.synchronize()
+            time.sleep(POINT_IDLE_S)
             t = time_op(fn, warmup=3, number=3, min_repeat_ms=10.0, graph=True)
             del fn
             ns, bound = roofline_ns(op, m_local, n_local, k, peaks)
@@ -379,6 +425,7 @@ def run_gpu(args):
             if op == "gemm" and (dominant is None or t["mean_us"] > dominant[1]["mean_us"]):
                 dominant = ((op, m_local, n_local, k), t)
         torch.cuda.empty_cache()
+    fused = fused_points(dev, peaks) if (per_point and world == 1) else None
     roofline = None
     if dominant is not None:
         (op, m, n, k), t = dominant
@@ -417,6 +464,7 @@ def run_gpu(args):
             "clocks": clocks,
             "mean_point_frac": mean_frac,
             "points": per_point,
+            "fused_points": fused,
         }
         print(json.dumps(line))
     if world > 1:

@@ -14,6 +14,7 @@ from .build import LIB_PATH
 
 OK, EINVAL, EALIGN, ECUDA, ETIMEOUT, EUNSUPPORTED = 0, 1, 2, 3, 4, 5
 F16, F32, I8 = 0, 1, 2
+ACT_NONE, ACT_GELU = 0, 1
 
 _ERR_NAMES = {
     EINVAL: "DTAS_EINVAL", EALIGN: "DTAS_EALIGN", ECUDA: "DTAS_ECUDA",
@@ -41,6 +42,8 @@ PROTOTYPES = {
     "dtas_layer_norm": (_i, [_p, _p, _p, _p, _i64, _i64, _f, _i, _i, _p]),
     "dtas_gemv": (_i, [_p, _p, _p, _p, _i64, _i64, _i, _i, _p]),
     "dtas_gemm_nt": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _i, _p]),
+    "dtas_gemm_nt_fused": (_i, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _p]),
+    "dtas_gemv_fused": (_i, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i, _i, _i, _i, _p]),
     "dtas_gemm_nt_static_scratch": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _i, _i, _p, _p]),
     "dtas_bucket_of": (_i, [ctypes.c_char_p, _i64]),
     "dtas_bucket_count": (_i, [ctypes.c_char_p]),

@@ -59,7 +59,7 @@ class PackedOp:
     def __call__(self, *args):
         s = self.spec
         n_in = {"cast": 1, "copy": 1, "softmax": 1, "add": 2, "rms_norm": 2, "layer_norm": 3,
-                "gemv": 2 + int(s.bias), "gemm": 2 + int(s.bias)}[s.op]
+                "gemv": 2 + int(s.bias) + s.residuals, "gemm": 2 + int(s.bias) + s.residuals}[s.op]
         if len(args) != n_in + 1:
             raise _abi.DtasError(_abi.EINVAL, f"{self.name}: expected {n_in} input(s) and 1 output, got {len(args)} tensors")
         out = args[-1]
@@ -82,10 +82,14 @@ class PackedOp:
             self._expect(args[0], "float16", s.k, "x")
             if tuple(args[1].shape) != (s.cols, s.k):
                 raise _abi.DtasError(_abi.EINVAL, f"{self.name}: weight must be [{s.cols}, {s.k}], got {tuple(args[1].shape)}")
+            # argument order of the reference's fused functions: x, W, bias, residuals..., out
+            # (experiment/ModelIR/dolly-v2-3b-q0f16/before_dl.py:163)
             bias = args[2] if s.bias else None
-            if s.op == "gemv":
-                return ops.gemv(args[0], args[1], out, bias=bias)
-            return ops.gemm_nt(args[0], args[1], out, bias=bias)
+            res = list(args[2 + int(s.bias):-1]) + [None, None]
+            if out.dtype != torch_dtype(s.out_dtype):
+                raise _abi.DtasError(_abi.EINVAL, f"{self.name}: output must be {s.out_dtype}, got {out.dtype}")
+            fn = ops.gemv if s.op == "gemv" else ops.gemm_nt
+            return fn(args[0], args[1], out, bias=bias, res1=res[0], res2=res[1], act=s.act or None)
         raise _abi.DtasError(_abi.EUNSUPPORTED, f"{self.name}: unknown op {s.op}")
 
 

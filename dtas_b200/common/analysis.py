@@ -156,10 +156,26 @@ def spec_from_prim_func(func, name):
                         raise UnsupportedWorkload(f"{name}: only the NT layout X[m,K].W[N,K]^T is supported")
                     rows = [_static(d) for d in ins[0].shape[:-1]]
                     dynamic = any(d is None for d in rows)
-                    bias = len(ins) >= 3
+                    # what follows the weight: an optional bias [N], then residuals shaped like the output
+                    # (fused_NT_matmul2_add1_add3_add3, experiment/ModelIR/dolly-v2-3b-q0f16/before_dl.py:163)
+                    extra = list(ins[2:])
+                    bias = bool(extra) and len(extra[0].shape) == 1
+                    if bias and _static(extra[0].shape[0]) != n:
+                        raise UnsupportedWorkload(f"{name}: bias must have N = {n} elements")
+                    res = extra[1:] if bias else extra
+                    if len(res) > 2 or any(len(r.shape) != len(out.shape) or _static(r.shape[-1]) != n for r in res):
+                        raise UnsupportedWorkload(f"{name}: at most two residuals shaped like the output are supported")
+                    calls, _ = _calls_and_ops(func.body)
+                    act = "gelu" if any("erf" in c for c in calls) else ""
+                    unknown = [c for c in calls if not any(t in c for t in ("erf", "if_then_else", "likely"))]
+                    if unknown:
+                        raise UnsupportedWorkload(f"{name}: matmul tail calls {sorted(unknown)} have no fused kernel")
+                    if str(out.dtype) not in ("float16", "float32"):
+                        raise UnsupportedWorkload(f"{name}: output dtype {out.dtype}")
+                    kw = dict(cols=n, k=k, bias=bias, residuals=len(res), act=act)
                     if not dynamic and all(d == 1 for d in rows):
-                        return OpSpec(name, "gemv", "float16", "float16", cols=n, k=k, bias=bias, upper=1)
-                    return OpSpec(name, "gemm", "float16", "float16", cols=n, k=k, bias=bias, upper=upper)
+                        return OpSpec(name, "gemv", "float16", str(out.dtype), upper=1, **kw)
+                    return OpSpec(name, "gemm", "float16", str(out.dtype), upper=upper, **kw)
     # general reduction over the last dim
     calls, nodes = _calls_and_ops(func.body)
     h = last_dim(ins[0])

@@ -10,6 +10,7 @@
 #include <atomic>
 
 #include "../../include/dtas_b200.h"
+#include "epilogue.cuh"
 
 namespace dtas {
 
@@ -146,12 +147,12 @@ int launch_row_op(RowOp op, const void* x, const void* p0, const void* p1, void*
 void row_variant_name(RowOp op, int64_t m, int64_t n_cols, char* buf, int len);
 void row_set_override(int tpr);
 
-int launch_gemv(const void* x, const void* w, const void* bias, void* y, int64_t n, int64_t k,
+int launch_gemv(const void* x, const void* w, const Epilogue& epi, void* y, int64_t n, int64_t k,
                 const DeviceCtx* ctx, cudaStream_t st);
 void gemv_variant_name(int64_t n, int64_t k, const DeviceCtx* ctx, char* buf, int len);
 void gemv_set_override(int wpr, int unroll);
 
-int launch_gemm(const void* x, const void* w, const void* bias, void* y, int64_t m, int64_t n,
+int launch_gemm(const void* x, const void* w, const Epilogue& epi, void* y, int64_t m, int64_t n,
                 int64_t k, int64_t ldy, DeviceCtx* ctx, cudaStream_t st);
 void gemm_variant_name(int64_t m, int64_t n, int64_t k, const DeviceCtx* ctx, char* buf, int len);
 void gemm_set_override(int bn, int split_k);

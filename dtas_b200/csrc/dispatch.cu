@@ -187,7 +187,39 @@ int dtas_gemv(const void* x, const void* w, const void* bias, void* y, int64_t n
   Call c;
   int rc;
   if ((rc = c.begin(device, stream))) return rc;
-  return launch_gemv(x, w, bias, y, n, k, c.ctx, c.stream);
+  Epilogue epi;
+  epi.bias = static_cast<const __half*>(bias);
+  return launch_gemv(x, w, epi, y, n, k, c.ctx, c.stream);
+}
+
+static int check_epilogue(const char* what, int act, int out_dtype) {
+  if (act != DTAS_ACT_NONE && act != DTAS_ACT_GELU) DTAS_FAIL(DTAS_EINVAL, "%s: unknown activation %d", what, act);
+  if (out_dtype != DTAS_F16 && out_dtype != DTAS_F32)
+    DTAS_FAIL(DTAS_EUNSUPPORTED, "%s: the output is fp16 or fp32 (dtype %d)", what, out_dtype);
+  return DTAS_OK;
+}
+
+int dtas_gemv_fused(const void* x, const void* w, const void* bias, const void* res1, const void* res2, void* y,
+                    int64_t n, int64_t k, int act, int out_dtype, int dtype, int device, void* stream) {
+  DTAS_NONNULL("gemv_fused", x);
+  DTAS_NONNULL("gemv_fused", w);
+  DTAS_NONNULL("gemv_fused", y);
+  if (n <= 0 || k <= 0)
+    DTAS_FAIL(DTAS_EINVAL, "gemv_fused: n and k must be > 0, got n=%lld k=%lld", (long long)n, (long long)k);
+  if (dtype != DTAS_F16) DTAS_FAIL(DTAS_EUNSUPPORTED, "gemv_fused: only fp16 operands are implemented (dtype %d)", dtype);
+  int rc;
+  if ((rc = check_epilogue("gemv_fused", act, out_dtype))) return rc;
+  if (res1 == nullptr && res2 != nullptr) DTAS_FAIL(DTAS_EINVAL, "gemv_fused: res2 without res1");
+  Call c;
+  if ((rc = c.begin(device, stream))) return rc;
+  Epilogue epi;
+  epi.bias = static_cast<const __half*>(bias);
+  epi.res1 = static_cast<const __half*>(res1);
+  epi.res2 = static_cast<const __half*>(res2);
+  epi.ldr = 0;
+  epi.act = act;
+  epi.out_f32 = out_dtype == DTAS_F32 ? 1 : 0;
+  return launch_gemv(x, w, epi, y, n, k, c.ctx, c.stream);
 }
 
 int dtas_gemm_nt(const void* x, const void* w, const void* bias, void* y, int64_t m, int64_t n, int64_t k,
@@ -202,7 +234,37 @@ int dtas_gemm_nt(const void* x, const void* w, const void* bias, void* y, int64_
   Call c;
   int rc;
   if ((rc = c.begin(device, stream))) return rc;
-  return launch_gemm(x, w, bias, y, m, n, k, ldy, c.ctx, c.stream);
+  Epilogue epi;
+  epi.bias = static_cast<const __half*>(bias);
+  return launch_gemm(x, w, epi, y, m, n, k, ldy, c.ctx, c.stream);
+}
+
+int dtas_gemm_nt_fused(const void* x, const void* w, const void* bias, const void* res1, const void* res2, void* y,
+                       int64_t m, int64_t n, int64_t k, int64_t ldy, int64_t ldr, int act, int out_dtype, int dtype,
+                       int device, void* stream) {
+  DTAS_NONNULL("gemm_fused", x);
+  DTAS_NONNULL("gemm_fused", w);
+  DTAS_NONNULL("gemm_fused", y);
+  if (m <= 0) DTAS_FAIL(DTAS_EINVAL, "gemm_fused: dynamic dim m must be > 0, got %lld", (long long)m);
+  if (n <= 0 || k <= 0)
+    DTAS_FAIL(DTAS_EINVAL, "gemm_fused: n and k must be > 0, got n=%lld k=%lld", (long long)n, (long long)k);
+  if (ldy < n) DTAS_FAIL(DTAS_EINVAL, "gemm_fused: ldy (%lld) must be >= n (%lld)", (long long)ldy, (long long)n);
+  if (dtype != DTAS_F16) DTAS_FAIL(DTAS_EUNSUPPORTED, "gemm_fused: only fp16 operands are implemented (dtype %d)", dtype);
+  int rc;
+  if ((rc = check_epilogue("gemm_fused", act, out_dtype))) return rc;
+  if (res1 == nullptr && res2 != nullptr) DTAS_FAIL(DTAS_EINVAL, "gemm_fused: res2 without res1");
+  if (res1 != nullptr && ldr < n)
+    DTAS_FAIL(DTAS_EINVAL, "gemm_fused: ldr (%lld) must be >= n (%lld)", (long long)ldr, (long long)n);
+  Call c;
+  if ((rc = c.begin(device, stream))) return rc;
+  Epilogue epi;
+  epi.bias = static_cast<const __half*>(bias);
+  epi.res1 = static_cast<const __half*>(res1);
+  epi.res2 = static_cast<const __half*>(res2);
+  epi.ldr = res1 != nullptr ? ldr : 0;
+  epi.act = act;
+  epi.out_f32 = out_dtype == DTAS_F32 ? 1 : 0;
+  return launch_gemm(x, w, epi, y, m, n, k, ldy, c.ctx, c.stream);
 }
 
 int dtas_bucket_of(const char* op, int64_t m) {

@@ -1,0 +1,130 @@
+// What happens to a GEMM / GEMV accumulator before it is stored: the fused tails of the
+// reference's real workloads
+//   fused_NT_matmul_add                  y = mm + bias
+//   fused_NT_matmul3_add2_gelu           y = gelu(mm + bias)
+//   fused_NT_matmul2_add1_add3_add3      y = (res1 + (mm + bias)) + res2
+//   fused_NT_matmul2_add1_add3_add3_cast the same, widened to fp32
+// (experiment/ModelIR/dolly-v2-3b-q0f16/before_dl.py:552-573, 248-318, 163-200, 202-246; the
+// decode-time GEMV forms at :96-114, 408-440, 442-481, 483-550).  The reference rounds every
+// intermediate to fp16; here the chain is evaluated in fp32 on the fp32 accumulator and rounded
+// to fp16 once, which is the closer of the two to exact arithmetic.  An fp32 output holds that
+// fp16 value widened, as the reference's trailing cast does.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "../../include/dtas_b200.h"
+
+namespace dtas {
+
+struct Epilogue {
+  const __half* bias = nullptr;   // [n], optional
+  const __half* res1 = nullptr;   // [m, n], rows ldr elements apart, optional
+  const __half* res2 = nullptr;   // [m, n], same stride, optional
+  int64_t ldr = 0;
+  int act = DTAS_ACT_NONE;
+  int out_f32 = 0;                // 0: Y is fp16, 1: Y is fp32
+  int vec_res = 0;                // 16-byte loads from residual rows are aligned (set by the launcher)
+};
+
+#ifdef __CUDACC__
+// x * (0.5 + 0.5 * erf(x / sqrt(2))): the erf form the reference's workload uses (before_dl.py:272-318).
+__device__ __forceinline__ float gelu_erf(float t) { return t * (0.5f + 0.5f * erff(t * 0.70710678118654757f)); }
+
+// What follows the bias: activation, then the residuals.
+__device__ __forceinline__ float epi_tail(const Epilogue& e, float t, int64_t row, int col) {
+  if (e.act == DTAS_ACT_GELU) t = gelu_erf(t);
+  if (e.res1 != nullptr) t += __half2float(e.res1[row * e.ldr + col]);
+  if (e.res2 != nullptr) t += __half2float(e.res2[row * e.ldr + col]);
+  return t;
+}
+// Value of one output element from its fp32 dot product.
+__device__ __forceinline__ float epi_value(const Epilogue& e, float acc, int64_t row, int col) {
+  if (e.bias != nullptr) acc += __half2float(e.bias[col]);
+  return epi_tail(e, acc, row, col);
+}
+
+__device__ __forceinline__ void epi_store(const Epilogue& e, void* y, int64_t ldy, int64_t row, int col, float v) {
+  const __half h = __float2half_rn(v);
+  if (e.out_f32) static_cast<float*>(y)[row * ldy + col] = __half2float(h);
+  else static_cast<__half*>(y)[row * ldy + col] = h;
+}
+
+__device__ __forceinline__ void epi_add_res32(const __half* res, int64_t off, int col0, int n, int vec, float* acc32) {
+  if (vec && col0 + 32 <= n) {
+    const uint4* src = reinterpret_cast<const uint4*>(res + off + col0);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint4 v = src[q];
+      const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]);
+        acc32[8 * q + 2 * i] += f.x;
+        acc32[8 * q + 2 * i + 1] += f.y;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < n) acc32[j] += __half2float(res[off + col0 + j]);
+  }
+}
+
+// Finishes 32 consecutive output columns col0 .. col0+31 of one row held in acc32 (fp32 dot
+// products) and stores them.  vec_store: 16-byte stores into Y rows are aligned.
+__device__ __forceinline__ void epi_store_row32(const Epilogue& e, void* y, int64_t ldy, int vec_store, int64_t row,
+                                                int col0, int n, float* acc32) {
+  if (e.bias != nullptr) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < n) acc32[j] += __half2float(e.bias[col0 + j]);
+  }
+  if (e.act == DTAS_ACT_GELU) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) acc32[j] = gelu_erf(acc32[j]);
+  }
+  if (e.res1 != nullptr) epi_add_res32(e.res1, row * e.ldr, col0, n, e.vec_res, acc32);
+  if (e.res2 != nullptr) epi_add_res32(e.res2, row * e.ldr, col0, n, e.vec_res, acc32);
+  const bool full = vec_store && col0 + 32 <= n;
+  if (!e.out_f32) {
+    __half* yrow = static_cast<__half*>(y) + row * ldy;
+    if (full) {
+      uint4* dst = reinterpret_cast<uint4*>(yrow + col0);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 v;
+        __half2 h0 = __floats2half2_rn(acc32[8 * q + 0], acc32[8 * q + 1]);
+        __half2 h1 = __floats2half2_rn(acc32[8 * q + 2], acc32[8 * q + 3]);
+        __half2 h2 = __floats2half2_rn(acc32[8 * q + 4], acc32[8 * q + 5]);
+        __half2 h3 = __floats2half2_rn(acc32[8 * q + 6], acc32[8 * q + 7]);
+        v.x = *reinterpret_cast<uint32_t*>(&h0);
+        v.y = *reinterpret_cast<uint32_t*>(&h1);
+        v.z = *reinterpret_cast<uint32_t*>(&h2);
+        v.w = *reinterpret_cast<uint32_t*>(&h3);
+        dst[q] = v;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < n) yrow[col0 + j] = __float2half_rn(acc32[j]);
+    }
+  } else {
+    float* yrow = static_cast<float*>(y) + row * ldy;
+    if (full) {
+      float4* dst = reinterpret_cast<float4*>(yrow + col0);
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        dst[q] = make_float4(__half2float(__float2half_rn(acc32[4 * q + 0])), __half2float(__float2half_rn(acc32[4 * q + 1])),
+                             __half2float(__float2half_rn(acc32[4 * q + 2])), __half2float(__float2half_rn(acc32[4 * q + 3])));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < n) yrow[col0 + j] = __half2float(__float2half_rn(acc32[j]));
+    }
+  }
+}
+#endif  // __CUDACC__
+
+}  // namespace dtas

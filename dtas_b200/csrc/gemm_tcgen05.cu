@@ -190,36 +190,6 @@ __device__ __forceinline__ void epilogue_bar_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
 }
 
-// Finishes 32 consecutive output columns of one row: bias, round to fp16, store.
-__device__ __forceinline__ void store_row32(__half* yrow, int col0, int n, const __half* bias, int vec_store,
-                                            float* acc32) {
-  if (bias != nullptr) {
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (col0 + j < n) acc32[j] += __half2float(bias[col0 + j]);
-  }
-  if (vec_store && col0 + 32 <= n) {
-    uint4* dst = reinterpret_cast<uint4*>(yrow + col0);
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      uint4 v;
-      __half2 h0 = __floats2half2_rn(acc32[8 * q + 0], acc32[8 * q + 1]);
-      __half2 h1 = __floats2half2_rn(acc32[8 * q + 2], acc32[8 * q + 3]);
-      __half2 h2 = __floats2half2_rn(acc32[8 * q + 4], acc32[8 * q + 5]);
-      __half2 h3 = __floats2half2_rn(acc32[8 * q + 6], acc32[8 * q + 7]);
-      v.x = *reinterpret_cast<uint32_t*>(&h0);
-      v.y = *reinterpret_cast<uint32_t*>(&h1);
-      v.z = *reinterpret_cast<uint32_t*>(&h2);
-      v.w = *reinterpret_cast<uint32_t*>(&h3);
-      dst[q] = v;
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (col0 + j < n) yrow[col0 + j] = __float2half_rn(acc32[j]);
-  }
-}
-
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 fp16)
 // laid out by TMA with the 128-byte swizzle: 8-row groups are 1024 bytes apart (stride
 // byte offset), the leading byte offset is unused for swizzled K-major layouts,
@@ -239,8 +209,8 @@ __host__ __device__ constexpr uint32_t make_idesc_f16_f32(int n) {
 }
 
 struct GemmArgs {
-  __half* y;
-  const __half* bias;
+  void* y;            // fp16, or fp32 when epi.out_f32
+  Epilogue epi;       // bias, activation, residuals, output dtype
   float* ws;          // partial tiles of shared output tiles (layout: see the epilogues)
   int* counters;      // one arrival counter per output tile (zero between launches)
   int* status;
@@ -458,7 +428,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int col_base = nt * BN;
 
       if (n_parts == 1) {
-        __half* yrow = a.y + (int64_t)row * a.ldy;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
@@ -466,31 +435,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           tmem_ld_wait();
           const int col0 = col_base + c * 32;
           if (row_ok && col0 < a.n) {
-            if (a.bias != nullptr) {
+            float f[32];
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < a.n) r[j] = __float_as_uint(__uint_as_float(r[j]) + __half2float(a.bias[col0 + j]));
-            }
-            if (a.vec_store && col0 + 32 <= a.n) {
-              uint4* dst = reinterpret_cast<uint4*>(yrow + col0);
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                uint4 v;
-                __half2 h0 = __floats2half2_rn(__uint_as_float(r[8 * q + 0]), __uint_as_float(r[8 * q + 1]));
-                __half2 h1 = __floats2half2_rn(__uint_as_float(r[8 * q + 2]), __uint_as_float(r[8 * q + 3]));
-                __half2 h2 = __floats2half2_rn(__uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5]));
-                __half2 h3 = __floats2half2_rn(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7]));
-                v.x = *reinterpret_cast<uint32_t*>(&h0);
-                v.y = *reinterpret_cast<uint32_t*>(&h1);
-                v.z = *reinterpret_cast<uint32_t*>(&h2);
-                v.w = *reinterpret_cast<uint32_t*>(&h3);
-                dst[q] = v;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < a.n) yrow[col0 + j] = __float2half_rn(__uint_as_float(r[j]));
-            }
+            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
+            epi_store_row32(a.epi, a.y, a.ldy, a.vec_store, row, col0, a.n, f);
           }
         }
         tc_fence_before();
@@ -535,7 +483,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (is_last) {
           __threadfence();
           if (row_ok) {
-            __half* yrow = a.y + (int64_t)row * a.ldy;
             // 64 columns and two slots per batch: 32 independent 16-byte loads in flight per
             // thread, one L2 round trip per 64 columns and slot pair; slots are added in slot
             // order = K order, whatever the arrival order
@@ -568,8 +515,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                   acc[4 * q] += v1[q].x; acc[4 * q + 1] += v1[q].y; acc[4 * q + 2] += v1[q].z; acc[4 * q + 3] += v1[q].w;
                 }
               }
-              store_row32(yrow, col0, a.n, a.bias, a.vec_store, acc);
-              if (col0 + 32 < a.n) store_row32(yrow, col0 + 32, a.n, a.bias, a.vec_store, acc + 32);
+              epi_store_row32(a.epi, a.y, a.ldy, a.vec_store, row, col0, a.n, acc);
+              if (col0 + 32 < a.n) epi_store_row32(a.epi, a.y, a.ldy, a.vec_store, row, col0 + 32, a.n, acc + 32);
             }
           }
         }
@@ -805,7 +752,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * MN);
 
       if (n_parts == 1) {
-        const float bias = (a.bias != nullptr && col_ok) ? __half2float(a.bias[col]) : 0.f;
+        const float bias = (a.epi.bias != nullptr && col_ok) ? __half2float(a.epi.bias[col]) : 0.f;
 #pragma unroll 1
         for (int c = 0; c < MN / kChunk; ++c) {
           uint32_t r[kChunk];
@@ -816,7 +763,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
             for (int j = 0; j < kChunk; ++j) {
               const int row = c * kChunk + j;
-              if (row < a.m) a.y[(int64_t)row * a.ldy + col] = __float2half_rn(__uint_as_float(r[j]) + bias);
+              if (row < a.m) epi_store(a.epi, a.y, a.ldy, row, col, epi_tail(a.epi, __uint_as_float(r[j]) + bias, row, col));
             }
           }
         }
@@ -865,7 +812,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (epi_tid == 0) DTAS_TRACE_AT(9);
         if (is_last) {
           __threadfence();
-          const float bias = (a.bias != nullptr && col_ok) ? __half2float(a.bias[col]) : 0.f;
+          const float bias = (a.epi.bias != nullptr && col_ok) ? __half2float(a.epi.bias[col]) : 0.f;
           // Up to eight row groups and four slots per batch: 16-32 independent 16-byte loads in
           // flight per thread, so that a tile of up to 32 rows costs one L2 round trip per four
           // slots.  Slots are summed in slot order = K order, whatever the arrival order.
@@ -902,7 +849,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                   const int row = (g0 + j) * 4 + i;
-                  if (row < a.m) a.y[(int64_t)row * a.ldy + col] = __float2half_rn(o[i] + bias);
+                  if (row < a.m) epi_store(a.epi, a.y, a.ldy, row, col, epi_tail(a.epi, o[i] + bias, row, col));
                 }
               }
             }
@@ -1150,7 +1097,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       const bool row_ok = row < a.m;
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kPairBN);
       const int col_base = nt * kPairBN;
-      __half* yrow = a.y + (int64_t)row * a.ldy;
 #pragma unroll 1
       for (int c = 0; c < kPairBN / 32; ++c) {
         uint32_t r[32];
@@ -1158,31 +1104,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         tmem_ld_wait();
         const int col0 = col_base + c * 32;
         if (row_ok && col0 < a.n) {
-          if (a.bias != nullptr) {
+          float f[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < a.n) r[j] = __float_as_uint(__uint_as_float(r[j]) + __half2float(a.bias[col0 + j]));
-          }
-          if (a.vec_store && col0 + 32 <= a.n) {
-            uint4* dst = reinterpret_cast<uint4*>(yrow + col0);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 v;
-              __half2 h0 = __floats2half2_rn(__uint_as_float(r[8 * q + 0]), __uint_as_float(r[8 * q + 1]));
-              __half2 h1 = __floats2half2_rn(__uint_as_float(r[8 * q + 2]), __uint_as_float(r[8 * q + 3]));
-              __half2 h2 = __floats2half2_rn(__uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5]));
-              __half2 h3 = __floats2half2_rn(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7]));
-              v.x = *reinterpret_cast<uint32_t*>(&h0);
-              v.y = *reinterpret_cast<uint32_t*>(&h1);
-              v.z = *reinterpret_cast<uint32_t*>(&h2);
-              v.w = *reinterpret_cast<uint32_t*>(&h3);
-              dst[q] = v;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < a.n) yrow[col0 + j] = __float2half_rn(__uint_as_float(r[j]));
-          }
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
+          epi_store_row32(a.epi, a.y, a.ldy, a.vec_store, row, col0, a.n, f);
         }
       }
       tc_fence_before();
@@ -1204,9 +1129,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 // per output element, fp32 accumulation.  Correct for every shape, not a performance path.
 // ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
-    gemm_f16_simt_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
-                         const __half* __restrict__ bias, __half* __restrict__ y, int m, int n,
-                         int k, int64_t ldy) {
+    gemm_f16_simt_kernel(const __half* __restrict__ x, const __half* __restrict__ w, const Epilogue epi,
+                         void* __restrict__ y, int m, int n, int k, int64_t ldy) {
   const int col = blockIdx.x * 16 + (threadIdx.x & 15);
   const int row = blockIdx.y * 16 + (threadIdx.x >> 4);
   pdl_wait();
@@ -1216,8 +1140,7 @@ __global__ void __launch_bounds__(256)
   const __half* wr = w + (int64_t)col * k;
   float acc = 0.f;
   for (int i = 0; i < k; ++i) acc = fmaf(__half2float(xr[i]), __half2float(wr[i]), acc);
-  if (bias != nullptr) acc += __half2float(bias[col]);
-  y[(int64_t)row * ldy + col] = __float2half_rn(acc);
+  epi_store(epi, y, ldy, row, col, epi_value(epi, acc, row, col));
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1691,7 +1614,14 @@ int ensure_splitk_scratch(DeviceCtx* ctx) {
   return DTAS_OK;
 }
 
-int launch_gemm(const void* x, const void* w, const void* bias, void* y, int64_t m, int64_t n,
+// Fills the launcher-owned fields of the epilogue and says whether 16-byte stores into Y rows are aligned.
+static int finish_epilogue(Epilogue& e, const void* y, int64_t ldy) {
+  e.vec_res = ((e.res1 == nullptr || aligned16(e.res1)) && (e.res2 == nullptr || aligned16(e.res2)) &&
+               e.ldr % 8 == 0) ? 1 : 0;
+  return (aligned16(y) && ldy % (e.out_f32 ? 4 : 8) == 0) ? 1 : 0;
+}
+
+int launch_gemm(const void* x, const void* w, const Epilogue& epi, void* y, int64_t m, int64_t n,
                 int64_t k, int64_t ldy, DeviceCtx* ctx, cudaStream_t st) {
   if (m > 0x7fffffffLL / 2 || n > 0x7fffffffLL / 2 || k > 0x7fffffffLL / 2)
     DTAS_FAIL(DTAS_EINVAL, "gemm: dimension too large");
@@ -1699,8 +1629,8 @@ int launch_gemm(const void* x, const void* w, const void* bias, void* y, int64_t
   if (p.simt) {
     dim3 grid((unsigned)((n + 15) / 16), (unsigned)((m + 15) / 16));
     if (grid.y > 65535) DTAS_FAIL(DTAS_EUNSUPPORTED, "gemm: unaligned operands with m > 1048560");
-    launch_kernel(gemm_f16_simt_kernel, grid, 256, 0, st, (const __half*)x, (const __half*)w,
-                  (const __half*)bias, (__half*)y, (int)m, (int)n, (int)k, ldy);
+    launch_kernel(gemm_f16_simt_kernel, grid, 256, 0, st, (const __half*)x, (const __half*)w, epi, y, (int)m,
+                  (int)n, (int)k, ldy);
     return after_launch("gemm_f16_simt_kernel");
   }
   if (p.splits > 1 || p.sk_per > 0) {
@@ -1714,8 +1644,8 @@ int launch_gemm(const void* x, const void* w, const void* bias, void* y, int64_t
   if (rc != DTAS_OK) return rc;
 
   GemmArgs a;
-  a.y = (__half*)y;
-  a.bias = (const __half*)bias;
+  a.y = y;
+  a.epi = epi;
   a.ws = ctx->splitk_ws;
   a.counters = ctx->tile_counters;
   a.status = ctx->status;
@@ -1730,7 +1660,7 @@ int launch_gemm(const void* x, const void* w, const void* bias, void* y, int64_t
   a.slots_cap = p.slots_cap > 0 ? p.slots_cap : p.splits;
   a.kb_per_split = p.kb_per_split;
   a.num_kb = (int)((k + BK - 1) / BK);
-  a.vec_store = (aligned16(y) && (ldy % 8 == 0)) ? 1 : 0;
+  a.vec_store = finish_epilogue(a.epi, y, ldy);
   if ((int64_t)a.m_tiles * a.n_tiles * a.splits > 0x7fffffffLL)
     DTAS_FAIL(DTAS_EINVAL, "gemm: too many tiles");
   if (p.pair) {
@@ -1888,8 +1818,8 @@ extern "C" int dtas_gemm_nt_static_scratch(const void* x, const void* w, const v
   if ((rc = make_tmap(&tx, x, m, k, BM)) != DTAS_OK) return rc;
   if ((rc = make_tmap(&tw, w, n, k, p.bn)) != DTAS_OK) return rc;
   GemmArgs a;
-  a.y = (__half*)y;
-  a.bias = (const __half*)bias;
+  a.y = y;
+  a.epi.bias = (const __half*)bias;
   a.ws = reinterpret_cast<float*>(sd->base);
   a.counters = reinterpret_cast<int*>(sd->base + kStaticPartialBytes);
   a.status = status_word != nullptr ? static_cast<int*>(status_word)
@@ -1904,7 +1834,7 @@ extern "C" int dtas_gemm_nt_static_scratch(const void* x, const void* w, const v
   a.slots_cap = splits;
   a.kb_per_split = kb_per;
   a.num_kb = num_kb;
-  a.vec_store = (aligned16(y) && (ldy % 8 == 0)) ? 1 : 0;
+  a.vec_store = finish_epilogue(a.epi, y, ldy);
   switch (p.bn) {
     case 256: return launch_tc<256>(tx, tw, a, sd->sm_count, st);
     case 128: return launch_tc<128>(tx, tw, a, sd->sm_count, st);

@@ -34,8 +34,8 @@ __device__ __forceinline__ float dot8(uint4 w, uint4 x, float acc) {
 
 template <int WPR, int UNROLL>
 __global__ void __launch_bounds__(kThreads)
-    gemv_f16_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
-                    const __half* __restrict__ bias, __half* __restrict__ y, int n, int k) {
+    gemv_f16_kernel(const __half* __restrict__ x, const __half* __restrict__ w, const Epilogue epi,
+                    void* __restrict__ y, int n, int k) {
   constexpr int kRowsPerCta = kWarps / WPR;
   __shared__ float partial[kWarps];
 
@@ -84,21 +84,19 @@ __global__ void __launch_bounds__(kThreads)
       float r = partial[warp];
 #pragma unroll
       for (int i = 1; i < WPR; ++i) r += partial[warp + i];
-      if (bias != nullptr) r += __half2float(bias[row]);
-      y[row] = __float2half_rn(r);
+      epi_store(epi, y, 0, 0, row, epi_value(epi, r, 0, row));
     }
   } else {
     if (lane == 0 && live) {
-      if (bias != nullptr) s += __half2float(bias[row]);
-      y[row] = __float2half_rn(s);
+      epi_store(epi, y, 0, 0, row, epi_value(epi, s, 0, row));
     }
   }
 }
 
 // Any K / any alignment: one warp per row, scalar loads.
 __global__ void __launch_bounds__(kThreads)
-    gemv_f16_scalar_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
-                           const __half* __restrict__ bias, __half* __restrict__ y, int n, int k) {
+    gemv_f16_scalar_kernel(const __half* __restrict__ x, const __half* __restrict__ w, const Epilogue epi,
+                           void* __restrict__ y, int n, int k) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * kWarps + warp;
   float s = 0.f;
@@ -111,8 +109,7 @@ __global__ void __launch_bounds__(kThreads)
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
   if (lane == 0 && row < n) {
-    if (bias != nullptr) s += __half2float(bias[row]);
-    y[row] = __float2half_rn(s);
+    epi_store(epi, y, 0, 0, row, epi_value(epi, s, 0, row));
   }
 }
 
@@ -149,17 +146,15 @@ void gemv_set_override(int wpr, int unroll) {
   g_gemv_unroll.store(unroll);
 }
 
-int launch_gemv(const void* x, const void* w, const void* bias, void* y, int64_t n, int64_t k,
+int launch_gemv(const void* x, const void* w, const Epilogue& epi, void* y, int64_t n, int64_t k,
                 const DeviceCtx* ctx, cudaStream_t st) {
   if (n > 0x7fffffffLL || k > 0x7fffffffLL) DTAS_FAIL(DTAS_EINVAL, "gemv: n or k too large");
   const __half* xp = (const __half*)x;
   const __half* wp = (const __half*)w;
-  const __half* bp = (const __half*)bias;
-  __half* yp = (__half*)y;
   const bool vec_ok = (k % 8 == 0) && aligned16(x) && aligned16(w);
   if (!vec_ok) {
     const unsigned grid = (unsigned)((n + kWarps - 1) / kWarps);
-    launch_kernel(gemv_f16_scalar_kernel, grid, kThreads, 0, st, xp, wp, bp, yp, (int)n, (int)k);
+    launch_kernel(gemv_f16_scalar_kernel, grid, kThreads, 0, st, xp, wp, epi, y, (int)n, (int)k);
     return after_launch("gemv_f16_scalar_kernel");
   }
   const int wpr = pick_wpr(n, k, ctx->sm_count);
@@ -168,7 +163,7 @@ int launch_gemv(const void* x, const void* w, const void* bias, void* y, int64_t
   const int unroll = pick_unroll(wpr);
 #define DTAS_GEMV_CASE(W, U)                                                                  \
   if (wpr == W && unroll == U) {                                                              \
-    launch_kernel(gemv_f16_kernel<W, U>, grid, kThreads, 0, st, xp, wp, bp, yp, (int)n, (int)k); \
+    launch_kernel(gemv_f16_kernel<W, U>, grid, kThreads, 0, st, xp, wp, epi, y, (int)n, (int)k); \
     return after_launch("gemv_f16_kernel");                                                   \
   }
   DTAS_GEMV_CASE(1, 4) DTAS_GEMV_CASE(1, 8) DTAS_GEMV_CASE(2, 4) DTAS_GEMV_CASE(2, 8)

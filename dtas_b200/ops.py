@@ -140,24 +140,60 @@ def layer_norm(x, gamma, beta, out, eps=1e-5):
     return out
 
 
-def gemv(x, w, out, bias=None):
-    """out[1, N] = x[1, K] @ w[N, K]^T (+ bias[N]); fp16, fp32 accumulation."""
-    tensors = (x, w, out) if bias is None else (x, w, out, bias)
+_ACTS = {None: _abi.ACT_NONE, "none": _abi.ACT_NONE, "gelu": _abi.ACT_GELU}
+
+
+def _tail_args(name, out, n, rows, bias, res1, res2, act):
+    """Checks the optional tail operands; -> (act code, out dtype code, ldr, fused?)."""
+    if act not in _ACTS:
+        raise _abi.DtasError(_abi.EINVAL, f"{name}: unknown activation {act!r} (None or 'gelu')")
+    if out.dtype not in (torch.float16, torch.float32):
+        raise _abi.DtasError(_abi.EUNSUPPORTED, f"{name}: the output must be fp16 or fp32, got {out.dtype}")
+    if res1 is None and res2 is not None:
+        raise _abi.DtasError(_abi.EINVAL, f"{name}: res2 without res1")
+    if bias is not None and (bias.dtype != torch.float16 or bias.numel() != n or not bias.is_contiguous()):
+        raise _abi.DtasError(_abi.EINVAL, f"{name}: bias must be a contiguous fp16 vector of N elements")
+    ldr = 0
+    for r in (res1, res2):
+        if r is None:
+            continue
+        if r.dtype != torch.float16 or r.numel() != rows * n or r.stride(-1) != 1:
+            raise _abi.DtasError(_abi.EINVAL, f"{name}: residuals must be fp16 [m, N] with unit inner stride")
+        ld = max(int(r.stride(-2)), n) if r.dim() >= 2 else n
+        if ldr and ld != ldr and rows > 1:
+            raise _abi.DtasError(_abi.EINVAL, f"{name}: both residuals must have the same row stride")
+        ldr = ld
+    fused = res1 is not None or _ACTS[act] != _abi.ACT_NONE or out.dtype == torch.float32
+    return _ACTS[act], (_abi.F32 if out.dtype == torch.float32 else _abi.F16), ldr, fused
+
+
+def _ptr(t):
+    return t.data_ptr() if t is not None else None
+
+
+def gemv(x, w, out, bias=None, res1=None, res2=None, act=None):
+    """out[1, N] = act(x[1, K] @ w[N, K]^T + bias[N]) + res1 + res2; fp16 operands, fp32 accumulation,
+    fp16 or fp32 `out` (the fp16 result widened).  bias, res1, res2 and act are optional."""
+    tensors = tuple(t for t in (x, w, out, bias, res1, res2) if t is not None)
     dev, st = _check("gemv", *tensors)
     n, k = int(w.shape[0]), int(w.shape[1])
     if w.dim() != 2 or x.numel() != k or out.numel() != n:
         raise _abi.DtasError(_abi.EINVAL, f"gemv: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
-    if not (x.dtype == w.dtype == out.dtype == torch.float16) or (bias is not None and bias.dtype != torch.float16):
-        raise _abi.DtasError(_abi.EUNSUPPORTED, "gemv: only fp16 is implemented")
-    if bias is not None and bias.numel() != n:
-        raise _abi.DtasError(_abi.EINVAL, "gemv: bias must have N elements")
-    _chk(_lib().dtas_gemv(x.data_ptr(), w.data_ptr(), bias.data_ptr() if bias is not None else None,
-                                    out.data_ptr(), n, k, _abi.F16, dev, st))
+    if not (x.dtype == w.dtype == torch.float16):
+        raise _abi.DtasError(_abi.EUNSUPPORTED, "gemv: only fp16 operands are implemented")
+    act_c, out_c, _, fused = _tail_args("gemv", out, n, 1, bias, res1, res2, act)
+    if fused:
+        _chk(_lib().dtas_gemv_fused(x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(res1), _ptr(res2), out.data_ptr(),
+                                    n, k, act_c, out_c, _abi.F16, dev, st))
+    else:
+        _chk(_lib().dtas_gemv(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), n, k, _abi.F16, dev, st))
     return out
 
 
-def gemm_nt(x, w, out, bias=None):
-    """out[m, N] = x[m, K] @ w[N, K]^T (+ bias[N]); fp16, fp32 accumulation, fp16 result.
+def gemm_nt(x, w, out, bias=None, res1=None, res2=None, act=None):
+    """out[m, N] = act(x[m, K] @ w[N, K]^T + bias[N]) + res1[m, N] + res2[m, N]; fp16 operands, fp32
+    accumulation, fp16 or fp32 `out` (the fp16 result widened).  bias, res1, res2 and act ('gelu')
+    are optional: the fused forms of the reference's model workloads.
 
     `out` may be a column slab of a wider row-major buffer (last-dim stride 1, any row
     stride >= N): a column-sharded rank writes its part of the full output in place.
@@ -169,22 +205,25 @@ def gemm_nt(x, w, out, bias=None):
     mo, n = _rows_cols(out, "gemm")
     if w.dim() != 2 or int(w.shape[1]) != k or int(w.shape[0]) != n or mo != m:
         raise _abi.DtasError(_abi.EINVAL, f"gemm: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
-    if not (x.dtype == w.dtype == out.dtype == torch.float16) or (bias is not None and bias.dtype != torch.float16):
-        raise _abi.DtasError(_abi.EUNSUPPORTED, "gemm: only fp16 is implemented")
-    if not x.is_contiguous() or not w.is_contiguous() or (bias is not None and not bias.is_contiguous()):
-        raise _abi.DtasError(_abi.EINVAL, "gemm: x, w and bias must be contiguous")
+    if not (x.dtype == w.dtype == torch.float16):
+        raise _abi.DtasError(_abi.EUNSUPPORTED, "gemm: only fp16 operands are implemented")
+    if not x.is_contiguous() or not w.is_contiguous():
+        raise _abi.DtasError(_abi.EINVAL, "gemm: x and w must be contiguous")
     if out.stride(-1) != 1:
         raise _abi.DtasError(_abi.EINVAL, "gemm: out must have unit stride in its last dim")
     ldy = int(out.stride(-2)) if m > 1 else max(int(out.stride(-2)), n)
-    for t in (w, out) + (() if bias is None else (bias,)):
-        if t.device != dev_t:
+    for t in (w, out, bias, res1, res2):
+        if t is not None and t.device != dev_t:
             raise _abi.DtasError(_abi.EINVAL, "gemm: tensors on different devices")
-    if bias is not None and bias.numel() != n:
-        raise _abi.DtasError(_abi.EINVAL, "gemm: bias must have N elements")
+    act_c, out_c, ldr, fused = _tail_args("gemm", out, n, m, bias, res1, res2, act)
     dev = dev_t.index if dev_t.index is not None else torch.cuda.current_device()
     st = _raw_stream(dev)
-    _chk(_lib().dtas_gemm_nt(x.data_ptr(), w.data_ptr(), bias.data_ptr() if bias is not None else None,
-                                       out.data_ptr(), m, n, k, ldy, _abi.F16, dev, st))
+    if fused:
+        _chk(_lib().dtas_gemm_nt_fused(x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(res1), _ptr(res2), out.data_ptr(),
+                                       m, n, k, ldy, ldr, act_c, out_c, _abi.F16, dev, st))
+    else:
+        _chk(_lib().dtas_gemm_nt(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), m, n, k, ldy, _abi.F16,
+                                 dev, st))
     return out
 
 

@@ -24,6 +24,8 @@ class OpSpec:
     k         : reduction length K for gemv / gemm
     eps       : epsilon of the norm ops
     bias      : gemv / gemm take a bias argument
+    residuals : gemv / gemm add this many [m, N] tensors after the activation (0, 1 or 2)
+    act       : activation fused behind the bias: "" or "gelu"
     upper     : upper bound of the symbolic dim (the reference's tir_var_upper_bound)
     """
     name: str
@@ -34,12 +36,18 @@ class OpSpec:
     k: int = 0
     eps: float = 0.0
     bias: bool = False
+    residuals: int = 0
+    act: str = ""
     upper: Optional[int] = None
     attrs: Dict[str, str] = field(default_factory=dict)
 
     def __post_init__(self):
         if self.op not in OP_KIND:
             raise ValueError(f"unknown op '{self.op}'")
+        if self.residuals not in (0, 1, 2) or self.act not in ("", "gelu"):
+            raise ValueError(f"{self.name}: residuals must be 0..2 and act '' or 'gelu'")
+        if (self.residuals or self.act) and self.op not in ("gemv", "gemm"):
+            raise ValueError(f"{self.name}: only gemv / gemm take a fused tail")
 
     @property
     def kind(self):

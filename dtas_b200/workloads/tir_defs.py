@@ -243,6 +243,59 @@ def gemv(N, K, name="gemv"):
     return func
 
 
+def matmul_fused(N, K, dynamic=True, bias=True, act="", residuals=0, out_dtype="float16", name="fused_NT_matmul"):
+    """The fused matmul forms of the reference's model workloads
+    (experiment/ModelIR/dolly-v2-3b-q0f16/before_dl.py: fused_NT_matmul_add :552,
+    fused_NT_matmul3_add2_gelu :248, fused_NT_matmul2_add1_add3_add3 :163, ..._cast :202, and the
+    decode-time forms with a static single row :96, :408, :442, :483), block by block:
+    matmul -> + bias -> [* 1/sqrt(2) -> erf in fp32 -> * 0.5 -> 0.5 + -> *] -> res1 + -> + res2 -> [cast].
+    Every block after the matmul stores fp16, as in the reference; the matmul itself accumulates
+    in fp32 and is rounded to fp16 once (the reference accumulates in fp16).  Arguments:
+    x, W, [bias], [res1], [res2], out.  Built with te.create_prim_func so that the optional
+    stages are plain Python conditions."""
+    tvm = _tvm()
+    from tvm import te, tir
+    rows = te.var("n", "int64") if dynamic else 1
+    shape = (1, rows, N)
+    x = te.placeholder((1, rows, K), "float16", name="lv_x")
+    w = te.placeholder((N, K), "float16", name="param_w")
+    args = [x, w]
+    k = te.reduce_axis((0, K), name="k")
+    acc = te.compute(shape, lambda i0, i1, i2: te.sum(x[i0, i1, k].astype("float32") * w[i2, k].astype("float32"), axis=k),
+                     name="NT_matmul")
+    t = te.compute(shape, lambda i0, i1, i2: acc[i0, i1, i2].astype("float16"), name="NT_matmul_intermediate")
+    if bias:
+        b = te.placeholder((N,), "float16", name="param_bias")
+        args.append(b)
+        prev = t
+        t = te.compute(shape, lambda i0, i1, i2: prev[i0, i1, i2] + b[i2], name="T_add")
+    if act == "gelu":
+        base = t
+        u = te.compute(shape, lambda i0, i1, i2: base[i0, i1, i2] * tir.const(0.70710678118654757, "float16"), name="T_multiply")
+        c0 = te.compute(shape, lambda i0, i1, i2: u[i0, i1, i2].astype("float32"), name="compute")
+        c1 = te.compute(shape, lambda i0, i1, i2: tir.erf(c0[i0, i1, i2]), name="compute_1")
+        c2 = te.compute(shape, lambda i0, i1, i2: c1[i0, i1, i2].astype("float16"), name="compute_2")
+        m1 = te.compute(shape, lambda i0, i1, i2: c2[i0, i1, i2] * tir.const(0.5, "float16"), name="T_multiply_1")
+        a1 = te.compute(shape, lambda i0, i1, i2: tir.const(0.5, "float16") + m1[i0, i1, i2], name="T_add_gelu")
+        t = te.compute(shape, lambda i0, i1, i2: base[i0, i1, i2] * a1[i0, i1, i2], name="T_multiply_2")
+    elif act:
+        raise ValueError(f"unknown activation {act!r}")
+    def add_stage(lhs, rhs, stage):
+        return te.compute(shape, lambda i0, i1, i2: lhs[i0, i1, i2] + rhs[i0, i1, i2], name=stage)
+
+    for r in range(residuals):
+        res = te.placeholder(shape, "float16", name=f"lv_res{r + 1}")
+        args.append(res)
+        # the reference adds the first residual on the left, the second on the right
+        t = add_stage(res, t, "T_add_1") if r == 0 else add_stage(t, res, "T_add_2")
+    if out_dtype != "float16":
+        prev = t
+        t = te.compute(shape, lambda i0, i1, i2: prev[i0, i1, i2].astype(out_dtype), name="compute_cast")
+    args.append(t)
+    func = te.create_prim_func(args)
+    return func.with_attr("global_symbol", name)
+
+
 def make_module(funcs, upper_bound=None):
     """IRModule from {name: PrimFunc}; `upper_bound` mirrors the reference's
     `tir_var_upper_bound` function attribute (tuning_test/tune_cast.py:27)."""

@@ -96,6 +96,28 @@ int dtas_gemm_nt(const void* x, const void* w, const void* bias, void* y,
                  int64_t m, int64_t n, int64_t k, int64_t ldy,
                  int dtype, int device, void* stream);
 
+/* ---- GEMM / GEMV with a fused tail -----------------------------------------
+ * The forms the reference's model workloads take after operator fusion
+ * (experiment/ModelIR/dolly-v2-3b-q0f16/before_dl.py):
+ *   fused_NT_matmul_add                   (:552)  y = x.W^T + bias
+ *   fused_NT_matmul3_add2_gelu            (:248)  y = gelu(x.W^T + bias)
+ *   fused_NT_matmul2_add1_add3_add3       (:163)  y = (res1 + (x.W^T + bias)) + res2
+ *   fused_NT_matmul2_add1_add3_add3_cast  (:202)  the same, written as fp32
+ * and their decode-time GEMV forms (:96, :408, :442, :483).  One call computes
+ *   y = act(x.W^T + bias) + res1 + res2
+ * on the fp32 accumulator, rounds to fp16 once, and stores fp16 or (out_dtype DTAS_F32) that
+ * fp16 value widened to fp32.  bias [n], res1 and res2 [m, n] (row stride ldr elements; [n] for
+ * the GEMV) are fp16 and optional (NULL); res2 needs res1.  act is DTAS_ACT_NONE or
+ * DTAS_ACT_GELU = t * (0.5 + 0.5 * erf(t / sqrt(2))), the erf form of the reference's workload.
+ * The reference rounds every intermediate to fp16; results agree within the GEMM tolerance.   */
+#define DTAS_ACT_NONE 0
+#define DTAS_ACT_GELU 1
+int dtas_gemm_nt_fused(const void* x, const void* w, const void* bias, const void* res1, const void* res2,
+                       void* y, int64_t m, int64_t n, int64_t k, int64_t ldy, int64_t ldr, int act,
+                       int out_dtype, int dtype, int device, void* stream);
+int dtas_gemv_fused(const void* x, const void* w, const void* bias, const void* res1, const void* res2,
+                    void* y, int64_t n, int64_t k, int act, int out_dtype, int dtype, int device, void* stream);
+
 /* ---- GEMM without any allocation ------------------------------------------
  * No counterpart in the reference.  Same operation and operands as dtas_gemm_nt, for callers
  * that must not create device memory when they call: runtimes that gave the whole device to

@@ -150,3 +150,32 @@ def gemm_nt(x, w, bias=None, rows=None, cols=None, out=None):
     _c().oracle_gemm_nt_f16(_ptr(x2), _ptr(w), _ptr(b) if b is not None else None, _ptr(out), _i64(m), _i64(n),
                             _i64(k), _i64(n), _i64(r0), _i64(r1), _i64(c0), _i64(c1))
     return out
+
+
+def gemm_nt_fused(x, w, bias=None, res1=None, res2=None, act=None, out_dtype=np.float16, rows=None, cols=None, out=None):
+    """The fused matmul forms of the model workloads with the reference's stage-by-stage fp16
+    rounding: y = cast(((res1 + gelu?(X W^T + bias)) + res2)).  rows / cols restrict the block."""
+    x2 = _2d(x)
+    w = np.ascontiguousarray(w)
+    assert x2.dtype == np.float16 and w.dtype == np.float16
+    m, k = x2.shape
+    n = w.shape[0]
+    assert w.shape[1] == k and act in (None, "gelu") and np.dtype(out_dtype) in (np.dtype(np.float16), np.dtype(np.float32))
+    if out is None:
+        out = np.zeros((m, n), out_dtype)
+    r0, r1 = rows if rows is not None else (0, m)
+    c0, c1 = cols if cols is not None else (0, n)
+    opt = [None if t is None else np.ascontiguousarray(t) for t in (bias, res1, res2)]
+    for r in opt[1:]:
+        assert r is None or (r.dtype == np.float16 and r.size == m * n)
+    ptrs = [_ptr(t) if t is not None else None for t in opt]
+    _c().oracle_gemm_nt_fused_f16(_ptr(x2), _ptr(w), ptrs[0], ptrs[1], ptrs[2], _ptr(out), _i64(m), _i64(n), _i64(k),
+                                  _i64(n), _i64(n), ctypes.c_int(1 if act == "gelu" else 0),
+                                  ctypes.c_int(1 if np.dtype(out_dtype) == np.dtype(np.float32) else 0),
+                                  _i64(r0), _i64(r1), _i64(c0), _i64(c1))
+    return out
+
+
+def gemv_fused(x, w, bias=None, res1=None, res2=None, act=None, out_dtype=np.float16):
+    x = np.ascontiguousarray(x).reshape(1, -1)
+    return gemm_nt_fused(x, w, bias, res1, res2, act, out_dtype)

@@ -199,3 +199,55 @@ void oracle_gemv_f16(const f16* x, const f16* w, const f16* bias, f16* y, int64_
     y[j] = (f16)acc;
   }
 }
+
+/* Fused matmul tails of the model workloads, stage by stage as the reference's TIR stores them
+ * (experiment/ModelIR/dolly-v2-3b-q0f16/before_dl.py:163-200 add/add/add, :202-246 + cast,
+ * :248-318 add + gelu; decode-time forms :96-114, :408-550): every stage after the matmul is a
+ * separate block writing an fp16 buffer, so every stage rounds to fp16.
+ *   T_add        t = mm + bias
+ *   T_multiply   u = t * (half)0.70710678118654757      gelu, erf form
+ *   compute      c = (float)u;  compute_1  e = erff(c);  compute_2  h = (half)e
+ *   T_multiply_1 h = h * (half)0.5;  T_add_1  s = (half)0.5 + h;  T_multiply_2  t = t * s
+ *   T_add_1      t = res1 + t;   T_add_2  t = t + res2
+ *   compute      y = (float)t                            the _cast variants
+ * The matmul itself is the fp32-accumulated one above, rounded to fp16 once. */
+static inline f16 fused_tail(f16 mm, const f16* bias, const f16* res1, const f16* res2, int64_t j, int64_t roff,
+                             int act) {
+  f16 t = mm;
+  if (bias) t = (f16)((float)t + (float)bias[j]);
+  if (act == 1) {
+    const f16 u = (f16)((float)t * (float)(f16)0.70710678118654757f);
+    const float e = erff((float)u);
+    f16 h = (f16)e;
+    h = (f16)((float)h * 0.5f);
+    const f16 sgm = (f16)(0.5f + (float)h);
+    t = (f16)((float)t * (float)sgm);
+  }
+  if (res1) t = (f16)((float)res1[roff + j] + (float)t);
+  if (res2) t = (f16)((float)t + (float)res2[roff + j]);
+  return t;
+}
+
+void oracle_gemm_nt_fused_f16(const f16* x, const f16* w, const f16* bias, const f16* res1, const f16* res2, void* y,
+                              int64_t m, int64_t n, int64_t k, int64_t ldy, int64_t ldr, int act, int out_f32,
+                              int64_t row0, int64_t row1, int64_t col0, int64_t col1) {
+  (void)m;
+  (void)n;
+#pragma omp parallel for schedule(static) collapse(2)
+  for (int64_t i = row0; i < row1; ++i) {
+    for (int64_t j = col0; j < col1; ++j) {
+      float acc = 0.0f;
+      const f16* xr = x + i * k;
+      const f16* wr = w + j * k;
+      for (int64_t kk = 0; kk < k; ++kk) acc = acc + ((float)xr[kk]) * ((float)wr[kk]);
+      const f16 t = fused_tail((f16)acc, bias, res1, res2, j, i * ldr, act);
+      if (out_f32) ((float*)y)[i * ldy + j] = (float)t;
+      else ((f16*)y)[i * ldy + j] = t;
+    }
+  }
+}
+
+void oracle_gemv_fused_f16(const f16* x, const f16* w, const f16* bias, const f16* res1, const f16* res2, void* y,
+                           int64_t n, int64_t k, int act, int out_f32) {
+  oracle_gemm_nt_fused_f16(x, w, bias, res1, res2, y, 1, n, k, n, n, act, out_f32, 0, 1, 0, n);
+}

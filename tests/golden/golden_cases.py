@@ -35,6 +35,16 @@ CASES = {
     "gemm_m16_4096_4096": dict(op="gemm", m=16, N=4096, K=4096, seed=4000),
     "gemm_m255_384_1024": dict(op="gemm", m=255, N=384, K=1024, seed=4010),
     "gemm_m64_200_264": dict(op="gemm", m=64, N=200, K=264, seed=4020),
+    # fused matmul tails of the model workloads (bias / gelu / two residuals / trailing cast) ---------
+    "gemm_bias_m33_384_512": dict(op="gemm_fused", m=33, N=384, K=512, seed=5000),
+    "gemm_gelu_m33_384_512": dict(op="gemm_fused", m=33, N=384, K=512, act="gelu", seed=5010),
+    "gemm_res2_m65_200_264": dict(op="gemm_fused", m=65, N=200, K=264, residuals=2, seed=5020),
+    "gemm_res2_cast_m16_512_1024": dict(op="gemm_fused", m=16, N=512, K=1024, residuals=2, out="float32", seed=5030),
+    "gemm_res1_nobias_m300_256_128": dict(op="gemm_fused", m=300, N=256, K=128, bias=False, residuals=1, seed=5040),
+    "gemv_bias_2560_10240": dict(op="gemv_fused", N=2560, K=10240, seed=6000),
+    "gemv_gelu_10240_2560": dict(op="gemv_fused", N=10240, K=2560, act="gelu", seed=6010),
+    "gemv_res2_2560_2560": dict(op="gemv_fused", N=2560, K=2560, residuals=2, seed=6020),
+    "gemv_res2_cast_2560_2560": dict(op="gemv_fused", N=2560, K=2560, residuals=2, out="float32", seed=6030),
 }
 
 
@@ -70,4 +80,13 @@ def make_inputs(case):
     if op == "gemm":
         m, n, k = case["m"], case["N"], case["K"]
         return [nd((1, m, k), 0, "float16"), nd((n, k), 1, "float16", scale=0.02)], np.zeros((1, m, n), "float16")
+    if op in ("gemm_fused", "gemv_fused"):
+        m = case["m"] if op == "gemm_fused" else 1
+        n, k = case["N"], case["K"]
+        ins = [nd((1, m, k), 0, "float16"), nd((n, k), 1, "float16", scale=0.02)]
+        if case.get("bias", True):
+            ins.append(nd((n,), 2, "float16", scale=0.5))
+        for r in range(case.get("residuals", 0)):
+            ins.append(nd((1, m, n), 3 + r, "float16"))
+        return ins, np.zeros((1, m, n), case.get("out", "float16"))
     raise ValueError(op)

@@ -1,7 +1,8 @@
 """Generates tests/golden/*.npz: outputs of the workload PrimFuncs built by TVM.
 
 Run in a container that has a TVM (here: the fork bundled with tilelang, 0.23.dev0):
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py                    # every case
+    python tests/golden/make_golden.py gemm_fused gemv    # only the cases of these operators
 Each PrimFunc from dtas_b200/workloads/tir_defs.py is built for target "c", compiled with
 g++ -O2 -Dhalf=_Float16 (TVM's own export_library), run on seeded inputs from
 dtas_b200.reference.seeded_normal, and the output is stored.  Inputs are not stored: the
@@ -50,12 +51,22 @@ def prim_func(case):
         return td.gemm_nt(p["N"], p["K"])
     if op == "gemv":
         return td.gemv(p["N"], p["K"])
+    if op in ("gemm_fused", "gemv_fused"):
+        return td.matmul_fused(p["N"], p["K"], dynamic=op == "gemm_fused", bias=p.get("bias", True), act=p.get("act", ""),
+                               residuals=p.get("residuals", 0), out_dtype=p.get("out", "float16"))
     raise ValueError(op)
 
 
 def main():
+    only = set(sys.argv[1:])
     outputs, meta = {}, {}
+    meta_path = os.path.join(HERE, "golden_meta.json")
+    if only and os.path.exists(meta_path):
+        with open(meta_path) as f:
+            meta = json.load(f)
     for name, case in CASES.items():
+        if only and case["op"] not in only:
+            continue
         tvm, rt = build({"f": prim_func(case)})
         ins, out = make_inputs(case)
         to_nd = tvm.runtime.tensor if hasattr(tvm.runtime, "tensor") else tvm.nd.array
@@ -72,7 +83,7 @@ def main():
         np.savez_compressed(os.path.join(HERE, f"{op}.npz"), **arrs)
     tvm = td._tvm()
     meta["_generator"] = {"tvm": tvm.__version__, "target": "c", "cc_options": ["-O2", "-Dhalf=_Float16"]}
-    with open(os.path.join(HERE, "golden_meta.json"), "w") as f:
+    with open(meta_path, "w") as f:
         json.dump(meta, f, indent=1, sort_keys=True)
 
 

@@ -114,3 +114,34 @@ def test_classification_of_tvmscript_primfuncs():
     rt = Engine(1, True, None).tune_module(mod, arch=arch.B200(0), range_div_factor=256)
     assert set(rt.keys()) == {"cast", "softmax"}
     assert len(rt.record["functions"]["cast"]["index_table"]) == 16
+
+
+def test_classification_of_fused_matmul_forms():
+    """The fused matmul functions of the reference's model IR (bias, GELU, residual adds, trailing
+    cast; dynamic rows or the single decode row) map to gemm / gemv specs with a fused tail."""
+    td = pytest.importorskip("dtas_b200.workloads.tir_defs")
+    try:
+        td._tvm()
+    except ImportError:
+        pytest.skip("no TVM in this environment")
+    forms = [
+        (dict(), ("gemm", True, 0, "", "float16")),                                   # fused_NT_matmul_add
+        (dict(act="gelu"), ("gemm", True, 0, "gelu", "float16")),                     # fused_NT_matmul3_add2_gelu
+        (dict(residuals=2), ("gemm", True, 2, "", "float16")),                        # ..._add1_add3_add3
+        (dict(residuals=2, out_dtype="float32"), ("gemm", True, 2, "", "float32")),   # ..._add1_add3_add3_cast
+        (dict(dynamic=False, residuals=2), ("gemv", True, 2, "", "float16")),         # fused_NT_matmul8_add5_add7_add7
+        (dict(dynamic=False, act="gelu"), ("gemv", True, 0, "gelu", "float16")),      # fused_NT_matmul9_add6_gelu1
+        (dict(bias=False, residuals=1), ("gemm", False, 1, "", "float16")),
+    ]
+    for kw, (op, bias, n_res, act, out) in forms:
+        s = FuncInfo(td.matmul_fused(2560, 10240, **kw), "f").spec
+        assert (s.op, s.bias, s.residuals, s.act, s.out_dtype, s.cols, s.k) == (op, bias, n_res, act, out, 2560, 10240), (kw, s)
+    with pytest.raises(ValueError):
+        OpSpec("f", "softmax", cols=8, act="gelu")
+    # a module record with a fused function survives the JSON round trip
+    dtas_b200.set_log_level(0)
+    mod = td.make_module({"ffn_up": td.matmul_fused(10240, 2560, act="gelu"),
+                          "attn_out": td.matmul_fused(2560, 2560, residuals=2, out_dtype="float32")}, upper_bound=1024)
+    rt = Engine(1, True, None).tune_module(mod, arch=arch.B200(0), range_div_factor=256)
+    assert rt["ffn_up"].spec.act == "gelu" and rt["attn_out"].spec.residuals == 2
+    assert OpSpec.from_dict(rt.record["functions"]["attn_out"]["spec"]).out_dtype == "float32"

@@ -21,6 +21,14 @@ def load_golden(op):
     return np.load(os.path.join(GOLDEN_DIR, f"{op}.npz"))
 
 
+def fused_operands(case, ins):
+    """(x, w, bias, res1, res2) of a fused-matmul golden case from its input list."""
+    x, w, rest = ins[0], ins[1], list(ins[2:])
+    bias = rest.pop(0) if case.get("bias", True) else None
+    rest += [None, None]
+    return x, w, bias, rest[0], rest[1]
+
+
 def bits(a):
     a = np.ascontiguousarray(a)
     return a.view({1: np.uint8, 2: np.uint16, 4: np.uint32}[a.dtype.itemsize])
