@@ -30,7 +30,9 @@ struct Epilogue {
 
 #ifdef __CUDACC__
 // x * (0.5 + 0.5 * erf(x / sqrt(2))): the erf form the reference's workload uses (before_dl.py:272-318).
-__device__ __forceinline__ float gelu_erf(float t) { return t * (0.5f + 0.5f * erff(t * 0.70710678118654757f)); }
+// Not inlined: the epilogues are unrolled over 16-32 elements, and as many copies of erff in
+// line made the kernels slower for everyone (instruction fetch), GELU or not.
+static __device__ __noinline__ float gelu_erf(float t) { return t * (0.5f + 0.5f * erff(t * 0.70710678118654757f)); }
 
 // What follows the bias: activation, then the residuals.
 __device__ __forceinline__ float epi_tail(const Epilogue& e, float t, int64_t row, int col) {
@@ -49,6 +51,22 @@ __device__ __forceinline__ void epi_store(const Epilogue& e, void* y, int64_t ld
   const __half h = __float2half_rn(v);
   if (e.out_f32) static_cast<float*>(y)[row * ldy + col] = __half2float(h);
   else static_cast<__half*>(y)[row * ldy + col] = h;
+}
+
+// COUNT consecutive rows row0, row0+1, ... of one output column; v[] holds dot product + bias.
+template <int COUNT>
+__device__ __forceinline__ void epi_store_column(const Epilogue& e, void* y, int64_t ldy, int row0, int m, int col,
+                                                 const float* v) {
+  if (e.act == DTAS_ACT_NONE && e.res1 == nullptr && !e.out_f32) {   // plain fp16 result: nothing but the store
+    __half* yc = static_cast<__half*>(y) + col;
+#pragma unroll
+    for (int j = 0; j < COUNT; ++j)
+      if (row0 + j < m) yc[(int64_t)(row0 + j) * ldy] = __float2half_rn(v[j]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < COUNT; ++j)
+      if (row0 + j < m) epi_store(e, y, ldy, row0 + j, col, epi_tail(e, v[j], row0 + j, col));
+  }
 }
 
 __device__ __forceinline__ void epi_add_res32(const __half* res, int64_t off, int col0, int n, int vec, float* acc32) {

@@ -760,11 +760,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           else tmem_ld32(t_addr + c * kChunk, r);
           tmem_ld_wait();
           if (col_ok) {
+            float f[kChunk];
 #pragma unroll
-            for (int j = 0; j < kChunk; ++j) {
-              const int row = c * kChunk + j;
-              if (row < a.m) epi_store(a.epi, a.y, a.ldy, row, col, epi_tail(a.epi, __uint_as_float(r[j]) + bias, row, col));
-            }
+            for (int j = 0; j < kChunk; ++j) f[j] = __uint_as_float(r[j]) + bias;
+            epi_store_column<kChunk>(a.epi, a.y, a.ldy, c * kChunk, a.m, col, f);
           }
         }
         tc_fence_before();
@@ -843,15 +842,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               }
             }
             if (col_ok) {
+              float o[4 * G];
 #pragma unroll
               for (int j = 0; j < G; ++j) {
-                const float o[4] = {sum4[j].x, sum4[j].y, sum4[j].z, sum4[j].w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const int row = (g0 + j) * 4 + i;
-                  if (row < a.m) epi_store(a.epi, a.y, a.ldy, row, col, epi_tail(a.epi, o[i] + bias, row, col));
-                }
+                o[4 * j] = sum4[j].x + bias; o[4 * j + 1] = sum4[j].y + bias;
+                o[4 * j + 2] = sum4[j].z + bias; o[4 * j + 3] = sum4[j].w + bias;
               }
+              epi_store_column<4 * G>(a.epi, a.y, a.ldy, g0 * 4, a.m, col, o);
             }
           }
         }
