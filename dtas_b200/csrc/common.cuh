@@ -136,6 +136,8 @@ int launch_cast(const void* a, void* out, int64_t n, int src, int dst, const Dev
                 cudaStream_t st, int bucket);
 int launch_add(const void* a, const void* b, void* out, int64_t n, int dt, const DeviceCtx* ctx,
                cudaStream_t st, int bucket);
+int launch_add_residuals(void* y, const void* res1, const void* res2, int64_t n, const DeviceCtx* ctx,
+                         cudaStream_t st, int bucket);   // y += res1 (+ res2), fp16, in place
 int launch_copy(const void* a, void* out, int64_t nbytes, const DeviceCtx* ctx, cudaStream_t st,
                 int bucket);
 const char* ew_variant_name(const char* op, int64_t m, int64_t n_cols, const DeviceCtx* ctx);

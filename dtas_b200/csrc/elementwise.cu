@@ -112,6 +112,38 @@ struct AddF16 {
   __device__ __forceinline__ void scalar(int64_t i) const { o[i] = __hadd(a[i], b[i]); }
 };
 
+// out = a + b (+ c), summed in fp32 and rounded once: the residual adds behind a large GEMM when
+// they run as their own pass (launch_add_residuals).  `out` may be `a`.
+struct AddResF16 {
+  static constexpr int kLoads = 3;
+  static constexpr int kVec = 8;
+  const __half *a, *b, *c;   // c may be null
+  __half* o;
+  struct Reg { uint4 x, y, z; };
+  template <bool H>
+  __device__ __forceinline__ void load(Reg& r, int64_t v) const {
+    r.x = ld_stream<H>(reinterpret_cast<const uint4*>(a) + v);
+    r.y = ld_stream<H>(reinterpret_cast<const uint4*>(b) + v);
+    r.z = c != nullptr ? ld_stream<H>(reinterpret_cast<const uint4*>(c) + v) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  static __device__ __forceinline__ uint32_t add3(uint32_t p, uint32_t q, uint32_t t) {
+    const float2 fp = unpack_half2(p), fq = unpack_half2(q), ft = unpack_half2(t);
+    return pack_half2_rn(fp.x + fq.x + ft.x, fp.y + fq.y + ft.y);
+  }
+  template <bool H>
+  __device__ __forceinline__ void store(const Reg& r, int64_t v) const {
+    uint4 w;
+    w.x = add3(r.x.x, r.y.x, r.z.x);
+    w.y = add3(r.x.y, r.y.y, r.z.y);
+    w.z = add3(r.x.z, r.y.z, r.z.z);
+    w.w = add3(r.x.w, r.y.w, r.z.w);
+    st_stream<H>(reinterpret_cast<uint4*>(o) + v, w);
+  }
+  __device__ __forceinline__ void scalar(int64_t i) const {
+    o[i] = __float2half_rn(__half2float(a[i]) + __half2float(b[i]) + (c != nullptr ? __half2float(c[i]) : 0.f));
+  }
+};
+
 struct AddF32 {
   static constexpr int kLoads = 2;   // 16-byte loads per vector
   static constexpr int kVec = 4;
@@ -304,6 +336,13 @@ int launch_add(const void* a, const void* b, void* out, int64_t n, int dt, const
                        bucket, "add_i8");
   }
   DTAS_FAIL(DTAS_EUNSUPPORTED, "add: unsupported dtype %d", dt);
+}
+
+int launch_add_residuals(void* y, const void* res1, const void* res2, int64_t n, const DeviceCtx* ctx,
+                         cudaStream_t st, int bucket) {
+  const bool al = aligned16(y) && aligned16(res1) && (res2 == nullptr || aligned16(res2));
+  return launch_ew(AddResF16{(const __half*)y, (const __half*)res1, (const __half*)res2, (__half*)y}, n, al, ctx, st,
+                   bucket, "add_residuals_f16");
 }
 
 int launch_copy(const void* a, void* out, int64_t nbytes, const DeviceCtx* ctx, cudaStream_t st,

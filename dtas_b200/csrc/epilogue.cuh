@@ -29,10 +29,51 @@ struct Epilogue {
 };
 
 #ifdef __CUDACC__
-// x * (0.5 + 0.5 * erf(x / sqrt(2))): the erf form the reference's workload uses (before_dl.py:272-318).
-// Not inlined: the epilogues are unrolled over 16-32 elements, and as many copies of erff in
-// line made the kernels slower for everyone (instruction fetch), GELU or not.
-static __device__ __noinline__ float gelu_erf(float t) { return t * (0.5f + 0.5f * erff(t * 0.70710678118654757f)); }
+// GELU, erf form: x * (0.5 + 0.5 * erf(x / sqrt(2))), as the reference's workload spells it
+// (before_dl.py:272-318).  erf by the rational approximation 7.1.26 of Abramowitz & Stegun,
+//   erf(z) = 1 - (a1 t + ... + a5 t^5) exp(-z^2),  t = 1 / (1 + p z),  z >= 0,
+// |error| <= 1.5e-7 in exact arithmetic and ~5e-7 here: three orders of magnitude under the fp16
+// rounding of the result.  It is branch-free, and it is written for N elements side by side,
+// stage by stage: the four epilogue warps of a CTA have a scheduler each, so nothing but
+// instruction-level parallelism hides the ~100-cycle dependent chain of one element (with a
+// per-element erff the epilogue of a 256 x 256 tile took longer than its main loop at K = 2560).
+__device__ __forceinline__ float epi_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float epi_rcp(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+template <int N>
+__device__ __forceinline__ void gelu_erf_n(float* v) {
+  float z[N], t[N], e[N], p[N];
+#pragma unroll
+  for (int j = 0; j < N; ++j) z[j] = fabsf(v[j]) * 0.70710678118654757f;
+#pragma unroll
+  for (int j = 0; j < N; ++j) t[j] = epi_rcp(fmaf(0.3275911f, z[j], 1.0f));
+#pragma unroll
+  for (int j = 0; j < N; ++j) e[j] = epi_ex2(-1.4426950408889634f * z[j] * z[j]);
+#pragma unroll
+  for (int j = 0; j < N; ++j) p[j] = fmaf(1.061405429f, t[j], -1.453152027f);
+#pragma unroll
+  for (int j = 0; j < N; ++j) p[j] = fmaf(p[j], t[j], 1.421413741f);
+#pragma unroll
+  for (int j = 0; j < N; ++j) p[j] = fmaf(p[j], t[j], -0.284496736f);
+#pragma unroll
+  for (int j = 0; j < N; ++j) p[j] = fmaf(p[j], t[j], 0.254829592f);
+#pragma unroll
+  for (int j = 0; j < N; ++j) {
+    const float erf_abs = fmaf(-p[j] * t[j], e[j], 1.0f);            // erf(|x| / sqrt(2))
+    v[j] = v[j] * fmaf(0.5f, copysignf(erf_abs, v[j]), 0.5f);
+  }
+}
+__device__ __forceinline__ float gelu_erf(float x) {
+  gelu_erf_n<1>(&x);
+  return x;
+}
 
 // What follows the bias: activation, then the residuals.
 __device__ __forceinline__ float epi_tail(const Epilogue& e, float t, int64_t row, int col) {
@@ -63,9 +104,57 @@ __device__ __forceinline__ void epi_store_column(const Epilogue& e, void* y, int
     for (int j = 0; j < COUNT; ++j)
       if (row0 + j < m) yc[(int64_t)(row0 + j) * ldy] = __float2half_rn(v[j]);
   } else {
+    // all residual values first, then the stores: a store in between would make every row wait for
+    // its own loads (the compiler cannot move loads over stores that might alias)
+    float r1[COUNT], r2[COUNT];
+#pragma unroll
+    for (int j = 0; j < COUNT; ++j) {
+      const bool on = row0 + j < m;
+      r1[j] = (on && e.res1 != nullptr) ? __half2float(e.res1[(int64_t)(row0 + j) * e.ldr + col]) : 0.f;
+      r2[j] = (on && e.res2 != nullptr) ? __half2float(e.res2[(int64_t)(row0 + j) * e.ldr + col]) : 0.f;
+    }
+    float t[COUNT];
+#pragma unroll
+    for (int j = 0; j < COUNT; ++j) t[j] = v[j];
+    if (e.act == DTAS_ACT_GELU) {
+      constexpr int kGroup = COUNT % 8 == 0 ? 8 : COUNT;
+#pragma unroll
+      for (int g = 0; g < COUNT; g += kGroup) gelu_erf_n<kGroup>(t + g);
+    }
 #pragma unroll
     for (int j = 0; j < COUNT; ++j)
-      if (row0 + j < m) epi_store(e, y, ldy, row0 + j, col, epi_tail(e, v[j], row0 + j, col));
+      if (row0 + j < m) epi_store(e, y, ldy, row0 + j, col, (t[j] + r1[j]) + r2[j]);
+  }
+}
+
+// Residual values of one 32-column chunk of one row, fetched ahead of use: 4 x 16 bytes per residual.
+struct ResChunk {
+  uint4 v[2][4];
+};
+// Whether chunk col0 .. col0+31 of a row can be fetched with 16-byte loads (else it is read in place).
+__device__ __forceinline__ bool epi_can_prefetch(const Epilogue& e, int col0, int n) {
+  return e.res1 != nullptr && e.vec_res && col0 + 32 <= n;
+}
+__device__ __forceinline__ void epi_prefetch_res32(const Epilogue& e, int64_t row, int col0, ResChunk& r) {
+  const uint4* s1 = reinterpret_cast<const uint4*>(e.res1 + row * e.ldr + col0);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) r.v[0][q] = s1[q];
+  if (e.res2 != nullptr) {
+    const uint4* s2 = reinterpret_cast<const uint4*>(e.res2 + row * e.ldr + col0);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) r.v[1][q] = s2[q];
+  }
+}
+__device__ __forceinline__ void epi_add_vec32(const uint4* v, float* acc32) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v[q]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(h[i]);
+      acc32[8 * q + 2 * i] += f.x;
+      acc32[8 * q + 2 * i + 1] += f.y;
+    }
   }
 }
 
@@ -91,9 +180,10 @@ __device__ __forceinline__ void epi_add_res32(const __half* res, int64_t off, in
 }
 
 // Finishes 32 consecutive output columns col0 .. col0+31 of one row held in acc32 (fp32 dot
-// products) and stores them.  vec_store: 16-byte stores into Y rows are aligned.
+// products) and stores them.  vec_store: 16-byte stores into Y rows are aligned.  `pre`, when
+// given, holds the residual values of this chunk fetched earlier (epi_prefetch_res32).
 __device__ __forceinline__ void epi_store_row32(const Epilogue& e, void* y, int64_t ldy, int vec_store, int64_t row,
-                                                int col0, int n, float* acc32) {
+                                                int col0, int n, float* acc32, const ResChunk* pre = nullptr) {
   if (e.bias != nullptr) {
 #pragma unroll
     for (int j = 0; j < 32; ++j)
@@ -101,10 +191,15 @@ __device__ __forceinline__ void epi_store_row32(const Epilogue& e, void* y, int6
   }
   if (e.act == DTAS_ACT_GELU) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) acc32[j] = gelu_erf(acc32[j]);
+    for (int g = 0; g < 32; g += 8) gelu_erf_n<8>(acc32 + g);
   }
-  if (e.res1 != nullptr) epi_add_res32(e.res1, row * e.ldr, col0, n, e.vec_res, acc32);
-  if (e.res2 != nullptr) epi_add_res32(e.res2, row * e.ldr, col0, n, e.vec_res, acc32);
+  if (pre != nullptr) {
+    epi_add_vec32(pre->v[0], acc32);
+    if (e.res2 != nullptr) epi_add_vec32(pre->v[1], acc32);
+  } else {
+    if (e.res1 != nullptr) epi_add_res32(e.res1, row * e.ldr, col0, n, e.vec_res, acc32);
+    if (e.res2 != nullptr) epi_add_res32(e.res2, row * e.ldr, col0, n, e.vec_res, acc32);
+  }
   const bool full = vec_store && col0 + 32 <= n;
   if (!e.out_f32) {
     __half* yrow = static_cast<__half*>(y) + row * ldy;

@@ -428,17 +428,26 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int col_base = nt * BN;
 
       if (n_parts == 1) {
+        // Residual rows are fetched two chunks ahead of their use, so that their latency is not
+        // paid once per chunk.
+        ResChunk r_next, r_after;
+        if (row_ok && epi_can_prefetch(a.epi, col_base, a.n)) epi_prefetch_res32(a.epi, row, col_base, r_next);
+        if (row_ok && BN > 32 && epi_can_prefetch(a.epi, col_base + 32, a.n)) epi_prefetch_res32(a.epi, row, col_base + 32, r_after);
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
           tmem_ld32(t_addr + c * 32, r);
-          tmem_ld_wait();
           const int col0 = col_base + c * 32;
+          const ResChunk r_now = r_next;
+          r_next = r_after;
+          if (row_ok && c + 2 < BN / 32 && epi_can_prefetch(a.epi, col0 + 64, a.n)) epi_prefetch_res32(a.epi, row, col0 + 64, r_after);
+          tmem_ld_wait();
           if (row_ok && col0 < a.n) {
             float f[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
-            epi_store_row32(a.epi, a.y, a.ldy, a.vec_store, row, col0, a.n, f);
+            epi_store_row32(a.epi, a.y, a.ldy, a.vec_store, row, col0, a.n, f,
+                            epi_can_prefetch(a.epi, col0, a.n) ? &r_now : nullptr);
           }
         }
         tc_fence_before();
@@ -483,10 +492,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (is_last) {
           __threadfence();
           if (row_ok) {
-            // 64 columns and two slots per batch: 32 independent 16-byte loads in flight per
-            // thread, one L2 round trip per 64 columns and slot pair; slots are added in slot
-            // order = K order, whatever the arrival order
-            constexpr int W = 64;
+            // 32 columns and two slots per batch: 16 independent 16-byte loads in flight per
+            // thread (twice that measured no faster and costs 64 registers); slots are added in
+            // slot order = K order, whatever the arrival order
+            constexpr int W = 32;
             const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 1
             for (int c = 0; c < BN / W; ++c) {
@@ -516,7 +525,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 }
               }
               epi_store_row32(a.epi, a.y, a.ldy, a.vec_store, row, col0, a.n, acc);
-              if (col0 + 32 < a.n) epi_store_row32(a.epi, a.y, a.ldy, a.vec_store, row, col0 + 32, a.n, acc + 32);
             }
           }
         }
@@ -1094,17 +1102,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       const bool row_ok = row < a.m;
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kPairBN);
       const int col_base = nt * kPairBN;
+      // Residual rows are fetched two chunks ahead of their use.
+      ResChunk r_next, r_after;
+      if (row_ok && epi_can_prefetch(a.epi, col_base, a.n)) epi_prefetch_res32(a.epi, row, col_base, r_next);
+      if (row_ok && epi_can_prefetch(a.epi, col_base + 32, a.n)) epi_prefetch_res32(a.epi, row, col_base + 32, r_after);
 #pragma unroll 1
       for (int c = 0; c < kPairBN / 32; ++c) {
         uint32_t r[32];
         tmem_ld32(t_addr + c * 32, r);
-        tmem_ld_wait();
         const int col0 = col_base + c * 32;
+        const ResChunk r_now = r_next;
+        r_next = r_after;
+        if (row_ok && c + 2 < kPairBN / 32 && epi_can_prefetch(a.epi, col0 + 64, a.n)) epi_prefetch_res32(a.epi, row, col0 + 64, r_after);
+        tmem_ld_wait();
         if (row_ok && col0 < a.n) {
           float f[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
-          epi_store_row32(a.epi, a.y, a.ldy, a.vec_store, row, col0, a.n, f);
+          epi_store_row32(a.epi, a.y, a.ldy, a.vec_store, row, col0, a.n, f,
+                          epi_can_prefetch(a.epi, col0, a.n) ? &r_now : nullptr);
         }
       }
       tc_fence_before();

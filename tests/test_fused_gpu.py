@@ -88,6 +88,24 @@ def test_gemm_fused_tails_every_kernel(cuda_device, tail, bn, split):
     util.assert_matmul_close(got, expected(host, t).astype(np.float32), what)
 
 
+@pytest.mark.parametrize("tail", ["res2", "res1_nobias"])
+def test_gemm_fused_residuals_as_own_pass(cuda_device, tail):
+    """From m = 2048 up (contiguous fp16 output) the residuals are added by a streaming pass behind
+    the GEMM instead of inside its epilogue; a column slab keeps them in the epilogue."""
+    t = TAILS[tail]
+    m, n, k = 2100, 264, 520
+    host, dev = operands(m, n, k, t, 1700, cuda_device)
+    want = expected(host, t).astype(np.float32)
+    before = _abi.launch_count()
+    got = run_gemm(dev, t, m, n, cuda_device)
+    assert _abi.launch_count() - before == 2
+    util.assert_matmul_close(got, want, f"gemm {tail} m={m} own pass")
+    before = _abi.launch_count()
+    got = run_gemm(dev, t, m, n, cuda_device, ld=n + 8)
+    assert _abi.launch_count() - before == 1
+    util.assert_matmul_close(got, want, f"gemm {tail} m={m} slab")
+
+
 def test_gemm_fused_unaligned_falls_back(cuda_device):
     """K not a multiple of 8 (no TMA) and an odd N (no 16-byte stores or residual loads)."""
     t = TAILS["res2"]
