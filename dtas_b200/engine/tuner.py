@@ -151,6 +151,8 @@ class Engine:
         copies = rotation_for(2 * n * k, max_copies=8)
         ws = [(torch.randn((n, k), device=device, dtype=torch.float32) * 0.02).to(torch.float16) for _ in range(copies)]
         best = {}
+        if not hasattr(self, "last_search_details"):
+            self.last_search_details = []    # every candidate's time, for reports (retune --details)
         try:
             for rt in ranges:
                 r = rt[0]
@@ -171,6 +173,9 @@ class Engine:
                 results.sort()
                 us, bn, split, variant = results[0]
                 best[rt] = (config_for("gemm", variant), bn, split, us)
+                self.last_search_details.append({"n": n, "k": k, "m_lo": r.start, "m_hi": r.end, "sampled_m": ms,
+                                                 "candidates": [{"us": round(u, 2), "bn": b, "split": sp, "variant": v}
+                                                                for u, b, sp, v in results]})
                 ops.poll_status(device.index or 0)
         finally:
             _abi.check(lib.dtas_gemm_set_override(0, 0))

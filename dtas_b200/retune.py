@@ -45,6 +45,7 @@ def main():
     ap.add_argument("--out", required=True)
     ap.add_argument("--device", type=int, default=0)
     ap.add_argument("--min-repeat-ms", type=float, default=10.0)
+    ap.add_argument("--details", default=None, help="also write every candidate's time per range to this JSON file")
     a = ap.parse_args()
     shapes = [tuple(int(v) for v in s.lower().split("x")) for s in a.shape] or default_shapes()
     set_log_level(0)
@@ -75,6 +76,9 @@ def main():
     with open(a.out, "w") as f:
         json.dump(rec, f, indent=1)
     print(f"wrote {a.out}")
+    if a.details:
+        with open(a.details, "w") as f:
+            json.dump(eng.last_search_details, f, indent=1)
 
 
 if __name__ == "__main__":
