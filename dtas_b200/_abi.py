@@ -69,11 +69,12 @@ def lib():
     """Loads lib/libdtas_b200.so once and installs the prototypes."""
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
+        path = os.environ.get("DTAS_B200_LIB") or LIB_PATH    # another build of the same ABI, e.g. for A/B timing
+        if not os.path.exists(path):
             raise RuntimeError(
-                f"{LIB_PATH} is missing: build it with `python -m dtas_b200.build` "
+                f"{path} is missing: build it with `python -m dtas_b200.build` "
                 "(or __graft_entry__.build()); dtas_b200 has no fallback path")
-        handle = ctypes.CDLL(LIB_PATH)
+        handle = ctypes.CDLL(path)
         for name, (restype, argtypes) in PROTOTYPES.items():
             fn = getattr(handle, name)  # AttributeError if the library lacks a declared symbol
             fn.restype = restype

@@ -179,6 +179,41 @@ __device__ __forceinline__ void epi_add_res32(const __half* res, int64_t off, in
   }
 }
 
+// True when the tail is nothing but an optional bias and an fp16 store: the path every plain GEMM
+// takes, kept free of the machinery below.
+__device__ __forceinline__ bool epi_is_plain(const Epilogue& e) {
+  return e.res1 == nullptr && e.act == DTAS_ACT_NONE && !e.out_f32;
+}
+// The plain tail for 32 consecutive columns of one row, from the raw accumulator words.
+__device__ __forceinline__ void epi_store_row32_plain(const __half* bias, __half* yrow, int vec_store, int col0, int n,
+                                                      uint32_t* r) {
+  if (bias != nullptr) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < n) r[j] = __float_as_uint(__uint_as_float(r[j]) + __half2float(bias[col0 + j]));
+  }
+  if (vec_store && col0 + 32 <= n) {
+    uint4* dst = reinterpret_cast<uint4*>(yrow + col0);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint4 v;
+      __half2 h0 = __floats2half2_rn(__uint_as_float(r[8 * q + 0]), __uint_as_float(r[8 * q + 1]));
+      __half2 h1 = __floats2half2_rn(__uint_as_float(r[8 * q + 2]), __uint_as_float(r[8 * q + 3]));
+      __half2 h2 = __floats2half2_rn(__uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5]));
+      __half2 h3 = __floats2half2_rn(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7]));
+      v.x = *reinterpret_cast<uint32_t*>(&h0);
+      v.y = *reinterpret_cast<uint32_t*>(&h1);
+      v.z = *reinterpret_cast<uint32_t*>(&h2);
+      v.w = *reinterpret_cast<uint32_t*>(&h3);
+      dst[q] = v;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < n) yrow[col0 + j] = __float2half_rn(__uint_as_float(r[j]));
+  }
+}
+
 // Finishes 32 consecutive output columns col0 .. col0+31 of one row held in acc32 (fp32 dot
 // products) and stores them.  vec_store: 16-byte stores into Y rows are aligned.  `pre`, when
 // given, holds the residual values of this chunk fetched earlier (epi_prefetch_res32).

@@ -428,6 +428,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int col_base = nt * BN;
 
       if (n_parts == 1) {
+        if (epi_is_plain(a.epi)) {
+          __half* yrow = static_cast<__half*>(a.y) + (int64_t)row * a.ldy;
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32(t_addr + c * 32, r);
+            tmem_ld_wait();
+            const int col0 = col_base + c * 32;
+            if (row_ok && col0 < a.n) epi_store_row32_plain(a.epi.bias, yrow, a.vec_store, col0, a.n, r);
+          }
+        } else {
         // Residual rows are fetched two chunks ahead of their use, so that their latency is not
         // paid once per chunk.
         ResChunk r_next, r_after;
@@ -449,6 +460,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             epi_store_row32(a.epi, a.y, a.ldy, a.vec_store, row, col0, a.n, f,
                             epi_can_prefetch(a.epi, col0, a.n) ? &r_now : nullptr);
           }
+        }
         }
         tc_fence_before();
         __syncwarp();
@@ -1102,6 +1114,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       const bool row_ok = row < a.m;
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kPairBN);
       const int col_base = nt * kPairBN;
+      if (epi_is_plain(a.epi)) {
+        __half* yrow = static_cast<__half*>(a.y) + (int64_t)row * a.ldy;
+#pragma unroll 1
+        for (int c = 0; c < kPairBN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_addr + c * 32, r);
+          tmem_ld_wait();
+          const int col0 = col_base + c * 32;
+          if (row_ok && col0 < a.n) epi_store_row32_plain(a.epi.bias, yrow, a.vec_store, col0, a.n, r);
+        }
+      } else {
       // Residual rows are fetched two chunks ahead of their use.
       ResChunk r_next, r_after;
       if (row_ok && epi_can_prefetch(a.epi, col_base, a.n)) epi_prefetch_res32(a.epi, row, col_base, r_next);
@@ -1122,6 +1145,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
           epi_store_row32(a.epi, a.y, a.ldy, a.vec_store, row, col0, a.n, f,
                           epi_can_prefetch(a.epi, col0, a.n) ? &r_now : nullptr);
         }
+      }
       }
       tc_fence_before();
       __syncwarp();
