@@ -473,8 +473,8 @@ def run_gpu(args):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant GEMM
 # (m=8192, n=22016, k=4096, two-CTA kernel), from the ncu capture summarised in
-# profiles/gemm_pair_kernel_m8192_n22016_k4096.md (1032.2 MB read + 346.1 MB written).
-GEMM_NCU_TRAFFIC_BYTES = 1378254592
+# profiles/gemm_pair_kernel_m8192_n22016_k4096.md (865.4 MB read + 344.5 MB written).
+GEMM_NCU_TRAFFIC_BYTES = 1209894144
 
 
 # -----------------------------------------------------------------------------------------
