@@ -75,6 +75,12 @@ class PackedOp:
         if s.op == "rms_norm":
             return ops.rms_norm(args[0], args[1], out, eps=s.eps)
         if s.op == "softmax":
+            if s.cols == 0:      # symbolic reduction length: [..., m] -> rows x m
+                if tuple(args[0].shape) != tuple(out.shape):
+                    raise _abi.DtasError(_abi.EINVAL, f"{self.name}: input {tuple(args[0].shape)} and output {tuple(out.shape)} differ")
+                cols = int(out.shape[-1])
+                ops.softmax(args[0].reshape(-1, cols), out.view(-1, cols))
+                return out
             return ops.softmax(args[0], out)
         if s.op == "layer_norm":
             return ops.layer_norm(args[0], args[1], args[2], out, eps=s.eps)

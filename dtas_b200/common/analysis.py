@@ -178,6 +178,10 @@ def spec_from_prim_func(func, name):
                     return OpSpec(name, "gemm", "float16", str(out.dtype), upper=upper, **kw)
     # general reduction over the last dim
     calls, nodes = _calls_and_ops(func.body)
+    if any("exp" in c for c in calls) and "Max" in nodes and _static(ins[0].shape[-1]) is None:
+        # softmax over a symbolic last dim (the attention scores [1, heads, n, m] of
+        # experiment/ModelIR/dolly-v2-3b-q0f16/before_dl.py:756-800): cols = 0 means "read it from the tensor"
+        return OpSpec(name, "softmax", str(ins[0].dtype), str(out.dtype), cols=0, upper=upper)
     h = last_dim(ins[0])
     eps = 0.0
     from tvm.tir import stmt_functor

@@ -71,7 +71,12 @@ class Engine:
         if len(func_info.dynamic_args) == 0:
             return [()]
         range_lists = []
-        for dyn in func_info.dynamic_args:
+        dyn_args = func_info.dynamic_args
+        if func_info.spec.op == "softmax" and func_info.spec.cols == 0:
+            # rows and reduction length are both symbolic: the table is keyed on the row-like dim, the
+            # kernel reads the reduction length from the tensor and picks its layout per call
+            dyn_args = dyn_args[:1]
+        for dyn in dyn_args:
             upper = func_info.spec.upper or self.upper_bound.get(dyn) or DEFAULT_UPPER_BOUND
             self.upper_bound[dyn] = upper
             range_lists.append(generate_range_list(dyn, 1, upper, range_div_factor))
@@ -114,7 +119,9 @@ class Engine:
         range_to_config: Dict[Tuple[Range], Config] = {}
         for rt in self.gen_range_tuples(info, range_div_factor):
             m = rt[0].end if rt else 1
-            variant = _abi.variant_of(spec.op, m, spec.cols, spec.k, getattr(arch, "dev_id", -1))
+            # a softmax with a symbolic reduction length is described at a nominal length; the kernel
+            # picks its layout from the actual one at call time
+            variant = _abi.variant_of(spec.op, m, spec.cols or 1024, spec.k, getattr(arch, "dev_id", -1))
             range_to_config[rt] = config_for(spec.kind, variant)
         merged = self.merge_same_configs(range_to_config)
         table, stmt = self.get_index_table(merged, range_div_factor)

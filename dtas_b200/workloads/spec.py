@@ -20,7 +20,8 @@ class OpSpec:
     op        : "cast" | "add" | "copy" | "rms_norm" | "softmax" | "layer_norm" | "gemv" | "gemm"
     in_dtype  : dtype of the streamed input ("float16" | "float32" | "int8")
     out_dtype : dtype of the output
-    cols      : static row length H for elementwise / reduction ops; N for gemv / gemm
+    cols      : static row length H for elementwise / reduction ops (0 for a softmax whose reduction
+                length is symbolic too: it is read from the tensor at call time); N for gemv / gemm
     k         : reduction length K for gemv / gemm
     eps       : epsilon of the norm ops
     bias      : gemv / gemm take a bias argument

@@ -243,6 +243,25 @@ def gemv(N, K, name="gemv"):
     return func
 
 
+def softmax_dynamic(heads=32, dtype="float32", name="fused_softmax_cast"):
+    """Softmax over a symbolic last dim, cast to fp16: the attention-score form
+    fused_softmax_cast3 of experiment/ModelIR/dolly-v2-3b-q0f16/before_dl.py:756-800
+    (x [1, heads, n, m] -> max over m, exp(x - max), sum, divide, cast), two symbolic dims."""
+    _tvm()
+    from tvm import te, tir
+    n, m = te.var("n", "int64"), te.var("m", "int64")
+    shape = (1, heads, n, m)
+    x = te.placeholder(shape, dtype, name="lv_scores")
+    k1 = te.reduce_axis((0, m), name="k")
+    mx = te.compute((1, heads, n), lambda i0, i1, i2: te.max(x[i0, i1, i2, k1].astype("float32"), axis=k1), name="T_softmax_maxelem")
+    ex = te.compute(shape, lambda i0, i1, i2, i3: tir.exp(x[i0, i1, i2, i3].astype("float32") - mx[i0, i1, i2]), name="T_softmax_exp")
+    k2 = te.reduce_axis((0, m), name="k")
+    sm = te.compute((1, heads, n), lambda i0, i1, i2: te.sum(ex[i0, i1, i2, k2], axis=k2), name="T_softmax_expsum")
+    nr = te.compute(shape, lambda i0, i1, i2, i3: ex[i0, i1, i2, i3] / sm[i0, i1, i2], name="T_softmax_norm")
+    out = te.compute(shape, lambda i0, i1, i2, i3: nr[i0, i1, i2, i3].astype("float16"), name="compute")
+    return te.create_prim_func([x, out]).with_attr("global_symbol", name)
+
+
 def matmul_fused(N, K, dynamic=True, bias=True, act="", residuals=0, out_dtype="float16", name="fused_NT_matmul"):
     """The fused matmul forms of the reference's model workloads
     (experiment/ModelIR/dolly-v2-3b-q0f16/before_dl.py: fused_NT_matmul_add :552,

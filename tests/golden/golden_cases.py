@@ -26,6 +26,8 @@ CASES = {
     "softmax_m33": dict(op="softmax", dtype="float16", H=4096, m=33, seed=2000),
     "softmax_f32_m4": dict(op="softmax", dtype="float32", H=1000, m=4, seed=2030),
     "layer_norm_f32_m3": dict(op="layer_norm", dtype="float32", H=2560, m=3, eps=1e-5, seed=2040),
+    "softmax_dyn_f32_h32_n5_m77": dict(op="softmax_dyn", dtype="float32", heads=32, n=5, m=77, seed=2050),
+    "softmax_dyn_f32_h32_n3_m256": dict(op="softmax_dyn", dtype="float32", heads=32, n=3, m=256, seed=2060),
     # gemv: the four Llama-2-7B shapes ------------------------------------------------------
     "gemv_4096_4096": dict(op="gemv", N=4096, K=4096, seed=3000),
     "gemv_11008_4096": dict(op="gemv", N=11008, K=4096, seed=3010),
@@ -70,6 +72,9 @@ def make_inputs(case):
     if op == "softmax":
         m, h = case["m"], case["H"]
         return [nd((1, m, h), 0, case["dtype"])], np.zeros((1, m, h), "float16")
+    if op == "softmax_dyn":
+        shape = (1, case["heads"], case["n"], case["m"])
+        return [nd(shape, 0, case["dtype"], scale=3.0)], np.zeros(shape, "float16")
     if op == "layer_norm":
         m, h = case["m"], case["H"]
         return [nd((1, m, h), 0, case["dtype"]), nd((h,), 1, "float32", scale=0.1, mean=1.0),

@@ -47,6 +47,8 @@ def prim_func(case):
         return td.softmax(p["H"], p["dtype"])
     if op == "layer_norm":
         return td.layer_norm(p["H"], p["dtype"], p["eps"])
+    if op == "softmax_dyn":
+        return td.softmax_dynamic(p["heads"], p["dtype"])
     if op == "gemm":
         return td.gemm_nt(p["N"], p["K"])
     if op == "gemv":

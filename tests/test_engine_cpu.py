@@ -145,3 +145,20 @@ def test_classification_of_fused_matmul_forms():
     rt = Engine(1, True, None).tune_module(mod, arch=arch.B200(0), range_div_factor=256)
     assert rt["ffn_up"].spec.act == "gelu" and rt["attn_out"].spec.residuals == 2
     assert OpSpec.from_dict(rt.record["functions"]["attn_out"]["spec"]).out_dtype == "float32"
+
+
+def test_classification_of_softmax_with_two_symbolic_dims():
+    """fused_softmax_cast3 of the reference's model IR: [1, 32, n, m], softmax over the symbolic m."""
+    td = pytest.importorskip("dtas_b200.workloads.tir_defs")
+    try:
+        td._tvm()
+    except ImportError:
+        pytest.skip("no TVM in this environment")
+    info = FuncInfo(td.softmax_dynamic(32, "float32"), "attn_softmax")
+    assert info.kind == FuncKind.kFunc_Reduction and info.spec.op == "softmax"
+    assert (info.spec.cols, info.spec.in_dtype, info.spec.out_dtype) == (0, "float32", "float16")
+    assert info.dynamic_args == ["n", "m"]
+    dtas_b200.set_log_level(0)
+    rt = Engine(1, True, None).tune_module(td.make_module({"attn_softmax": td.softmax_dynamic(32, "float32")}, upper_bound=2048),
+                                           arch=arch.B200(0), range_div_factor=256)
+    assert rt["attn_softmax"].spec.cols == 0

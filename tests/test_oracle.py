@@ -24,7 +24,7 @@ def run_oracle(case, ins):
         return oracle.copy(ins[0])
     if op == "rms_norm":
         return oracle.rms_norm(ins[0], ins[1], case["eps"])
-    if op == "softmax":
+    if op in ("softmax", "softmax_dyn"):
         return oracle.softmax(ins[0])
     if op == "layer_norm":
         return oracle.layer_norm(ins[0], ins[1], ins[2], case["eps"])

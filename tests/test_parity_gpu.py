@@ -390,6 +390,8 @@ def test_against_tvm_golden(cuda_device, name):
         ops.rms_norm(d[0], d[1], y, eps=case["eps"])
     elif op == "softmax":
         ops.softmax(d[0], y)
+    elif op == "softmax_dyn":
+        ops.softmax(d[0].view(-1, case["m"]), y.view(-1, case["m"]))
     elif op == "layer_norm":
         ops.layer_norm(d[0], d[1], d[2], y, eps=case["eps"])
     elif op == "gemv":
@@ -404,6 +406,24 @@ def test_against_tvm_golden(cuda_device, name):
         util.assert_matmul_close(got, want.astype(np.float32), name)
     else:
         util.assert_reduction_close(got, want, name, abs_floor=1e-6 if op == "layer_norm" else 0.0)
+
+
+@pytest.mark.parametrize("n,m", [(1, 1), (7, 77), (64, 1000), (128, 2048), (3, 40000)])
+def test_softmax_with_symbolic_reduction_length(cuda_device, n, m):
+    """The attention-score softmax of the reference's model IR: fp32 [1, 32, n, m] -> fp16, both n and m
+    symbolic (experiment/ModelIR/dolly-v2-3b-q0f16/before_dl.py:756-800), through one bound function."""
+    import dtas_b200
+    from dtas_b200 import Engine, arch
+    from dtas_b200.workloads import OpSpec
+    dtas_b200.set_log_level(0)
+    rt = Engine(1, True, None).tune_module([OpSpec("attn_softmax", "softmax", "float32", "float16", cols=0)],
+                                           arch=arch.B200(0), range_div_factor=256)
+    x = seeded_normal((1, 32, n, m), 7000 + m, "float32", scale=3.0)
+    y = torch.full((1, 32, n, m), 9.0, dtype=torch.float16, device=cuda_device)
+    rt["attn_softmax"](x.to(cuda_device), y)
+    got = np_of(y)
+    util.assert_reduction_close(got, oracle.softmax(x.numpy()).reshape(got.shape), f"softmax [1,32,{n},{m}]")
+    assert abs(float(got.astype(np.float64).sum()) - 32 * n) < 32 * n * 2e-3      # every row sums to one
 
 
 def test_engine_search_installs_measured_table(cuda_device, tmp_path):
