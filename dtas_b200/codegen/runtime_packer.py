@@ -11,8 +11,6 @@ dims, merged ranges, index table) stored as JSON in `work_dir`; reloading rebuil
 import json
 import os
 
-import torch
-
 from .. import _abi, ops
 from ..profiling import time_op
 from ..reference import torch_dtype

@@ -572,7 +572,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 // when the tile count is no multiple of the SM count.  Partial tiles are float4s of four
 // consecutive rows, laid out [tile][slot][row group][column], so that warps write and read
 // 512 contiguous bytes; the last CTA to arrive at a tile sums the slots in K order with
-// eight independent loads in flight per thread.
+// 16-32 independent loads in flight per thread.
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
   asm volatile(

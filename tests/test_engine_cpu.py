@@ -7,7 +7,7 @@ import pytest
 import dtas_b200
 from dtas_b200 import Engine, arch, load_module_from_file
 from dtas_b200.codegen.runtime_packer import MODULE_FILE
-from dtas_b200.common.analysis import FuncInfo, FuncKind, UnsupportedWorkload
+from dtas_b200.common.analysis import FuncInfo, FuncKind
 from dtas_b200.common.config import Config, Range, config_for, generate_range_list
 from dtas_b200.workloads import OpSpec, llama2_7b_specs
 

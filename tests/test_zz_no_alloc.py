@@ -9,7 +9,7 @@ other test.  It must pass alone in a fresh process and after the other tests.
 """
 import ctypes
 
-import numpy as np
+
 import pytest
 import torch
 
