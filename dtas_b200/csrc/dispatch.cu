@@ -342,8 +342,9 @@ int dtas_row_set_override(int threads_per_row) {
 }
 
 int dtas_gemv_set_override(int warps_per_row, int unroll) {
-  if (!(warps_per_row == 0 || warps_per_row == 1 || warps_per_row == 2 || warps_per_row == 4 || warps_per_row == 8))
-    DTAS_FAIL(DTAS_EINVAL, "gemv override: warps per row must be 0, 1, 2, 4 or 8");
+  if (!(warps_per_row == 0 || warps_per_row == 1 || warps_per_row == 2 || warps_per_row == 4 || warps_per_row == 8 ||
+        warps_per_row == 16))
+    DTAS_FAIL(DTAS_EINVAL, "gemv override: warps per row must be 0, 1, 2, 4, 8, or 16 for the streaming kernel");
   if (!(unroll == 0 || unroll == 4 || unroll == 8)) DTAS_FAIL(DTAS_EINVAL, "gemv override: unroll must be 0, 4 or 8");
   gemv_set_override(warps_per_row, unroll);
   return DTAS_OK;

@@ -11,6 +11,13 @@
 // L1/L2), accumulates 8 products per chunk in fp32, and the partials meet through warp
 // shuffles and one shared-memory hop.  WPR is chosen from K alone (pick_wpr).
 // Algorithmic bytes: 2*N*K + 2*K + 2*N.  Bound: HBM bandwidth.
+//
+// Second kernel, for weights that do not fit the first kernel's two short waves well
+// (gemv_f16_stream_kernel): one persistent CTA per SM owns a contiguous band of rows - a
+// contiguous slab of W - and a producer thread streams it row by row into a shared-memory
+// ring with bulk copies (one 8-22 KB copy per row, full DRAM pages, tens of KB in flight per
+// SM without a register), while eight consumer warps take a row each from the ring and
+// reduce it against x held in shared memory.  No second wave, no cross-CTA reduction.
 #include "common.cuh"
 
 namespace dtas {
@@ -113,6 +120,140 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Streaming kernel: bulk copies into a ring of whole rows.
+// ---------------------------------------------------------------------------------------
+constexpr int kStreamConsumers = 8;                       // consumer warps
+constexpr int kStreamThreads = 32 * (1 + kStreamConsumers);
+constexpr int ERR_GEMV_PRODUCER = 0x201, ERR_GEMV_CONSUMER = 0x202;
+
+__device__ __forceinline__ uint32_t sm_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void gv_mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void gv_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void gv_mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool gv_mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Bounded wait (about a second): records `code` in the status word and returns false.
+__device__ __noinline__ bool gv_mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+  for (int i = 0; i < 64; ++i)
+    if (gv_mbar_try_wait(bar, parity)) return true;
+  uint64_t t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (;;) {
+    for (int i = 0; i < 2048; ++i)
+      if (gv_mbar_try_wait(bar, parity)) return true;
+    uint64_t t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    if (t1 - t0 > 1000000000ull) {
+      atomicExch(status, code);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void gv_bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               :
+               : "r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+// Shared memory: x (k fp16), then STAGES row buffers of k fp16 each, then the barriers.
+// Stage s is always consumed by consumer warp s % 8 (STAGES is a multiple of 8).
+template <int STAGES>
+__global__ void __launch_bounds__(kStreamThreads, 1)
+    gemv_f16_stream_kernel(const __half* __restrict__ x, const __half* __restrict__ w, const Epilogue epi,
+                           void* __restrict__ y, int n, int k, int* status) {
+  static_assert(STAGES % kStreamConsumers == 0, "stage -> warp mapping");
+  extern __shared__ __align__(128) uint8_t gv_smem[];
+  const uint32_t row_bytes = (uint32_t)k * 2u;
+  uint8_t* x_s = gv_smem;
+  uint8_t* ring = gv_smem + row_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)STAGES * row_bytes);
+  const uint32_t bar0 = sm_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  const uint32_t x_bar = bar0 + 8u * (2 * STAGES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // this CTA's band of rows
+  const int r0 = (int)(((int64_t)blockIdx.x * n) / gridDim.x);
+  const int r1 = (int)(((int64_t)(blockIdx.x + 1) * n) / gridDim.x);
+  const int rows = r1 - r0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      gv_mbar_init(full_bar(s), 1);
+      gv_mbar_init(empty_bar(s), 1);
+    }
+    gv_mbar_init(x_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+  pdl_wait();
+  pdl_launch_dependents();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      gv_mbar_expect_tx(x_bar, row_bytes);
+      gv_bulk_load(sm_u32(x_s), x, row_bytes, x_bar);
+      bool ok = true;
+      for (int i = 0; i < rows && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t parity = (uint32_t)(i / STAGES) & 1u;
+        if (!gv_mbar_wait(empty_bar(s), parity ^ 1u, status, ERR_GEMV_PRODUCER)) { ok = false; break; }
+        gv_mbar_expect_tx(full_bar(s), row_bytes);
+        gv_bulk_load(sm_u32(ring + (size_t)s * row_bytes), w + (int64_t)(r0 + i) * k, row_bytes, full_bar(s));
+      }
+    }
+  } else {
+    const int cw = warp - 1;
+    const int n_chunks = k >> 3;
+    const uint4* xv = reinterpret_cast<const uint4*>(x_s);
+    bool ok = gv_mbar_wait(x_bar, 0u, status, ERR_GEMV_CONSUMER);
+    for (int i = cw; i < rows && ok; i += kStreamConsumers) {
+      const int s = i % STAGES;
+      const uint32_t parity = (uint32_t)(i / STAGES) & 1u;
+      if (!gv_mbar_wait(full_bar(s), parity, status, ERR_GEMV_CONSUMER)) { ok = false; break; }
+      const uint4* wv = reinterpret_cast<const uint4*>(ring + (size_t)s * row_bytes);
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      int c = lane;
+      for (; c + 96 < n_chunks; c += 128) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) acc[u] = dot8(wv[c + 32 * u], xv[c + 32 * u], acc[u]);
+      }
+      for (; c < n_chunks; c += 32) acc[0] = dot8(wv[c], xv[c], acc[0]);
+      float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      __syncwarp();                                   // every lane has read the stage
+      if (lane == 0) {
+        gv_mbar_arrive(empty_bar(s));
+        const int row = r0 + i;
+        epi_store(epi, y, 0, 0, row, epi_value(epi, sum, 0, row));
+      }
+    }
+  }
+}
+
 std::atomic<int> g_gemv_wpr{0}, g_gemv_unroll{0};
 
 // Warps per row and loads in flight per lane.  Measured on B200 over the Llama-2-7B shapes
@@ -130,6 +271,24 @@ inline int pick_wpr(int64_t n, int64_t k, int sm_count) {
   int wpr = 1;
   while (wpr < 8 && n_chunks / (wpr * 2) >= 128) wpr *= 2;
   return wpr;
+}
+
+// Ring depth of the streaming kernel for this shape, 0 = use the per-row kernel.  A row must fit a
+// stage (16 stages up to K = 5632, 8 up to K = 11264 in ~200 KB of shared memory).  Override code
+// 16 (dtas_gemv_set_override) forces the streaming kernel where it fits, 1/2/4/8 the per-row kernel.
+constexpr int kStreamSmemMax = 200 * 1024;
+constexpr bool kStreamByDefault = false;          // opt-in (override code 16) until its dispatch range is measured
+constexpr int64_t kStreamMinBytes = 16ll << 20;   // below that the per-row kernel's single wave is as good
+inline int pick_stream(int64_t n, int64_t k, int sm_count) {
+  (void)sm_count;
+  const int forced = g_gemv_wpr.load();
+  if (forced == 1 || forced == 2 || forced == 4 || forced == 8) return 0;
+  int stages = 0;
+  if ((1 + 16) * k * 2 + 33 * 8 + 8 <= kStreamSmemMax) stages = 16;
+  else if ((1 + 8) * k * 2 + 17 * 8 + 8 <= kStreamSmemMax) stages = 8;
+  if (stages == 0 || n < kStreamConsumers) return 0;
+  if (forced == 16) return stages;
+  return (kStreamByDefault && 2 * n * k >= kStreamMinBytes) ? stages : 0;
 }
 
 inline int pick_unroll(int wpr) {
@@ -157,6 +316,29 @@ int launch_gemv(const void* x, const void* w, const Epilogue& epi, void* y, int6
     launch_kernel(gemv_f16_scalar_kernel, grid, kThreads, 0, st, xp, wp, epi, y, (int)n, (int)k);
     return after_launch("gemv_f16_scalar_kernel");
   }
+  const int stream_stages = pick_stream(n, k, ctx->sm_count);
+  if (stream_stages > 0) {
+    const size_t smem = (size_t)(1 + stream_stages) * (size_t)k * 2 + (size_t)(2 * stream_stages + 1) * 8 + 8;
+    const int64_t bands = (n + kStreamConsumers - 1) / kStreamConsumers;      // at least a row per consumer warp
+    const unsigned grid = (unsigned)(bands < ctx->sm_count ? bands : ctx->sm_count);
+    int dev = 0;
+    DTAS_CUDA(cudaGetDevice(&dev));
+    static bool attr_set[2][64] = {{false}};
+    if (stream_stages == 16) {
+      if (dev < 64 && !attr_set[0][dev]) {
+        DTAS_CUDA(cudaFuncSetAttribute(gemv_f16_stream_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmemMax));
+        attr_set[0][dev] = true;
+      }
+      launch_kernel(gemv_f16_stream_kernel<16>, grid, kStreamThreads, smem, st, xp, wp, epi, y, (int)n, (int)k, ctx->status);
+    } else {
+      if (dev < 64 && !attr_set[1][dev]) {
+        DTAS_CUDA(cudaFuncSetAttribute(gemv_f16_stream_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmemMax));
+        attr_set[1][dev] = true;
+      }
+      launch_kernel(gemv_f16_stream_kernel<8>, grid, kStreamThreads, smem, st, xp, wp, epi, y, (int)n, (int)k, ctx->status);
+    }
+    return after_launch("gemv_f16_stream_kernel");
+  }
   const int wpr = pick_wpr(n, k, ctx->sm_count);
   const int rows_per_cta = kWarps / wpr;
   const unsigned grid = (unsigned)((n + rows_per_cta - 1) / rows_per_cta);
@@ -175,6 +357,11 @@ int launch_gemv(const void* x, const void* w, const Epilogue& epi, void* y, int6
 void gemv_variant_name(int64_t n, int64_t k, const DeviceCtx* ctx, char* buf, int len) {
   if (k % 8 != 0) {
     snprintf(buf, len, "gemv_scalar_warp_per_row");
+    return;
+  }
+  const int stages = pick_stream(n, k, ctx ? ctx->sm_count : 148);
+  if (stages > 0) {
+    snprintf(buf, len, "gemv_stream_rows_s%d", stages);
     return;
   }
   const int wpr = pick_wpr(n, k, ctx ? ctx->sm_count : 148);

@@ -176,8 +176,9 @@ int dtas_ew_set_override(int unroll, int ctas_per_sm, int stream_hints);
 
 /* Row reductions: threads that own one row (0 = per-bucket default, else a power of two in
  * [32, 1024]; raised automatically when a row would not fit the register budget).
- * GEMV: warps per output row (0 = automatic, else 1, 2, 4, 8) and 16-byte loads in flight per
- * lane (0 = automatic, else 4 or 8).                                                          */
+ * GEMV: warps per output row (0 = automatic, else 1, 2, 4, 8; 16 = the streaming kernel, one
+ * persistent CTA per SM fed by bulk copies, wherever a row fits its ring) and 16-byte loads in
+ * flight per lane (0 = automatic, else 4 or 8).                                               */
 int dtas_row_set_override(int threads_per_row);
 int dtas_gemv_set_override(int warps_per_row, int unroll);
 

@@ -203,6 +203,29 @@ def test_gemv_sharded_and_odd_shapes(cuda_device, n, k):
     util.assert_matmul_close(np_of(y), want, f"gemv+bias {n}x{k}")
 
 
+@pytest.mark.parametrize("n,k", [(4096, 4096), (4096, 11008), (8, 8), (9, 264), (1000, 5632), (300, 11264), (20000, 1024)])
+def test_gemv_streaming_kernel(cuda_device, n, k):
+    """The bulk-copy-fed persistent kernel, forced (code 16) on shapes at its limits: one row per consumer
+    warp, the longest rows each ring depth takes, ragged bands; with a bias, and twice (barrier phases)."""
+    x = seeded_normal((1, k), 60, "float16")
+    w = seeded_normal((n, k), 61, "float16", scale=0.02)
+    b = seeded_normal((n,), 62, "float16", scale=0.3)
+    big, y = guarded((1, n), torch.float16, cuda_device, 5.0)
+    lib = _abi.lib()
+    _abi.check(lib.dtas_gemv_set_override(16, 0))
+    try:
+        assert _abi.variant_of("gemv", 1, n, k).startswith("gemv_stream_rows")
+        ops.gemv(x.to(cuda_device), w.to(cuda_device), y, bias=b.to(cuda_device))
+        first = y.clone()
+        ops.gemv(x.to(cuda_device), w.to(cuda_device), y, bias=b.to(cuda_device))
+        ops.poll_status()
+    finally:
+        lib.dtas_gemv_set_override(0, 0)
+    assert torch.equal(first, y)
+    assert_guards(big, n, 5.0, f"gemv stream n={n} k={k}")
+    util.assert_matmul_close(np_of(y), oracle.gemv(x.numpy(), w.numpy(), b.numpy()).astype(np.float32), f"gemv stream n={n} k={k}")
+
+
 # ---------------------------------------------------------------------------------------
 # GEMM
 # ---------------------------------------------------------------------------------------
