@@ -45,11 +45,16 @@ class ColumnShardedLinear:
 
     `compute` is the kernel entry (default: dtas_b200.ops.gemm_nt, or ops.gemv for one row);
     it is a parameter so the host-side logic can be exercised on CPU ranks.
+
+    The fused tail shards with the columns: `bias` ([N], or this rank's [N/g] when
+    already_sharded) and `act` are fixed at construction; residuals are passed per call as full
+    [m, N] tensors and each rank adds its column slab of them, so
+    Y = act(X W^T + bias) + res1 + res2 needs no exchange either.
     """
 
     def __init__(self, w_full_or_shard: torch.Tensor, n_total: int, rank: Optional[int] = None,
                  world: Optional[int] = None, group=None, compute: Optional[Callable] = None,
-                 already_sharded: bool = False):
+                 already_sharded: bool = False, bias: Optional[torch.Tensor] = None, act: Optional[str] = None):
         self.group = group
         self.rank = dist.get_rank(group) if rank is None else rank
         self.world = dist.get_world_size(group) if world is None else world
@@ -60,21 +65,45 @@ class ColumnShardedLinear:
             raise ValueError(f"weight shard has {self.w.shape[0]} rows, expected {self.n_local}")
         self.even = self.n_total % self.world == 0
         self._compute = compute
+        self.act = act
+        self.bias = None
+        if bias is not None:
+            self.bias = bias if already_sharded else bias[self.col_start:self.col_start + self.n_local].contiguous()
+            if self.bias.numel() != self.n_local:
+                raise ValueError(f"bias shard has {self.bias.numel()} elements, expected {self.n_local}")
 
-    def _kernel(self, x, w, out):
+    def _slab(self, res):
+        """This rank's columns of a full [m, N] residual (a view: the kernels take its row stride)."""
+        if res is None:
+            return None
+        if res.shape[-1] != self.n_total:
+            raise ValueError(f"residual has {res.shape[-1]} columns, expected {self.n_total}")
+        return res[..., self.col_start:self.col_start + self.n_local]
+
+    def _kernel(self, x, w, out, res1=None, res2=None):
+        tail = {}
+        if self.bias is not None:
+            tail["bias"] = self.bias
+        if self.act is not None:
+            tail["act"] = self.act
+        if res1 is not None:
+            tail["res1"] = self._slab(res1)
+        if res2 is not None:
+            tail["res2"] = self._slab(res2)
         if self._compute is not None:
-            return self._compute(x, w, out)
+            return self._compute(x, w, out, **tail)
         from . import ops
         if x.shape[0] == 1:
-            return ops.gemv(x, w, out)
-        return ops.gemm_nt(x, w, out)
+            tail = {k: (v.contiguous() if k.startswith("res") else v) for k, v in tail.items()}   # [1, N/g] rows
+            return ops.gemv(x, w, out, **tail)
+        return ops.gemm_nt(x, w, out, **tail)
 
-    def forward_local(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward_local(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, res1=None, res2=None) -> torch.Tensor:
         """This rank's column slab Y[:, col_start : col_start + n_local]; no communication."""
         m = x.shape[0]
         if out is None:
             out = torch.empty((m, self.n_local), dtype=x.dtype, device=x.device)
-        self._kernel(x, self.w, out)
+        self._kernel(x, self.w, out, res1, res2)
         return out
 
     def gather_buffer(self, m: int, dtype, device) -> torch.Tensor:
@@ -83,13 +112,13 @@ class ColumnShardedLinear:
             raise ValueError("gather buffer needs N divisible by the number of ranks")
         return torch.empty((self.world, m, self.n_local), dtype=dtype, device=device)
 
-    def forward_gathered(self, x: torch.Tensor, buf: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward_gathered(self, x: torch.Tensor, buf: Optional[torch.Tensor] = None, res1=None, res2=None) -> torch.Tensor:
         """Full output on every rank as [g, m, N/g]: kernel into this rank's slot, then one
         all-gather in place."""
         m = x.shape[0]
         if buf is None:
             buf = self.gather_buffer(m, x.dtype, x.device)
-        self._kernel(x, self.w, buf[self.rank])
+        self._kernel(x, self.w, buf[self.rank], res1, res2)
         if self.world > 1:
             dist.all_gather_into_tensor(buf.view(-1), buf[self.rank].reshape(-1), group=self.group)
         return buf

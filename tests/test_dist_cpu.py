@@ -32,8 +32,17 @@ def _free_port():
     return port
 
 
-def _cpu_matmul(x, w, out):
-    out.copy_((x.float() @ w.float().T).to(out.dtype))
+def _cpu_matmul(x, w, out, bias=None, res1=None, res2=None, act=None):
+    t = x.float() @ w.float().T
+    if bias is not None:
+        t = t + bias.float()
+    if act == "gelu":
+        t = torch.nn.functional.gelu(t)
+    if res1 is not None:
+        t = t + res1.float()
+    if res2 is not None:
+        t = t + res2.float()
+    out.copy_(t.to(out.dtype))
     return out
 
 
@@ -54,6 +63,15 @@ def _worker(rank, world, port, results):
         want = torch.empty(m, n, dtype=torch.float16)
         _cpu_matmul(x, w, want)
         ok_gemm = torch.equal(full, want)
+        # fused tail: bias and activation shard with the columns, residuals are sliced per rank
+        b = (torch.randn(n, generator=g) * 0.5).half()
+        r1, r2 = torch.randn(m, n, generator=g).half(), torch.randn(m, n, generator=g).half()
+        fused = ColumnShardedLinear(w, n, compute=_cpu_matmul, bias=b, act="gelu")
+        assert fused.bias.numel() == n // world
+        got = ColumnShardedLinear.as_row_major(fused.forward_gathered(x, res1=r1, res2=r2))
+        want_f = torch.empty(m, n, dtype=torch.float16)
+        _cpu_matmul(x, w, want_f, bias=b, res1=r1, res2=r2, act="gelu")
+        ok_gemm = ok_gemm and torch.equal(got, want_f)
         # one-row (GEMV) case: the flat gather already is [N]
         y = ColumnShardedLinear(w, n, compute=_cpu_matmul).forward_gathered(x[:1])
         ok_gemv = torch.equal(y.reshape(1, n), want[:1])

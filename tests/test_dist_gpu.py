@@ -46,6 +46,21 @@ def _worker(rank, world, port, results):
                 want[:, lo:hi] = slab
             ops.poll_status(rank)
             ok[(m, n, k)] = bool(torch.equal(full, want))
+        # fused tail through the sharded layer: bias + GELU + two residuals, against one single-GPU call
+        for m in (1, 40):
+            n, k = 2048, 1024
+            x = seeded_normal((m, k), 11, "float16").to(dev)
+            w = seeded_normal((n, k), 12, "float16", scale=0.02).to(dev)
+            b = seeded_normal((n,), 13, "float16", scale=0.5).to(dev)
+            r1 = seeded_normal((m, n), 14, "float16").to(dev)
+            r2 = seeded_normal((m, n), 15, "float16").to(dev)
+            lin = ColumnShardedLinear(w, n, bias=b, act="gelu")
+            full = ColumnShardedLinear.as_row_major(lin.forward_gathered(x, res1=r1, res2=r2))
+            want = torch.empty((m, n), dtype=torch.float16, device=dev)
+            (ops.gemv if m == 1 else ops.gemm_nt)(x, w, want, bias=b, res1=r1, res2=r2, act="gelu")
+            ops.poll_status(rank)
+            err = (full.float() - want.float()).abs().max().item()
+            ok[("fused", m)] = err <= 2e-2 * want.float().abs().max().item()
         a = seeded_normal((7, 11008), 3, "float16").to(dev)
         b = seeded_normal((7, 11008), 4, "float16").to(dev)
         out = torch.zeros_like(a)
