@@ -175,18 +175,20 @@ __device__ __forceinline__ void gv_bulk_load(uint32_t dst, const void* src, uint
                : "memory");
 }
 
-// Shared memory: x (k fp16), then STAGES row buffers of k fp16 each, then the barriers.
-// Stage s is always consumed by consumer warp s % 8 (STAGES is a multiple of 8).
+// Shared memory: x (k fp16), then STAGES buffers of `rps` consecutive rows each (one bulk copy:
+// the rows of a band are contiguous in W), then the barriers.  Stage s is always consumed by
+// consumer warp s % 8 (STAGES is a multiple of 8), which reduces its rows one after another.
 template <int STAGES>
 __global__ void __launch_bounds__(kStreamThreads, 1)
     gemv_f16_stream_kernel(const __half* __restrict__ x, const __half* __restrict__ w, const Epilogue epi,
-                           void* __restrict__ y, int n, int k, int* status) {
+                           void* __restrict__ y, int n, int k, int rps, int* status) {
   static_assert(STAGES % kStreamConsumers == 0, "stage -> warp mapping");
   extern __shared__ __align__(128) uint8_t gv_smem[];
   const uint32_t row_bytes = (uint32_t)k * 2u;
+  const uint32_t stage_bytes = row_bytes * (uint32_t)rps;
   uint8_t* x_s = gv_smem;
   uint8_t* ring = gv_smem + row_bytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)STAGES * row_bytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)STAGES * stage_bytes);
   const uint32_t bar0 = sm_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
@@ -197,6 +199,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1)
   const int r0 = (int)(((int64_t)blockIdx.x * n) / gridDim.x);
   const int r1 = (int)(((int64_t)(blockIdx.x + 1) * n) / gridDim.x);
   const int rows = r1 - r0;
+  const int items = (rows + rps - 1) / rps;       // stage fills: rps rows each, the last one maybe fewer
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -215,13 +218,16 @@ __global__ void __launch_bounds__(kStreamThreads, 1)
     if (lane == 0) {
       gv_mbar_expect_tx(x_bar, row_bytes);
       gv_bulk_load(sm_u32(x_s), x, row_bytes, x_bar);
+    }
+    if (lane == 0) {                                // one thread: lanes that spin side by side slow each other
       bool ok = true;
-      for (int i = 0; i < rows && ok; ++i) {
+      for (int i = 0; i < items && ok; ++i) {
         const int s = i % STAGES;
         const uint32_t parity = (uint32_t)(i / STAGES) & 1u;
         if (!gv_mbar_wait(empty_bar(s), parity ^ 1u, status, ERR_GEMV_PRODUCER)) { ok = false; break; }
-        gv_mbar_expect_tx(full_bar(s), row_bytes);
-        gv_bulk_load(sm_u32(ring + (size_t)s * row_bytes), w + (int64_t)(r0 + i) * k, row_bytes, full_bar(s));
+        const uint32_t bytes = (uint32_t)min(rps, rows - i * rps) * row_bytes;
+        gv_mbar_expect_tx(full_bar(s), bytes);
+        gv_bulk_load(sm_u32(ring + (size_t)s * stage_bytes), w + (int64_t)(r0 + i * rps) * k, bytes, full_bar(s));
       }
     }
   } else {
@@ -229,26 +235,31 @@ __global__ void __launch_bounds__(kStreamThreads, 1)
     const int n_chunks = k >> 3;
     const uint4* xv = reinterpret_cast<const uint4*>(x_s);
     bool ok = gv_mbar_wait(x_bar, 0u, status, ERR_GEMV_CONSUMER);
-    for (int i = cw; i < rows && ok; i += kStreamConsumers) {
+    for (int i = cw; i < items && ok; i += kStreamConsumers) {
       const int s = i % STAGES;
       const uint32_t parity = (uint32_t)(i / STAGES) & 1u;
       if (!gv_mbar_wait(full_bar(s), parity, status, ERR_GEMV_CONSUMER)) { ok = false; break; }
-      const uint4* wv = reinterpret_cast<const uint4*>(ring + (size_t)s * row_bytes);
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
-      int c = lane;
-      for (; c + 96 < n_chunks; c += 128) {
+      const int nrows = min(rps, rows - i * rps);
+      float mine = 0.f;                              // lane rr keeps the dot product of row rr of the stage
+      for (int rr = 0; rr < nrows; ++rr) {
+        const uint4* wv = reinterpret_cast<const uint4*>(ring + (size_t)s * stage_bytes + (size_t)rr * row_bytes);
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        int c = lane;
+        for (; c + 96 < n_chunks; c += 128) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) acc[u] = dot8(wv[c + 32 * u], xv[c + 32 * u], acc[u]);
+          for (int u = 0; u < 4; ++u) acc[u] = dot8(wv[c + 32 * u], xv[c + 32 * u], acc[u]);
+        }
+        for (; c < n_chunks; c += 32) acc[0] = dot8(wv[c], xv[c], acc[0]);
+        float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == rr) mine = sum;
       }
-      for (; c < n_chunks; c += 32) acc[0] = dot8(wv[c], xv[c], acc[0]);
-      float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
       __syncwarp();                                   // every lane has read the stage
-      if (lane == 0) {
-        gv_mbar_arrive(empty_bar(s));
-        const int row = r0 + i;
-        epi_store(epi, y, 0, 0, row, epi_value(epi, sum, 0, row));
+      if (lane == 0) gv_mbar_arrive(empty_bar(s));    // hand the stage back before the stores
+      if (lane < nrows) {
+        const int row = r0 + i * rps + lane;
+        epi_store(epi, y, 0, 0, row, epi_value(epi, mine, 0, row));
       }
     }
   }
@@ -277,18 +288,41 @@ inline int pick_wpr(int64_t n, int64_t k, int sm_count) {
 // stage (16 stages up to K = 5632, 8 up to K = 11264 in ~200 KB of shared memory).  Override code
 // 16 (dtas_gemv_set_override) forces the streaming kernel where it fits, 1/2/4/8 the per-row kernel.
 constexpr int kStreamSmemMax = 200 * 1024;
-constexpr bool kStreamByDefault = false;          // opt-in (override code 16) until its dispatch range is measured
+// Measured on B200 against the per-row kernel (us): W[4096,4096] 7.4 vs 7.9, [11008,4096] 15.8 vs 17.1,
+// [4096,11008] 16.1 vs 20.1, [32000,4096] 41.3 vs 44.0, [2048,4096] 4.9 vs 5.2; [1024,4096] 3.8 vs 3.2.
+constexpr bool kStreamByDefault = true;
 constexpr int64_t kStreamMinBytes = 16ll << 20;   // below that the per-row kernel's single wave is as good
-inline int pick_stream(int64_t n, int64_t k, int sm_count) {
+constexpr int kStreamStageBytes16 = 11264, kStreamStageBytes8 = 22528;   // stage capacity at 16 / 8 stages
+struct StreamPlan {
+  int stages = 0;   // 0: use the per-row kernel
+  int rps = 1;      // rows per stage
+};
+inline StreamPlan pick_stream(int64_t n, int64_t k, int sm_count) {
   (void)sm_count;
+  StreamPlan p;
   const int forced = g_gemv_wpr.load();
-  if (forced == 1 || forced == 2 || forced == 4 || forced == 8) return 0;
-  int stages = 0;
-  if ((1 + 16) * k * 2 + 33 * 8 + 8 <= kStreamSmemMax) stages = 16;
-  else if ((1 + 8) * k * 2 + 17 * 8 + 8 <= kStreamSmemMax) stages = 8;
-  if (stages == 0 || n < kStreamConsumers) return 0;
-  if (forced == 16) return stages;
-  return (kStreamByDefault && 2 * n * k >= kStreamMinBytes) ? stages : 0;
+  if (forced == 1 || forced == 2 || forced == 4 || forced == 8) return p;
+  const int64_t row_bytes = 2 * k;
+  // One thread issues a copy in ~0.2 us and an SM has to take in ~45 KB per us, so a copy should carry
+  // two rows of 8 KB where the band of a CTA is long enough to still give every consumer warp two stage
+  // fills (W[32000,4096]: 41.3 us with two rows per copy, 43.9 with one); short bands keep one row per
+  // copy and the deeper ring (W[4096,4096]: 7.4-7.7 us against 8.1).  Rows under 5.5 KB always travel
+  // several to a copy (W[4096,2560]: 6.2 us against 7.1; W[50280,2560]: 39.7 against 62.2).
+  if (row_bytes > kStreamStageBytes8 || n < kStreamConsumers) return p;
+  if (forced != 16 && !(kStreamByDefault && 2 * n * k >= kStreamMinBytes)) return p;
+  const int64_t band = (n + sm_count - 1) / (sm_count > 0 ? sm_count : 1);
+  const int64_t fit16 = kStreamStageBytes16 / row_bytes, fit8 = kStreamStageBytes8 / row_bytes;
+  if (fit16 >= 2) {                    // short rows: as many as fill an 11 KB stage
+    p.stages = 16;
+    p.rps = (int)(fit16 < 32 ? fit16 : 32);        // one lane per row of a stage keeps its result
+  } else if (fit8 >= 2 && band >= 2 * kStreamConsumers * fit8) {
+    p.stages = 8;                      // 5.5-11 KB rows in a long band: two per copy, 8 deep stages
+    p.rps = (int)fit8;
+  } else {
+    p.stages = fit16 >= 1 ? 16 : 8;
+    p.rps = 1;
+  }
+  return p;
 }
 
 inline int pick_unroll(int wpr) {
@@ -316,9 +350,10 @@ int launch_gemv(const void* x, const void* w, const Epilogue& epi, void* y, int6
     launch_kernel(gemv_f16_scalar_kernel, grid, kThreads, 0, st, xp, wp, epi, y, (int)n, (int)k);
     return after_launch("gemv_f16_scalar_kernel");
   }
-  const int stream_stages = pick_stream(n, k, ctx->sm_count);
+  const StreamPlan sp = pick_stream(n, k, ctx->sm_count);
+  const int stream_stages = sp.stages;
   if (stream_stages > 0) {
-    const size_t smem = (size_t)(1 + stream_stages) * (size_t)k * 2 + (size_t)(2 * stream_stages + 1) * 8 + 8;
+    const size_t smem = (size_t)(1 + stream_stages * sp.rps) * (size_t)k * 2 + (size_t)(2 * stream_stages + 1) * 8 + 8;
     const int64_t bands = (n + kStreamConsumers - 1) / kStreamConsumers;      // at least a row per consumer warp
     const unsigned grid = (unsigned)(bands < ctx->sm_count ? bands : ctx->sm_count);
     int dev = 0;
@@ -329,13 +364,13 @@ int launch_gemv(const void* x, const void* w, const Epilogue& epi, void* y, int6
         DTAS_CUDA(cudaFuncSetAttribute(gemv_f16_stream_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmemMax));
         attr_set[0][dev] = true;
       }
-      launch_kernel(gemv_f16_stream_kernel<16>, grid, kStreamThreads, smem, st, xp, wp, epi, y, (int)n, (int)k, ctx->status);
+      launch_kernel(gemv_f16_stream_kernel<16>, grid, kStreamThreads, smem, st, xp, wp, epi, y, (int)n, (int)k, sp.rps, ctx->status);
     } else {
       if (dev < 64 && !attr_set[1][dev]) {
         DTAS_CUDA(cudaFuncSetAttribute(gemv_f16_stream_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmemMax));
         attr_set[1][dev] = true;
       }
-      launch_kernel(gemv_f16_stream_kernel<8>, grid, kStreamThreads, smem, st, xp, wp, epi, y, (int)n, (int)k, ctx->status);
+      launch_kernel(gemv_f16_stream_kernel<8>, grid, kStreamThreads, smem, st, xp, wp, epi, y, (int)n, (int)k, sp.rps, ctx->status);
     }
     return after_launch("gemv_f16_stream_kernel");
   }
@@ -359,9 +394,9 @@ void gemv_variant_name(int64_t n, int64_t k, const DeviceCtx* ctx, char* buf, in
     snprintf(buf, len, "gemv_scalar_warp_per_row");
     return;
   }
-  const int stages = pick_stream(n, k, ctx ? ctx->sm_count : 148);
-  if (stages > 0) {
-    snprintf(buf, len, "gemv_stream_rows_s%d", stages);
+  const StreamPlan sp = pick_stream(n, k, ctx ? ctx->sm_count : 148);
+  if (sp.stages > 0) {
+    snprintf(buf, len, "gemv_stream_s%d_rows%d", sp.stages, sp.rps);
     return;
   }
   const int wpr = pick_wpr(n, k, ctx ? ctx->sm_count : 148);

@@ -56,7 +56,12 @@ def test_variant_names(lib):
     assert _abi.variant_of("copy", 1, 11008) == "ew_vec16_unroll1"
     assert "softmax_regs" in _abi.variant_of("softmax", 4096, 4096)
     assert "generic" in _abi.variant_of("rms_norm", 4, 101)
-    assert _abi.variant_of("gemv", 1, 4096, 4096).startswith("gemv_vec16")
+    assert _abi.variant_of("gemv", 1, 4096, 4096) == "gemv_stream_s16_rows1"       # 33.5 MB: the streaming kernel
+    assert _abi.variant_of("gemv", 1, 32000, 2560) == "gemv_stream_s16_rows2"     # short rows: 16 shallow stages
+    assert _abi.variant_of("gemv", 1, 32000, 4096) == "gemv_stream_s8_rows2"      # long band: two 8 KB rows per copy
+    assert _abi.variant_of("gemv", 1, 4096, 11008) == "gemv_stream_s8_rows1"
+    assert _abi.variant_of("gemv", 1, 512, 4096).startswith("gemv_vec16")          # 4 MB: the per-row kernel
+    assert _abi.variant_of("gemv", 1, 4096, 16384).startswith("gemv_vec16")        # a row does not fit a stage
     assert _abi.variant_of("gemm", 8192, 22016, 4096) == "gemm_tcgen05_2cta_bm256_bn256_bk64_s7"
     assert _abi.variant_of("gemm", 16, 22016, 4096).startswith("gemm_tcgen05_swap_n128_m16")
     assert _abi.variant_of("gemm", 255, 22016, 4096).startswith("gemm_tcgen05_bm128_bn")

@@ -203,7 +203,7 @@ def test_gemv_sharded_and_odd_shapes(cuda_device, n, k):
     util.assert_matmul_close(np_of(y), want, f"gemv+bias {n}x{k}")
 
 
-@pytest.mark.parametrize("n,k", [(4096, 4096), (4096, 11008), (8, 8), (9, 264), (1000, 5632), (300, 11264), (20000, 1024)])
+@pytest.mark.parametrize("n,k", [(4096, 4096), (4096, 11008), (8, 8), (9, 264), (1000, 5632), (300, 11264), (20000, 1024), (50280, 2560), (1187, 512)])
 def test_gemv_streaming_kernel(cuda_device, n, k):
     """The bulk-copy-fed persistent kernel, forced (code 16) on shapes at its limits: one row per consumer
     warp, the longest rows each ring depth takes, ragged bands; with a bias, and twice (barrier phases)."""
@@ -214,7 +214,7 @@ def test_gemv_streaming_kernel(cuda_device, n, k):
     lib = _abi.lib()
     _abi.check(lib.dtas_gemv_set_override(16, 0))
     try:
-        assert _abi.variant_of("gemv", 1, n, k).startswith("gemv_stream_rows")
+        assert _abi.variant_of("gemv", 1, n, k).startswith("gemv_stream_s")
         ops.gemv(x.to(cuda_device), w.to(cuda_device), y, bias=b.to(cuda_device))
         first = y.clone()
         ops.gemv(x.to(cuda_device), w.to(cuda_device), y, bias=b.to(cuda_device))
