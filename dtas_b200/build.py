@@ -66,9 +66,25 @@ def build_trace_library():
     return TRACE_LIB_PATH
 
 
+PROBE_PATH = os.path.join(LIB_DIR, "l2_probe")
+
+
+def build_probe():
+    """The stand-alone per-SM L2 throughput probe (csrc/l2_probe.cu) -> lib/l2_probe."""
+    os.makedirs(LIB_DIR, exist_ok=True)
+    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-o", PROBE_PATH,
+           os.path.join(CSRC, "l2_probe.cu")]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+    return PROBE_PATH
+
+
 if __name__ == "__main__":
     import sys
-    if "--trace" in sys.argv:
+    if "--probe" in sys.argv:
+        print(build_probe())
+    elif "--trace" in sys.argv:
         print(build_trace_library())
     else:
         print(build_library(force=True, verbose=True))
