@@ -1162,6 +1162,199 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 }
 
 // ---------------------------------------------------------------------------------------
+// K cut in two inside a cluster: the hand-over of the second half goes through shared memory.
+//
+// For 128 < m <= ~512 at N ~ 4096 the output has too few 128 x 128 tiles to fill the SMs, and a
+// tile finished through the global workspace pays ~6 us for it at m = 255 (park the partial,
+// fence, ticket, read both partials back with four warps).  Here the two K halves of a tile are
+// the two CTAs of a cluster: each runs the usual TMA / MMA pipeline on its half; CTA 1 then moves
+// its accumulator (TMEM -> registers -> its own shared memory) into a staging area of CTA 0 with
+// one bulk copy through distributed shared memory, and CTA 0 adds its own accumulator and runs the
+// epilogue.  No workspace, no ticket, no fence; the sum is own half + other half: deterministic.
+// One tile per cluster (the regime is a single wave).  BN = 64 or 128 (the staging tile has to fit
+// beside the ring).
+// ---------------------------------------------------------------------------------------
+template <int BN>
+struct K2Cfg {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStagingBytes = BM * BN * 4;                 // one fp32 accumulator tile
+  static constexpr int kStages = (224 * 1024 - kStagingBytes) / kStageBytes;
+  static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+  static constexpr int kBarBytes = (2 * kStages + 2) * 8 + 16;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kStagingBytes + kBarBytes;
+  static_assert(kSmemBytes <= 227 * 1024 && kStages >= 3, "smem");
+};
+constexpr int ERR_K2_DATA = 0x106;
+
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t cta) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta));
+  return r;
+}
+// Bulk copy from this CTA's shared memory into a peer's (both addresses 16-byte aligned, size a
+// multiple of 16); completion is counted on the peer's mbarrier.
+__device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster, uint32_t src_cta, uint32_t bytes,
+                                                  uint32_t bar_cluster) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               :
+               : "r"(dst_cluster), "r"(src_cta), "r"(bytes), "r"(bar_cluster)
+               : "memory");
+}
+
+// a.m_tiles x a.n_tiles tiles of 128 x BN; grid = 2 x tiles; a.num_kb >= 2; a.splits is not used.
+template <int BN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+    gemm_f16_tcgen05_k2_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                               const __grid_constant__ CUtensorMap tmap_w, const GemmArgs a) {
+  using C = K2Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t staging = base + C::kStages * C::kStageBytes;           // [column group][128 rows] float4
+  const uint32_t bars = staging + C::kStagingBytes;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (C::kStages + s); };
+  const uint32_t tfull_bar = bars + 8u * (2 * C::kStages);
+  const uint32_t data_bar = bars + 8u * (2 * C::kStages + 1);            // CTA 0: the peer's tile has landed
+  const uint32_t tmem_slot = bars + 8u * (2 * C::kStages + 2);
+  uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  float4* staging4 = reinterpret_cast<float4*>(gen_base + C::kStages * C::kStageBytes);
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(
+      gen_base + C::kStages * C::kStageBytes + C::kStagingBytes + 8 * (2 * C::kStages + 2));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int tile = blockIdx.x >> 1;
+  int mt, nt;
+  decode_tile(a, tile, mt, nt);
+  const int half = (a.num_kb + 1) >> 1;
+  const int kb0 = rank == 0 ? 0 : half, kb1 = rank == 0 ? half : a.num_kb;
+
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_x)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w)) : "memory");
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(tfull_bar, 1);
+    mbar_init(data_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (rank == 0) mbar_expect_tx(data_bar, C::kStagingBytes);    // armed before the peer can send
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  cluster_sync_all();          // both CTAs' barriers exist before anything crosses
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+  pdl_wait();
+  pdl_launch_dependents();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(empty_bar(stage), phase ^ 1u, a.status, ERR_PRODUCER)) break;
+        mbar_expect_tx(full_bar(stage), C::kStageBytes);
+        const uint32_t sa = base + stage * C::kStageBytes;
+        tma_load_2d(sa, &tmap_x, kb * BK, mt * BM, full_bar(stage));
+        tma_load_2d(sa + C::kABytes, &tmap_w, kb * BK, nt * BN, full_bar(stage));
+        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16_f32(BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(full_bar(stage), phase, a.status, ERR_MMA_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sa = base + stage * C::kStageBytes;
+        const uint64_t da = make_kmajor_sw128_desc(sa);
+        const uint64_t db = make_kmajor_sw128_desc(sa + C::kABytes);
+#pragma unroll
+        for (int kk = 0; kk < BK / UMMA_K; ++kk)
+          umma_f16(tmem_base, da + 2u * kk, db + 2u * kk, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
+        umma_commit(empty_bar(stage));
+        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+      }
+      if (ok) umma_commit(tfull_bar);
+    }
+    __syncwarp();
+  } else {
+    const int quarter = warp & 3;
+    const int epi_tid = threadIdx.x - 64;
+    const int r_in_tile = quarter * 32 + lane;
+    const int row = mt * BM + r_in_tile;
+    const bool row_ok = row < a.m;
+    const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const int col_base = nt * BN;
+    bool ok = mbar_wait(tfull_bar, 0u, a.status, ERR_EPILOGUE);
+    tc_fence_after();
+    if (rank == 1) {
+      // accumulator -> own staging area -> one bulk copy into CTA 0's staging area
+      if (ok) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_addr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            staging4[(c * 8 + q) * BM + r_in_tile] =
+                make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
+                            __uint_as_float(r[4 * q + 3]));
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the copy reads what the threads wrote
+      epilogue_bar_sync();
+      if (epi_tid == 0 && ok) bulk_copy_to_peer(mapa_u32(staging, 0), staging, C::kStagingBytes, mapa_u32(data_bar, 0));
+    } else {
+      if (ok) ok = mbar_wait(data_bar, 0u, a.status, ERR_K2_DATA);
+      if (ok) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_addr + c * 32, r);
+          tmem_ld_wait();
+          const int col0 = col_base + c * 32;
+          if (row_ok && col0 < a.n) {
+            float f[32];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const float4 v = staging4[(c * 8 + q) * BM + r_in_tile];
+              f[4 * q] = __uint_as_float(r[4 * q]) + v.x;
+              f[4 * q + 1] = __uint_as_float(r[4 * q + 1]) + v.y;
+              f[4 * q + 2] = __uint_as_float(r[4 * q + 2]) + v.z;
+              f[4 * q + 3] = __uint_as_float(r[4 * q + 3]) + v.w;
+            }
+            epi_store_row32(a.epi, a.y, a.ldy, a.vec_store, row, col0, a.n, f);
+          }
+        }
+      }
+    }
+  }
+
+  // CTA 1 may not leave while its copy is still reading its shared memory: CTA 0 comes here only
+  // after the data barrier (or after giving up on it).
+  tc_fence_before();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // SIMT fallback for shapes TMA cannot describe (k % 8 != 0 or unaligned bases): one thread
 // per output element, fp32 accumulation.  Correct for every shape, not a performance path.
 // ---------------------------------------------------------------------------------------
@@ -1249,6 +1442,7 @@ struct GemmPlan {
   int kb_per_split;
   bool simt;
   bool pair = false;   // two-CTA 256 x 256 tiles (gemm_f16_tcgen05_pair_kernel)
+  bool k2 = false;     // K cut in two inside a cluster of two CTAs (gemm_f16_tcgen05_k2_kernel<bn>), bn = 64 or 128
   int swap_mn = 0;     // > 0: swapped-operand kernel with the X tile padded to this many rows
   int sk_per = 0;      // swapped kernel, stream-K: (tile, k-block) units per CTA (0 = fixed split)
   int sk_grid = 0;     //   CTAs launched
@@ -1319,6 +1513,13 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
   if (p.simt) return p;
   int obn0 = 0, osp0 = 0;
   effective_choice(m, n, k, &obn0, &osp0);
+  if ((obn0 == 8192 + 64 || obn0 == 8192 + 128) && num_kb >= 2) {   // tile codes 8256 / 8320
+    p.bn = obn0 - 8192;
+    p.splits = 1;
+    p.k2 = true;
+    return p;
+  }
+  if (obn0 >= 8192) obn0 = 0;      // not applicable to this shape: plan as usual
   if ((m <= 256 && (obn0 == 1024 || obn0 == 2048)) || (m <= kSwapMaxM && obn0 == 0 && kSwapByDefault)) {
     // Swapped-operand kernel: 128-row W tiles, split K until the work items fill the SMs.
     const int mn = m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256)));
@@ -1595,6 +1796,23 @@ int launch_pair(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a,
   return after_launch("gemm_f16_tcgen05_pair_kernel");
 }
 
+template <int BN>
+int launch_k2(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a, cudaStream_t st) {
+  using C = K2Cfg<BN>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  DTAS_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_set[dev]) {
+    DTAS_CUDA(cudaFuncSetAttribute(gemm_f16_tcgen05_k2_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   C::kSmemBytes));
+    attr_set[dev] = true;
+  }
+  const int64_t grid = 2ll * a.m_tiles * a.n_tiles;
+  if (grid > 0x7fffffffLL) DTAS_FAIL(DTAS_EINVAL, "gemm: too many tiles");
+  launch_kernel(gemm_f16_tcgen05_k2_kernel<BN>, (unsigned)grid, kGemmThreads, C::kSmemBytes, st, tx, tw, a);
+  return after_launch("gemm_f16_tcgen05_k2_kernel");
+}
+
 template <int MN>
 int launch_swap(const CUtensorMap& tw, const CUtensorMap& tx, const GemmArgs& a, int sm_count, cudaStream_t st) {
   using C = SwapCfg<MN>;
@@ -1700,6 +1918,7 @@ int launch_gemm(const void* x, const void* w, const Epilogue& epi, void* y, int6
   a.vec_store = finish_epilogue(a.epi, y, ldy);
   if ((int64_t)a.m_tiles * a.n_tiles * a.splits > 0x7fffffffLL)
     DTAS_FAIL(DTAS_EINVAL, "gemm: too many tiles");
+  if (p.k2) return p.bn == 128 ? launch_k2<128>(tx, tw, a, st) : launch_k2<64>(tx, tw, a, st);
   if (p.pair) {
     a.m_tiles = (int)((m + 2 * BM - 1) / (2 * BM));
     a.n_tiles = (int)((n + kPairBN - 1) / kPairBN);
@@ -1739,6 +1958,10 @@ void gemm_variant_name(int64_t m, int64_t n, int64_t k, const DeviceCtx* ctx, ch
   }
   if (p.pair) {
     snprintf(buf, len, "gemm_tcgen05_2cta_bm256_bn256_bk64_s%d", kPairStages);
+    return;
+  }
+  if (p.k2) {
+    snprintf(buf, len, "gemm_tcgen05_bm128_bn%d_bk64_s%d_k2cluster", p.bn, p.bn == 128 ? K2Cfg<128>::kStages : K2Cfg<64>::kStages);
     return;
   }
   if (p.swap_mn > 0) {

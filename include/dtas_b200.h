@@ -158,7 +158,9 @@ int dtas_variant_of(const char* op, int64_t m, int64_t n, int64_t k, int device,
  * width bn in {64,128,256} (0 = automatic; 512 = the two-CTA kernel with 256 x 256 tiles;
  * 1024 = the swapped-operand kernel, which applies to m <= 256; 2048 = the same kernel with
  * stream-K work distribution; 4096 + 64/128/256 = single-CTA tiles of that width with stream-K;
- * split_k is ignored by the stream-K codes) and split-K factor (0 = automatic). */
+ * 8192 + 64/128 = tiles of that width with K cut in two inside a two-CTA cluster, the second half
+ * handed over through shared memory; split_k is ignored by the stream-K and cluster codes) and
+ * split-K factor (0 = automatic). */
 int dtas_gemm_set_override(int bn, int split_k);
 
 /* Measured dispatch table for the GEMM: for weight shape (n, k) and row counts m_lo..m_hi use

@@ -66,13 +66,13 @@ def test_gemm_fused_tails_default_dispatch(cuda_device, tail, m, n, k):
         assert np.array_equal(got, got.astype(np.float16).astype(np.float32)), what
 
 
-@pytest.mark.parametrize("bn,split", [(64, 1), (128, 3), (256, 2), (512, 1), (1024, 1), (1024, 4), (2048, 0), (4224, 0)])
+@pytest.mark.parametrize("bn,split", [(64, 1), (128, 3), (256, 2), (512, 1), (1024, 1), (1024, 4), (2048, 0), (4224, 0), (8320, 0)])
 @pytest.mark.parametrize("tail", ["gelu", "res2_f32"])
 def test_gemm_fused_tails_every_kernel(cuda_device, tail, bn, split):
     """The tail is applied in five places (direct and reduced epilogues of the tiled and swapped
     kernels, the two-CTA kernel): force each with ragged sizes."""
     t = TAILS[tail]
-    m, n, k = (200, 520, 1160) if bn < 1024 or bn > 2048 else (40, 520, 1160)
+    m, n, k = (200, 520, 1160) if bn < 1024 or bn > 2048 else (40, 520, 1160)   # the swapped kernel takes m <= 256
     if bn == 512:
         m = 300
     host, dev = operands(m, n, k, t, 900 + bn + split, cuda_device)

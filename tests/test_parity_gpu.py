@@ -279,7 +279,7 @@ def test_gemm_small_m_full_oracle(cuda_device):
 
 
 @pytest.mark.parametrize("bn,split", [(64, 1), (128, 1), (256, 1), (64, 4), (128, 3), (256, 2), (128, 16), (512, 1),
-                                      (1024, 1), (1024, 4), (1024, 7), (2048, 0), (4160, 0), (4224, 0), (4352, 0)])
+                                      (1024, 1), (1024, 4), (1024, 7), (2048, 0), (4160, 0), (4224, 0), (4352, 0), (8256, 0), (8320, 0)])
 def test_gemm_every_tile_width_and_split(cuda_device, bn, split):
     """Forces each kernel instantiation and split factor on ragged shapes (m, n, k not
     multiples of the tile), with a bias, writing into a column slab of a wider buffer."""
@@ -325,6 +325,34 @@ def test_gemm_two_cta_kernel(cuda_device, m, n, k):
     ref = (xd @ wd.T).float()
     err = (y.float() - ref).abs().max().item()
     assert err <= 2e-2 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("code", [8256, 8320])
+@pytest.mark.parametrize("m,n,k", [(255, 4096, 4096), (512, 4096, 11008), (130, 200, 136), (1, 64, 128), (300, 1000, 72), (2000, 520, 1160)])
+def test_gemm_cluster_k_split_kernel(cuda_device, m, n, k, code):
+    """K cut in two inside a two-CTA cluster, the second half handed over through distributed shared
+    memory: full and ragged shapes, odd k-block counts (k = 72: the halves are 1 and 1 with zero fill),
+    several waves of clusters (m = 2000), bias, strided output; two runs are bit-identical."""
+    x = seeded_normal((m, k), 77, "float16")
+    w = seeded_normal((n, k), 78, "float16", scale=0.02)
+    b = seeded_normal((n,), 79, "float16", scale=0.1)
+    xd, wd, bd = x.to(cuda_device), w.to(cuda_device), b.to(cuda_device)
+    wide = torch.full((m, n + 16), 5.0, dtype=torch.float16, device=cuda_device)
+    y = wide[:, :n]
+    _abi.check(_abi.lib().dtas_gemm_set_override(code, 0))
+    try:
+        assert "k2cluster" in _abi.variant_of("gemm", m, n, k)
+        ops.gemm_nt(xd, wd, y, bias=bd)
+        ops.poll_status()
+        first = y.clone()
+        ops.gemm_nt(xd, wd, y, bias=bd)
+        ops.poll_status()
+    finally:
+        _abi.check(_abi.lib().dtas_gemm_set_override(0, 0))
+    assert torch.equal(first, y), "two runs differ"
+    assert bool((wide[:, n:] == 5.0).all()), "wrote outside its column slab"
+    want = x.float().numpy() @ w.float().numpy().T + b.float().numpy()
+    util.assert_matmul_close(np_of(y), want, f"k2 cluster gemm m={m} n={n} k={k} code={code}")
 
 
 @pytest.mark.parametrize("m", [1, 15, 16, 17, 33, 100, 129, 256])
