@@ -1494,6 +1494,7 @@ constexpr bool kSwapByDefault = true;    // swapped-operand kernel for small m
 constexpr int kSwapMaxM = 64;            // beyond that the X tile crowds W out of the ring
 constexpr bool kPairByDefault = true;    // consider two-CTA tiles
 constexpr int kPairMinM = 257;           // below that a 256-row tile is mostly padding
+constexpr bool kK2ByDefault = true;      // consider the cluster K-split kernel where it fits one wave
 constexpr size_t kSplitKWorkspaceBytes = 64ull << 20;
 constexpr int kTileCounters = 4096;
 
@@ -1604,6 +1605,8 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
   static const int kSplits[10] = {1, 2, 3, 4, 5, 6, 8, 10, 12, 16};
   double best = 1e30;
   int best_bn = 256, best_splits = 1;
+  double k2_cost = 1e30;     // K cut in two inside a cluster (single wave only): no workspace tail
+  int k2_bn = 0;
   for (int bi = 0; bi < 3; ++bi) {
     const int bn = kBn[bi];
     const int64_t n_tiles = (n + bn - 1) / bn;
@@ -1630,6 +1633,15 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
       const double an = active / am < 1.0 ? 1.0 : active / am;
       const double t_hbm = 128.0 * (an * bn + am * rows_x) / kHbmGBs;
       double cost = (double)rounds * (kb_per * (t_core > t_hbm ? t_core : t_hbm) + kItemFixedNs);
+      if (s == 2 && bn <= 128 && rounds == 1 && kK2ByDefault) {
+        // the same main loop, the second half handed over through shared memory (~1.5 us measured
+        // against ~4.5 us through the workspace at m = 255)
+        const double c2 = cost + 1500.0;
+        if (c2 < k2_cost * 0.999) {
+          k2_cost = c2;
+          k2_bn = bn;
+        }
+      }
       // split-K tail: partial traffic, plus the last CTA summing chunk by chunk and split by
       // split, one L2 round trip (~0.7 us) each
       if (s > 1) cost += 2.0 * s * (double)m * (double)n * 4.0 / kHbmGBs + 1500.0 + 700.0 * (bn / 32) * ((s + 1) / 2);
@@ -1705,7 +1717,7 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
     const double an = active / am < 1.0 ? 1.0 : active / am;
     const double t_hbm = 128.0 * (an * kPairBN + am * 2 * BM) / kHbmGBs;
     const double cost = (double)rounds * (num_kb * (t_core > t_hbm ? t_core : t_hbm) + kItemFixedNs);
-    pair = cost < best;
+    pair = cost < (k2_cost < best ? k2_cost : best);
   }
   if (obn == 512) pair = true;
   if (obn == 64 || obn == 128 || obn == 256) pair = false;
@@ -1714,6 +1726,12 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
     p.splits = 1;
     p.kb_per_split = num_kb;
     p.pair = true;
+    return p;
+  }
+  if (k2_bn > 0 && k2_cost < best && obn == 0 && osp == 0 && obn0 < 4096) {
+    p.bn = k2_bn;
+    p.splits = 1;
+    p.k2 = true;
     return p;
   }
   if (sk_bn > 0) {
