@@ -1355,6 +1355,184 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 }
 
 // ---------------------------------------------------------------------------------------
+// The same hand-over for the swapped-operand kernel at m <= 32: K cut in S = 2, 3 or 4 slices, the
+// S CTAs of a cluster.  CTAs 1 .. S-1 send their MN x 128 accumulators (8 or 16 KB) into slots of
+// CTA 0's staging area with one bulk copy each; CTA 0 adds them to its own in rank order = K order.
+// One 128-column tile of Y per cluster; single wave.
+// ---------------------------------------------------------------------------------------
+template <int MN>
+struct SwapKcCfg {
+  static constexpr int kWBytes = BM * BK * 2;
+  static constexpr int kXBytes = MN * BK * 2;
+  static constexpr int kXPad = (kXBytes + 1023) / 1024 * 1024;
+  static constexpr int kStageBytes = kWBytes + kXPad;
+  static constexpr int kSlotBytes = MN * BM * 4;                    // one accumulator tile: [row group][column] float4
+  static constexpr int kStagingBytes = 3 * kSlotBytes;              // up to three peers
+  static constexpr int kStages = (224 * 1024 - kStagingBytes) / kStageBytes > 12 ? 12 : (224 * 1024 - kStagingBytes) / kStageBytes;
+  static constexpr int kTmemCols = MN < 32 ? 32 : MN;
+  static constexpr int kBarBytes = (2 * kStages + 2) * 8 + 16;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kStagingBytes + kBarBytes;
+  static_assert(kSmemBytes <= 227 * 1024 && kStages >= 4, "smem");
+};
+
+// a.n_tiles 128-column tiles; grid = S x a.n_tiles; a.num_kb >= S.
+template <int MN, int S>
+__global__ void __cluster_dims__(S, 1, 1) __launch_bounds__(kGemmThreads, 1)
+    gemm_f16_tcgen05_swap_kc_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                                    const __grid_constant__ CUtensorMap tmap_x, const GemmArgs a) {
+  using C = SwapKcCfg<MN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t staging = base + C::kStages * C::kStageBytes;
+  const uint32_t bars = staging + C::kStagingBytes;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (C::kStages + s); };
+  const uint32_t tfull_bar = bars + 8u * (2 * C::kStages);
+  const uint32_t data_bar = bars + 8u * (2 * C::kStages + 1);
+  const uint32_t tmem_slot = bars + 8u * (2 * C::kStages + 2);
+  uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  float4* staging4 = reinterpret_cast<float4*>(gen_base + C::kStages * C::kStageBytes);
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(
+      gen_base + C::kStages * C::kStageBytes + C::kStagingBytes + 8 * (2 * C::kStages + 2));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int nt = blockIdx.x / S;
+  const int per = (a.num_kb + S - 1) / S;
+  const int kb0 = min((int)rank * per, a.num_kb), kb1 = min(kb0 + per, a.num_kb);   // the last slices may be short or empty
+
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_x)) : "memory");
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(tfull_bar, 1);
+    mbar_init(data_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (rank == 0) mbar_expect_tx(data_bar, (S - 1) * C::kSlotBytes);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+  pdl_wait();
+  pdl_launch_dependents();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(empty_bar(stage), phase ^ 1u, a.status, ERR_PRODUCER)) break;
+        mbar_expect_tx(full_bar(stage), C::kWBytes + C::kXBytes);
+        const uint32_t sa = base + stage * C::kStageBytes;
+        tma_load_2d(sa, &tmap_w, kb * BK, nt * BM, full_bar(stage));
+        tma_load_2d(sa + C::kWBytes, &tmap_x, kb * BK, 0, full_bar(stage));
+        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16_f32(MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(full_bar(stage), phase, a.status, ERR_MMA_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sa = base + stage * C::kStageBytes;
+        const uint64_t da = make_kmajor_sw128_desc(sa);
+        const uint64_t db = make_kmajor_sw128_desc(sa + C::kWBytes);
+#pragma unroll
+        for (int kk = 0; kk < BK / UMMA_K; ++kk)
+          umma_f16(tmem_base, da + 2u * kk, db + 2u * kk, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
+        umma_commit(empty_bar(stage));
+        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+      }
+      if (ok) umma_commit(tfull_bar);     // with an empty slice this arrives at once
+    }
+    __syncwarp();
+  } else {
+    const int quarter = warp & 3;
+    const int epi_tid = threadIdx.x - 64;
+    const int c_in_tile = quarter * 32 + lane;
+    const int col = nt * BM + c_in_tile;
+    const bool col_ok = col < a.n;
+    const bool mine_empty = kb1 <= kb0;                 // nothing accumulated: this CTA contributes zeros
+    const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    constexpr int kChunk = MN < 32 ? 16 : 32;
+    bool ok = mbar_wait(tfull_bar, 0u, a.status, ERR_EPILOGUE);
+    tc_fence_after();
+    if (rank != 0) {
+      if (ok) {
+#pragma unroll 1
+        for (int c = 0; c < MN / kChunk; ++c) {
+          uint32_t r[kChunk];
+          if constexpr (kChunk == 16) tmem_ld16(t_addr + c * kChunk, r);
+          else tmem_ld32(t_addr + c * kChunk, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < kChunk / 4; ++q) {
+            const int g = c * (kChunk / 4) + q;
+            staging4[g * BM + c_in_tile] =
+                mine_empty ? make_float4(0.f, 0.f, 0.f, 0.f)
+                           : make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                         __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+          }
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      epilogue_bar_sync();
+      if (epi_tid == 0 && ok)
+        bulk_copy_to_peer(mapa_u32(staging + (rank - 1) * C::kSlotBytes, 0), staging, C::kSlotBytes, mapa_u32(data_bar, 0));
+    } else {
+      if (ok) ok = mbar_wait(data_bar, 0u, a.status, ERR_K2_DATA);
+      if (ok) {
+        const float bias = (a.epi.bias != nullptr && col_ok) ? __half2float(a.epi.bias[col]) : 0.f;
+#pragma unroll 1
+        for (int c = 0; c < MN / kChunk; ++c) {
+          uint32_t r[kChunk];
+          if constexpr (kChunk == 16) tmem_ld16(t_addr + c * kChunk, r);
+          else tmem_ld32(t_addr + c * kChunk, r);
+          tmem_ld_wait();
+          if (col_ok) {
+            float f[kChunk];
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j) f[j] = __uint_as_float(r[j]);
+#pragma unroll
+            for (int p = 0; p < S - 1; ++p) {          // rank order = K order
+#pragma unroll
+              for (int q = 0; q < kChunk / 4; ++q) {
+                const float4 v = staging4[(p * (MN / 4) + c * (kChunk / 4) + q) * BM + c_in_tile];
+                f[4 * q] += v.x; f[4 * q + 1] += v.y; f[4 * q + 2] += v.z; f[4 * q + 3] += v.w;
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j) f[j] += bias;
+            epi_store_column<kChunk>(a.epi, a.y, a.ldy, c * kChunk, a.m, col, f);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // SIMT fallback for shapes TMA cannot describe (k % 8 != 0 or unaligned bases): one thread
 // per output element, fp32 accumulation.  Correct for every shape, not a performance path.
 // ---------------------------------------------------------------------------------------
@@ -1443,6 +1621,7 @@ struct GemmPlan {
   bool simt;
   bool pair = false;   // two-CTA 256 x 256 tiles (gemm_f16_tcgen05_pair_kernel)
   bool k2 = false;     // K cut in two inside a cluster of two CTAs (gemm_f16_tcgen05_k2_kernel<bn>), bn = 64 or 128
+  int kc = 0;          // > 0: swapped operands, K cut in kc = 2..4 slices inside a cluster (m <= 32)
   int swap_mn = 0;     // > 0: swapped-operand kernel with the X tile padded to this many rows
   int sk_per = 0;      // swapped kernel, stream-K: (tile, k-block) units per CTA (0 = fixed split)
   int sk_grid = 0;     //   CTAs launched
@@ -1495,6 +1674,7 @@ constexpr int kSwapMaxM = 64;            // beyond that the X tile crowds W out 
 constexpr bool kPairByDefault = true;    // consider two-CTA tiles
 constexpr int kPairMinM = 257;           // below that a 256-row tile is mostly padding
 constexpr bool kK2ByDefault = true;      // consider the cluster K-split kernel where it fits one wave
+constexpr bool kSwapKcByDefault = true;  // the same for the swapped-operand kernel at m <= 32
 constexpr size_t kSplitKWorkspaceBytes = 64ull << 20;
 constexpr int kTileCounters = 4096;
 
@@ -1518,6 +1698,13 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
     p.bn = obn0 - 8192;
     p.splits = 1;
     p.k2 = true;
+    return p;
+  }
+  if (obn0 >= 16384 + 2 && obn0 <= 16384 + 4 && m <= 32 && num_kb >= obn0 - 16384) {   // tile codes 16386 .. 16388
+    p.swap_mn = m <= 16 ? 16 : 32;
+    p.bn = BM;
+    p.splits = 1;
+    p.kc = obn0 - 16384;
     return p;
   }
   if (obn0 >= 8192) obn0 = 0;      // not applicable to this shape: plan as usual
@@ -1590,6 +1777,13 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
           p.kb_per_split = num_kb;
         }
       }
+    }
+    // Fixed split of 2..4 in one wave at m <= 32: the slices are the CTAs of a cluster and hand over through
+    // shared memory instead of the workspace.
+    if (kSwapKcByDefault && obn0 == 0 && osp0 == 0 && p.sk_per == 0 && m <= 32 && p.splits >= 2 && p.splits <= 4 &&
+        t * p.splits <= sm_count) {
+      p.kc = p.splits;
+      p.splits = 1;
     }
     return p;
   }
@@ -1831,6 +2025,23 @@ int launch_k2(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a, c
   return after_launch("gemm_f16_tcgen05_k2_kernel");
 }
 
+template <int MN, int S>
+int launch_swap_kc(const CUtensorMap& tw, const CUtensorMap& tx, const GemmArgs& a, cudaStream_t st) {
+  using C = SwapKcCfg<MN>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  DTAS_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_set[dev]) {
+    DTAS_CUDA(cudaFuncSetAttribute((gemm_f16_tcgen05_swap_kc_kernel<MN, S>), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   C::kSmemBytes));
+    attr_set[dev] = true;
+  }
+  const int64_t grid = (int64_t)S * a.n_tiles;
+  if (grid > 0x7fffffffLL) DTAS_FAIL(DTAS_EINVAL, "gemm: too many tiles");
+  launch_kernel(gemm_f16_tcgen05_swap_kc_kernel<MN, S>, (unsigned)grid, kGemmThreads, C::kSmemBytes, st, tw, tx, a);
+  return after_launch("gemm_f16_tcgen05_swap_kc_kernel");
+}
+
 template <int MN>
 int launch_swap(const CUtensorMap& tw, const CUtensorMap& tx, const GemmArgs& a, int sm_count, cudaStream_t st) {
   using C = SwapCfg<MN>;
@@ -1953,6 +2164,17 @@ int launch_gemm(const void* x, const void* w, const Epilogue& epi, void* y, int6
       a.ws = ctx->splitk_ws;
       a.counters = ctx->tile_counters;
     }
+    if (p.kc > 0) {
+      const int code = (p.swap_mn == 16 ? 0 : 10) + p.kc;
+      switch (code) {
+        case 2: return launch_swap_kc<16, 2>(tw, tx, a, st);
+        case 3: return launch_swap_kc<16, 3>(tw, tx, a, st);
+        case 4: return launch_swap_kc<16, 4>(tw, tx, a, st);
+        case 12: return launch_swap_kc<32, 2>(tw, tx, a, st);
+        case 13: return launch_swap_kc<32, 3>(tw, tx, a, st);
+        default: return launch_swap_kc<32, 4>(tw, tx, a, st);
+      }
+    }
     switch (p.swap_mn) {
       case 16: return launch_swap<16>(tw, tx, a, ctx->sm_count, st);
       case 32: return launch_swap<32>(tw, tx, a, ctx->sm_count, st);
@@ -1980,6 +2202,10 @@ void gemm_variant_name(int64_t m, int64_t n, int64_t k, const DeviceCtx* ctx, ch
   }
   if (p.k2) {
     snprintf(buf, len, "gemm_tcgen05_bm128_bn%d_bk64_s%d_k2cluster", p.bn, p.bn == 128 ? K2Cfg<128>::kStages : K2Cfg<64>::kStages);
+    return;
+  }
+  if (p.swap_mn > 0 && p.kc > 0) {
+    snprintf(buf, len, "gemm_tcgen05_swap_n128_m%d_bk64_k%dcluster", p.swap_mn, p.kc);
     return;
   }
   if (p.swap_mn > 0) {

@@ -133,12 +133,15 @@ class Engine:
         """(tile code, split) candidates for row counts up to m_hi; tile codes as in
         dtas_gemm_set_override (64/128/256 single-CTA widths, 512 two-CTA, 1024 swapped operands with a
         fixed split, 2048 swapped operands with stream-K, 4096 + width single-CTA tiles with stream-K,
-        8192 + width K cut in two inside a two-CTA cluster)."""
+        8192 + width K cut in two inside a two-CTA cluster, 16384 + S swapped operands with K cut in S
+        inside a cluster)."""
         cands = []
         if m_hi <= 256:
             cands += [(1024, s) for s in (1, 2, 3, 4, 6, 8, 12, 16)] + [(2048, 0)]
             cands += [(bn, s) for bn in (64, 128, 256) for s in (1, 2, 4)] + [(4096 + bn, 0) for bn in (64, 128)]
             cands += [(8192 + 64, 0), (8192 + 128, 0)]
+            if m_hi <= 32:
+                cands += [(16384 + s, 0) for s in (2, 3, 4)]
         elif m_hi <= 1024:
             cands += [(bn, s) for bn in (128, 256) for s in (1, 2)] + [(512, 1), (4096 + 128, 0), (4096 + 256, 0), (8192 + 64, 0), (8192 + 128, 0)]
         else:

@@ -327,6 +327,33 @@ def test_gemm_two_cta_kernel(cuda_device, m, n, k):
     assert err <= 2e-2 * ref.abs().max().item()
 
 
+@pytest.mark.parametrize("slices", [2, 3, 4])
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (16, 4096, 11008), (17, 1000, 1096), (32, 520, 320), (5, 136, 256)])
+def test_gemm_swapped_kernel_cluster_k_split(cuda_device, m, n, k, slices):
+    """Swapped operands with K cut in 2..4 slices inside a cluster (codes 16386..16388): ragged n and k,
+    slices of unequal length (k = 320: five k-blocks) down to an empty one, bias, strided output."""
+    x = seeded_normal((m, k), 87, "float16")
+    w = seeded_normal((n, k), 88, "float16", scale=0.02)
+    b = seeded_normal((n,), 89, "float16", scale=0.1)
+    xd, wd, bd = x.to(cuda_device), w.to(cuda_device), b.to(cuda_device)
+    wide = torch.full((m, n + 16), 5.0, dtype=torch.float16, device=cuda_device)
+    y = wide[:, :n]
+    _abi.check(_abi.lib().dtas_gemm_set_override(16384 + slices, 0))
+    try:
+        assert f"k{slices}cluster" in _abi.variant_of("gemm", m, n, k)
+        ops.gemm_nt(xd, wd, y, bias=bd)
+        ops.poll_status()
+        first = y.clone()
+        ops.gemm_nt(xd, wd, y, bias=bd)
+        ops.poll_status()
+    finally:
+        _abi.check(_abi.lib().dtas_gemm_set_override(0, 0))
+    assert torch.equal(first, y), "two runs differ"
+    assert bool((wide[:, n:] == 5.0).all()), "wrote outside its column slab"
+    want = x.float().numpy() @ w.float().numpy().T + b.float().numpy()
+    util.assert_matmul_close(np_of(y), want, f"swap kc gemm m={m} n={n} k={k} slices={slices}")
+
+
 @pytest.mark.parametrize("code", [8256, 8320])
 @pytest.mark.parametrize("m,n,k", [(255, 4096, 4096), (512, 4096, 11008), (130, 200, 136), (1, 64, 128), (300, 1000, 72), (2000, 520, 1160)])
 def test_gemm_cluster_k_split_kernel(cuda_device, m, n, k, code):
