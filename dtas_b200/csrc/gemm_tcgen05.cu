@@ -1355,8 +1355,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 }
 
 // ---------------------------------------------------------------------------------------
-// The same hand-over for the swapped-operand kernel at m <= 32: K cut in S = 2, 3 or 4 slices, the
-// S CTAs of a cluster.  CTAs 1 .. S-1 send their MN x 128 accumulators (8 or 16 KB) into slots of
+// The same hand-over for the swapped-operand kernel at m <= 64: K cut in S = 2, 3 or 4 slices, the
+// S CTAs of a cluster.  CTAs 1 .. S-1 send their MN x 128 accumulators (8 - 32 KB) into slots of
 // CTA 0's staging area with one bulk copy each; CTA 0 adds them to its own in rank order = K order.
 // One 128-column tile of Y per cluster; single wave.
 // ---------------------------------------------------------------------------------------
@@ -1621,7 +1621,7 @@ struct GemmPlan {
   bool simt;
   bool pair = false;   // two-CTA 256 x 256 tiles (gemm_f16_tcgen05_pair_kernel)
   bool k2 = false;     // K cut in two inside a cluster of two CTAs (gemm_f16_tcgen05_k2_kernel<bn>), bn = 64 or 128
-  int kc = 0;          // > 0: swapped operands, K cut in kc = 2..4 slices inside a cluster (m <= 32)
+  int kc = 0;          // > 0: swapped operands, K cut in kc = 2..4 slices inside a cluster (m <= 64)
   int swap_mn = 0;     // > 0: swapped-operand kernel with the X tile padded to this many rows
   int sk_per = 0;      // swapped kernel, stream-K: (tile, k-block) units per CTA (0 = fixed split)
   int sk_grid = 0;     //   CTAs launched
@@ -1674,7 +1674,8 @@ constexpr int kSwapMaxM = 64;            // beyond that the X tile crowds W out 
 constexpr bool kPairByDefault = true;    // consider two-CTA tiles
 constexpr int kPairMinM = 257;           // below that a 256-row tile is mostly padding
 constexpr bool kK2ByDefault = true;      // consider the cluster K-split kernel where it fits one wave
-constexpr bool kSwapKcByDefault = true;  // the same for the swapped-operand kernel at m <= 32
+constexpr bool kSwapKcByDefault = true;  // the same for the swapped-operand kernel
+constexpr int kSwapKcMaxM = 32;          //   by default up to this m (codes 16386..16388 force it up to m = 64)
 constexpr size_t kSplitKWorkspaceBytes = 64ull << 20;
 constexpr int kTileCounters = 4096;
 
@@ -1700,8 +1701,8 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
     p.k2 = true;
     return p;
   }
-  if (obn0 >= 16384 + 2 && obn0 <= 16384 + 4 && m <= 32 && num_kb >= obn0 - 16384) {   // tile codes 16386 .. 16388
-    p.swap_mn = m <= 16 ? 16 : 32;
+  if (obn0 >= 16384 + 2 && obn0 <= 16384 + 4 && m <= 64 && num_kb >= obn0 - 16384) {   // tile codes 16386 .. 16388
+    p.swap_mn = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
     p.bn = BM;
     p.splits = 1;
     p.kc = obn0 - 16384;
@@ -1780,8 +1781,8 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
     }
     // Fixed split of 2..4 in one wave at m <= 32: the slices are the CTAs of a cluster and hand over through
     // shared memory instead of the workspace.
-    if (kSwapKcByDefault && obn0 == 0 && osp0 == 0 && p.sk_per == 0 && m <= 32 && p.splits >= 2 && p.splits <= 4 &&
-        t * p.splits <= sm_count) {
+    if (kSwapKcByDefault && obn0 == 0 && osp0 == 0 && p.sk_per == 0 && m <= kSwapKcMaxM && p.splits >= 2 && p.splits <= 4 &&
+        t * p.splits <= sm_count - (p.splits >= 3 ? 16 : 4)) {   // clusters do not pack every SM of every GPC
       p.kc = p.splits;
       p.splits = 1;
     }
@@ -1827,7 +1828,7 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
       const double an = active / am < 1.0 ? 1.0 : active / am;
       const double t_hbm = 128.0 * (an * bn + am * rows_x) / kHbmGBs;
       double cost = (double)rounds * (kb_per * (t_core > t_hbm ? t_core : t_hbm) + kItemFixedNs);
-      if (s == 2 && bn <= 128 && rounds == 1 && kK2ByDefault) {
+      if (s == 2 && bn <= 128 && work <= sm_count - 4 && kK2ByDefault) {
         // the same main loop, the second half handed over through shared memory (~1.5 us measured
         // against ~4.5 us through the workspace at m = 255)
         const double c2 = cost + 1500.0;
@@ -2165,14 +2166,17 @@ int launch_gemm(const void* x, const void* w, const Epilogue& epi, void* y, int6
       a.counters = ctx->tile_counters;
     }
     if (p.kc > 0) {
-      const int code = (p.swap_mn == 16 ? 0 : 10) + p.kc;
+      const int code = (p.swap_mn == 16 ? 0 : (p.swap_mn == 32 ? 10 : 20)) + p.kc;
       switch (code) {
         case 2: return launch_swap_kc<16, 2>(tw, tx, a, st);
         case 3: return launch_swap_kc<16, 3>(tw, tx, a, st);
         case 4: return launch_swap_kc<16, 4>(tw, tx, a, st);
         case 12: return launch_swap_kc<32, 2>(tw, tx, a, st);
         case 13: return launch_swap_kc<32, 3>(tw, tx, a, st);
-        default: return launch_swap_kc<32, 4>(tw, tx, a, st);
+        case 14: return launch_swap_kc<32, 4>(tw, tx, a, st);
+        case 22: return launch_swap_kc<64, 2>(tw, tx, a, st);
+        case 23: return launch_swap_kc<64, 3>(tw, tx, a, st);
+        default: return launch_swap_kc<64, 4>(tw, tx, a, st);
       }
     }
     switch (p.swap_mn) {

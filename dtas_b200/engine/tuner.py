@@ -140,7 +140,7 @@ class Engine:
             cands += [(1024, s) for s in (1, 2, 3, 4, 6, 8, 12, 16)] + [(2048, 0)]
             cands += [(bn, s) for bn in (64, 128, 256) for s in (1, 2, 4)] + [(4096 + bn, 0) for bn in (64, 128)]
             cands += [(8192 + 64, 0), (8192 + 128, 0)]
-            if m_hi <= 32:
+            if m_hi <= 64:
                 cands += [(16384 + s, 0) for s in (2, 3, 4)]
         elif m_hi <= 1024:
             cands += [(bn, s) for bn in (128, 256) for s in (1, 2)] + [(512, 1), (4096 + 128, 0), (4096 + 256, 0), (8192 + 64, 0), (8192 + 128, 0)]

@@ -159,7 +159,7 @@ int dtas_variant_of(const char* op, int64_t m, int64_t n, int64_t k, int device,
  * 1024 = the swapped-operand kernel, which applies to m <= 256; 2048 = the same kernel with
  * stream-K work distribution; 4096 + 64/128/256 = single-CTA tiles of that width with stream-K;
  * 8192 + 64/128 = tiles of that width with K cut in two inside a two-CTA cluster, the second half
- * handed over through shared memory; 16384 + 2/3/4 = the swapped-operand kernel (m <= 32) with K cut
+ * handed over through shared memory; 16384 + 2/3/4 = the swapped-operand kernel (m <= 64) with K cut
  * in that many slices inside a cluster; split_k is ignored by the stream-K and cluster codes) and
  * split-K factor (0 = automatic). */
 int dtas_gemm_set_override(int bn, int split_k);

@@ -328,7 +328,8 @@ def test_gemm_two_cta_kernel(cuda_device, m, n, k):
 
 
 @pytest.mark.parametrize("slices", [2, 3, 4])
-@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (16, 4096, 11008), (17, 1000, 1096), (32, 520, 320), (5, 136, 256)])
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (16, 4096, 11008), (17, 1000, 1096), (32, 520, 320), (5, 136, 256),
+                                   (33, 1000, 1096), (64, 4096, 4096)])
 def test_gemm_swapped_kernel_cluster_k_split(cuda_device, m, n, k, slices):
     """Swapped operands with K cut in 2..4 slices inside a cluster (codes 16386..16388): ragged n and k,
     slices of unequal length (k = 320: five k-blocks) down to an empty one, bias, strided output."""
