@@ -1675,7 +1675,7 @@ constexpr bool kPairByDefault = true;    // consider two-CTA tiles
 constexpr int kPairMinM = 257;           // below that a 256-row tile is mostly padding
 constexpr bool kK2ByDefault = true;      // consider the cluster K-split kernel where it fits one wave
 constexpr bool kSwapKcByDefault = true;  // the same for the swapped-operand kernel
-constexpr int kSwapKcMaxM = 32;          //   by default up to this m (codes 16386..16388 force it up to m = 64)
+constexpr int kSwapKcMaxM = 64;          //   up to this m (the X tile of larger m leaves too little room for the slots)
 constexpr size_t kSplitKWorkspaceBytes = 64ull << 20;
 constexpr int kTileCounters = 4096;
 
