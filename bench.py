@@ -17,9 +17,11 @@ With N GPUs the same sweep is sharded (GEMM / GEMV by output columns, the other 
 no collective on the data path; "scaling": "strong") and the value is still relative to one
 GPU's roofline, so value(N) / value(1) is the speed-up.
 
-Also reported: per-point device times from CUDA-graph replay ("points"), the roofline of the
-dominant kernel, an end-to-end figure through the public API with host buffers ("e2e"), the
-CPU baseline, SM clocks during the timed region, and the number of kernels launched.
+Also reported: per-point device times from CUDA-graph replay ("points", with the fraction of the
+measured and of the data-sheet peaks), the roofline of the dominant kernel, an end-to-end figure
+through the public API with host buffers ("e2e"), the CPU baseline, SM clocks during the timed
+region, the number of kernels launched and, with N > 1, what gathering a column-sharded result
+onto every rank adds ("gathered_points": kernel alone against kernel + one NCCL all-gather).
 
 `--impl reference` times the reference workload PrimFuncs on the host CPU instead (built by
 TVM for target "c" when that runtime is available on the box, else the C port under oracle/).
@@ -66,6 +68,12 @@ def roofline_ns(op, m, n, k, peaks):
     t_hbm = a["bytes"] / peaks["hbm_gbs"]                     # bytes / (GB/s) = ns
     t_tc = a["flops"] / (peaks["bf16_tflops"] * 1e3)          # flop / (TFLOP/s) = ps -> /1e3 = ns
     return max(t_hbm, t_tc), ("tensor" if t_tc > t_hbm else "hbm")
+
+
+def nominal_ns(op, m, n, k):
+    """The same bound at the data-sheet peaks (8 TB/s, 2.25 PFLOP/s dense fp16)."""
+    from dtas_b200.profiling import NOMINAL
+    return roofline_ns(op, m, n, k, {"hbm_gbs": NOMINAL["hbm_gbs"], "bf16_tflops": NOMINAL["fp16_tflops"]})[0]
 
 
 def shard(total, rank, world):
@@ -287,6 +295,66 @@ def fused_points(dev, peaks):
     return out
 
 
+GATHER_POINTS = [("gemm", 8192, 22016, 4096), ("gemm", 64, 4096, 4096), ("gemv", 1, 32000, 4096)]
+
+
+def gather_points(rank, world, dev, barrier):
+    """N > 1 only: what a caller pays who needs the whole Y on every rank.  Per point the kernel
+    alone (this rank's column slab, written into its slot of the [g, m, N/g] buffer) and the
+    kernel followed by one NCCL all-gather of that buffer, and the same result by pushing row
+    blocks into the peers' buffers behind the kernel (this library's push kernel, or one
+    cudaMemcpyAsync per peer), all timed with CUDA events on the launching stream over a batch of
+    eager calls, max over ranks.  Weights rotate through enough
+    copies that a shard is not served from L2."""
+    import torch
+    import torch.distributed as dist
+    from dtas_b200.dist import ColumnShardedLinear, PeerGatherBuffer
+    from dtas_b200.profiling import rotation_for
+    f16 = torch.float16
+    out = []
+    for (op, m, n, k) in GATHER_POINTS:
+        if n % world:
+            continue
+        n_local = n // world
+        copies = min(8, rotation_for(2 * n_local * k))
+        gen = torch.Generator(device=dev).manual_seed(77 + rank)
+        x = torch.randn((m, k), generator=gen, device=dev, dtype=torch.float32).to(f16)
+        lins = [ColumnShardedLinear((torch.randn((n_local, k), generator=gen, device=dev, dtype=torch.float32) * 0.02).to(f16),
+                                    n, rank=rank, world=world, already_sharded=True) for _ in range(copies)]
+        buf = lins[0].gather_buffer(m, f16, dev)
+        reps = 20 if m >= 1024 else 100
+
+        def timed(fn):
+            for i in range(3):
+                fn(i)
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(reps):
+                fn(i)
+            e1.record()
+            e1.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) * 1e3 / reps], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+
+        local_us = timed(lambda i: lins[i % copies].forward_local(x, out=buf[rank]))
+        gathered_us = timed(lambda i: lins[i % copies].forward_gathered(x, buf=buf))
+        pushed = {}
+        for engine in ("kernel", "copy"):
+            pbuf = PeerGatherBuffer(world, m, n_local, f16, dev, engine=engine)
+            pushed[engine] = timed(lambda i: lins[i % copies].forward_pushed(x, pbuf, min_push_bytes=0))
+            del pbuf
+        out.append({"op": op, "m": m, "n": n, "k": k, "kernel_us": round(local_us, 2),
+                    "kernel_plus_all_gather_us": round(gathered_us, 2),
+                    "kernel_plus_peer_push_us": round(pushed["kernel"], 2),
+                    "kernel_plus_copy_engine_push_us": round(pushed["copy"], 2),
+                    "gather_bytes_per_rank": 2 * m * n_local, "mode": "eager calls, max over ranks"})
+        del lins, buf, x
+        torch.cuda.empty_cache()
+    return out
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
@@ -342,6 +410,7 @@ def run_gpu(args):
         launches = int(lt.item())
     ms_per_step = elapsed_ms / args.steps
     value = 100.0 * (ideal_ns * 1e-6) / ms_per_step
+    value_nominal = 100.0 * (sum(nominal_ns(*p) for p in points) * 1e-6) / ms_per_step
 
     # ---- end to end through the public API with host buffers ------------------------------
     pinned_in = [[torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t) for t in ins] for ins, _ in sweep.e2e]
@@ -419,6 +488,7 @@ def run_gpu(args):
             a = algorithmic(op, m_local, n_local, k)
             per_point.append({"op": op, "m": m, "n": n, "k": k, "us": round(t["mean_us"], 2), "bound": bound,
                               "frac": round(ns * 1e-3 / t["mean_us"], 3),
+                              "frac_nominal": round(nominal_ns(op, m_local, n_local, k) * 1e-3 / t["mean_us"], 3),
                               "gbs": round(a["bytes"] / t["mean_us"] / 1e3, 1),
                               "tflops": round(a["flops"] / t["mean_us"] / 1e6, 1), "copies": copies,
                               "variant": _abi.variant_of(op, m_local, n_local, k, local)})
@@ -426,6 +496,7 @@ def run_gpu(args):
                 dominant = ((op, m_local, n_local, k), t)
         torch.cuda.empty_cache()
     fused = fused_points(dev, peaks) if (per_point and world == 1) else None
+    gathered = gather_points(rank, world, dev, barrier) if (world > 1 and not args.no_points) else None
     roofline = None
     if dominant is not None:
         (op, m, n, k), t = dominant
@@ -462,9 +533,11 @@ def run_gpu(args):
                             "every step on copy streams chained to the kernels by events; weights stay resident"},
             "gpu_launches": launches,
             "clocks": clocks,
+            "value_vs_nominal_peaks": round(value_nominal, 2),
             "mean_point_frac": mean_frac,
             "points": per_point,
             "fused_points": fused,
+            "gathered_points": gathered,
         }
         print(json.dumps(line))
     if world > 1:

@@ -14,7 +14,7 @@ CSRC = os.path.join(_HERE, "csrc")
 LIB_DIR = os.path.join(_HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libdtas_b200.so")
 
-SOURCES = ["dispatch.cu", "elementwise.cu", "row_reduce.cu", "gemv.cu", "gemm_tcgen05.cu"]
+SOURCES = ["dispatch.cu", "elementwise.cu", "row_reduce.cu", "gemv.cu", "gemm_tcgen05.cu", "peer_push.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--threads", "4", "-shared", "-Xcompiler", "-fPIC",

@@ -140,6 +140,8 @@ int launch_add_residuals(void* y, const void* res1, const void* res2, int64_t n,
                          cudaStream_t st, int bucket);   // y += res1 (+ res2), fp16, in place
 int launch_copy(const void* a, void* out, int64_t nbytes, const DeviceCtx* ctx, cudaStream_t st,
                 int bucket);
+int launch_peer_push(const void* src, void* const* dsts, int n_dsts, int64_t bytes, const DeviceCtx* ctx,
+                     cudaStream_t st);
 const char* ew_variant_name(const char* op, int64_t m, int64_t n_cols, const DeviceCtx* ctx);
 void ew_set_override(int unroll, int ctas_per_sm, int hints);
 

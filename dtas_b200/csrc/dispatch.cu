@@ -142,6 +142,24 @@ int dtas_copy(const void* a, void* out, int64_t m, int64_t n_cols, int dtype, in
   return launch_copy(a, out, m * n_cols * es, c.ctx, c.stream, bucket_of(m));
 }
 
+int dtas_peer_push(const void* src, void* const* dsts, int n_dsts, int64_t bytes, int device, void* stream) {
+  DTAS_NONNULL("peer_push", src);
+  DTAS_NONNULL("peer_push", dsts);
+  if (n_dsts < 1 || n_dsts > DTAS_MAX_PEERS)
+    DTAS_FAIL(DTAS_EINVAL, "peer_push: n_dsts = %d is not in 1..%d", n_dsts, DTAS_MAX_PEERS);
+  if (bytes < 1) DTAS_FAIL(DTAS_EINVAL, "peer_push: bytes = %lld must be >= 1", (long long)bytes);
+  if (!aligned16(src)) DTAS_FAIL(DTAS_EALIGN, "peer_push: src is not 16-byte aligned");
+  for (int j = 0; j < n_dsts; ++j) {
+    if (dsts[j] == nullptr) DTAS_FAIL(DTAS_EINVAL, "peer_push: dsts[%d] is null", j);
+    if (!aligned16(dsts[j])) DTAS_FAIL(DTAS_EALIGN, "peer_push: dsts[%d] is not 16-byte aligned", j);
+    if (dsts[j] == src) DTAS_FAIL(DTAS_EINVAL, "peer_push: dsts[%d] is the source", j);
+  }
+  Call c;
+  int rc = c.begin(device, stream);
+  if (rc) return rc;
+  return launch_peer_push(src, dsts, n_dsts, bytes, c.ctx, c.stream);
+}
+
 int dtas_rms_norm(const void* x, const void* weight, void* y, int64_t m, int64_t n_cols, float eps,
                   int in_dtype, int device, void* stream) {
   DTAS_NONNULL("rms_norm", x);

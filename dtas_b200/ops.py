@@ -103,6 +103,19 @@ def copy(a, out):
     return out
 
 
+def peer_push(src, dsts):
+    """Copies the contiguous tensor `src` to every tensor of `dsts`: views, on this device, of the
+    same place in the other ranks' gather buffers (peer memory).  One launch, plain stores over
+    NVLink, no cross-rank waiting: run a barrier across ranks before a gathered buffer is read."""
+    import ctypes
+    dev, st = _check("peer_push", src, *dsts)
+    for d in dsts:
+        if d.dtype != src.dtype or d.numel() != src.numel():
+            raise _abi.DtasError(_abi.EINVAL, "peer_push: destination of another size or dtype")
+    ptrs = (ctypes.c_void_p * len(dsts))(*[d.data_ptr() for d in dsts])
+    _chk(_lib().dtas_peer_push(src.data_ptr(), ptrs, len(dsts), src.numel() * src.element_size(), dev, st))
+
+
 def rms_norm(x, weight, out, eps=1e-6):
     """out = x * rsqrt(mean(x^2, -1) + eps) * weight; fp32 arithmetic, fp16 result."""
     dev, st = _check("rms_norm", x, weight, out)

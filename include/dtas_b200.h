@@ -195,6 +195,21 @@ int dtas_gemv_set_override(int warps_per_row, int unroll);
  * previous mode, or -1 for any other value.                                                  */
 int dtas_set_pdl(int mode);
 
+/* ---- multi-GPU: pushing a column slab to the other ranks -------------------
+ * No counterpart in the reference, which opens one device (python/dtas/arch/RTX3090.py:6-7).
+ * With Y's columns sharded over g GPUs, dtas_peer_push copies `bytes` bytes at `src` (this rank's
+ * slab, or a block of its rows) to each of the n_dsts addresses in `dsts`: device pointers, valid
+ * in this process, to the same place in the other ranks' gather buffers (peer memory mapped
+ * through CUDA IPC or a symmetric-memory allocation).  `dsts` is a host array, read during the
+ * call.  One launch on `stream`: it reads the source once and stores over NVLink; it waits on no
+ * other rank and signals none, so the caller runs a barrier across ranks behind the last push
+ * before anyone reads a gathered buffer.  src and every destination must be 16-byte aligned
+ * (DTAS_EALIGN), 1 <= n_dsts <= DTAS_MAX_PEERS, bytes >= 1.  This replaces the all-gather a
+ * caller would run behind dtas_gemm_nt / dtas_gemv; Python: dtas_b200.dist.PeerGatherBuffer.
+ * The environment variable DTAS_B200_PUSH_CTAS limits its grid (default: one CTA per SM).     */
+#define DTAS_MAX_PEERS 7
+int dtas_peer_push(const void* src, void* const* dsts, int n_dsts, int64_t bytes, int device, void* stream);
+
 /* ---- bookkeeping ---------------------------------------------------------
  * dtas_last_error : message of the last failing call on this thread ("" if none).
  * dtas_launch_count: kernels launched by this library since load (all threads).

@@ -61,6 +61,24 @@ def _worker(rank, world, port, results):
             ops.poll_status(rank)
             err = (full.float() - want.float()).abs().max().item()
             ok[("fused", m)] = err <= 2e-2 * want.float().abs().max().item()
+        # the gather without a collective on the data: row blocks pushed into the peers' buffers
+        from dtas_b200.dist import PeerGatherBuffer
+        for engine in ("kernel", "copy"):
+            for (m, n, k, block) in [(1, 4096, 1024, 2048), (40, 2048, 1024, 2048), (2500, 2048, 512, 1024)]:
+                w = seeded_normal((n, k), 22, "float16", scale=0.02).to(dev)
+                b = seeded_normal((n,), 23, "float16", scale=0.5).to(dev)
+                lin = ColumnShardedLinear(w, n, bias=b)
+                pbuf = PeerGatherBuffer(world, m, n // world, torch.float16, dev, engine=engine)
+                same = True
+                for seed in (31, 32):          # the second call reuses the buffer
+                    x = seeded_normal((m, k), seed, "float16").to(dev)
+                    r1 = seeded_normal((m, n), seed + 10, "float16").to(dev)
+                    want = lin.forward_gathered(x, res1=r1).clone()
+                    got = lin.forward_pushed(x, pbuf, res1=r1, block_rows=block, min_push_bytes=0)
+                    ops.poll_status(rank)
+                    same = same and bool(torch.equal(got, want))
+                ok[("pushed", engine, m)] = same
+                del pbuf
         a = seeded_normal((7, 11008), 3, "float16").to(dev)
         b = seeded_normal((7, 11008), 4, "float16").to(dev)
         out = torch.zeros_like(a)
