@@ -1,0 +1,57 @@
+"""dtas_peer_push on one GPU: the destinations are ordinary buffers of the same device, which the
+kernel cannot tell from mapped peer memory.  Bit-exact copies, ragged byte counts, argument errors.
+The two-GPU path (real peer buffers) is in tests/test_dist_gpu.py."""
+import ctypes
+
+import pytest
+import torch
+
+from dtas_b200 import _abi, ops
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("n_dsts", [1, 3, 7])
+@pytest.mark.parametrize("numel", [8, 4096, 1 << 20, (1 << 22) + 8])
+def test_peer_push_copies_to_every_destination(cuda_device, n_dsts, numel):
+    g = torch.Generator(device=cuda_device).manual_seed(numel + n_dsts)
+    src = torch.randn(numel, generator=g, device=cuda_device).half()
+    dsts = [torch.zeros_like(src) for _ in range(n_dsts)]
+    before = _abi.launch_count()
+    ops.peer_push(src, dsts)
+    torch.cuda.synchronize()
+    assert _abi.launch_count() - before == 1
+    for d in dsts:
+        assert torch.equal(d.view(torch.int16), src.view(torch.int16))
+
+
+def test_peer_push_ragged_bytes_and_guard_band(cuda_device):
+    """A byte count that is not a multiple of 16, and nothing written past it."""
+    lib = _abi.lib()
+    src = torch.arange(0, 256, dtype=torch.uint8, device=cuda_device).repeat(5)          # 1280 bytes
+    dsts = [torch.full((1280,), 0xEE, dtype=torch.uint8, device=cuda_device) for _ in range(2)]
+    nbytes = 1000 + 7
+    ptrs = (ctypes.c_void_p * 2)(*[d.data_ptr() for d in dsts])
+    _abi.check(lib.dtas_peer_push(src.data_ptr(), ptrs, 2, nbytes, cuda_device.index or 0, None))
+    torch.cuda.synchronize()
+    for d in dsts:
+        assert torch.equal(d[:nbytes], src[:nbytes])
+        assert bool((d[nbytes:] == 0xEE).all())
+
+
+def test_peer_push_argument_errors(cuda_device):
+    lib = _abi.lib()
+    dev = cuda_device.index or 0
+    src = torch.zeros(64, dtype=torch.float16, device=cuda_device)
+    dst = torch.zeros(80, dtype=torch.float16, device=cuda_device)
+    one = (ctypes.c_void_p * 1)(dst.data_ptr())
+    assert lib.dtas_peer_push(src.data_ptr(), one, 0, 128, dev, None) == _abi.EINVAL
+    assert lib.dtas_peer_push(src.data_ptr(), one, 8, 128, dev, None) == _abi.EINVAL
+    assert lib.dtas_peer_push(src.data_ptr(), one, 1, 0, dev, None) == _abi.EINVAL
+    assert lib.dtas_peer_push(None, one, 1, 128, dev, None) == _abi.EINVAL
+    odd = (ctypes.c_void_p * 1)(dst.data_ptr() + 2)
+    assert lib.dtas_peer_push(src.data_ptr(), odd, 1, 128, dev, None) == _abi.EALIGN
+    same = (ctypes.c_void_p * 1)(src.data_ptr())
+    assert lib.dtas_peer_push(src.data_ptr(), same, 1, 128, dev, None) == _abi.EINVAL
+    with pytest.raises(_abi.DtasError):
+        ops.peer_push(src, [dst])                       # another size
