@@ -173,17 +173,21 @@ class PeerGatherBuffer:
     over NVLink (ColumnShardedLinear.forward_pushed).  Collective: every rank of `group`
     constructs it at the same point.
 
-    engine "copy" (default) moves a row block with one cudaMemcpyAsync per peer: copy engines, no
-    SM, which is what overlaps best with a GEMM that holds every SM.  engine "kernel" uses this
-    library's push kernel (ops.peer_push: the block is read once and stored to all peers in one
-    launch); its stores reach about 13 GB/s per CTA, so it needs most SMs to fill NVLink and loses
-    to the copy engines beside a large GEMM (m = 8192, N = 22016 on two GPUs: 729 us against
-    619 us; one all-gather behind the kernel: 889 us)."""
+    engine "copy" moves a row block with one cudaMemcpyAsync per peer: copy engines, no SM, which
+    is what overlaps best with a GEMM that holds every SM.  engine "kernel" uses this library's
+    push kernel (ops.peer_push: the block is read once and stored to all peers in one launch); its
+    stores reach about 13 GB/s per CTA and peer, so with one peer it needs most SMs to fill NVLink
+    and loses to the copy engines beside a large GEMM (m = 8192, N = 22016 on two GPUs: 729 us
+    against 619 us; one all-gather behind the kernel: 889 us), while with seven peers it fills
+    NVLink from a few SMs and one launch replaces seven copies (eight GPUs: 670 us against 838 us;
+    all-gather: 686 us).  "auto" takes "copy" for two ranks and "kernel" above."""
 
-    def __init__(self, world: int, m: int, n_local: int, dtype, device, group=None, engine: str = "copy"):
+    def __init__(self, world: int, m: int, n_local: int, dtype, device, group=None, engine: str = "auto"):
         import torch.distributed._symmetric_memory as symm
+        if engine == "auto":
+            engine = "copy" if world <= 2 else "kernel"
         if engine not in ("kernel", "copy"):
-            raise ValueError("engine is 'kernel' (this library's push kernel) or 'copy' (cudaMemcpyAsync per peer)")
+            raise ValueError("engine is 'auto', 'kernel' (this library's push kernel) or 'copy' (cudaMemcpyAsync per peer)")
         group = group if group is not None else dist.group.WORLD
         self.group = group
         self.rank = dist.get_rank(group)
