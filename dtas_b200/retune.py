@@ -2,6 +2,7 @@
 
     python -m dtas_b200.retune --out dtas_b200/tables/b200_gemm.json            # Llama-2-7B shapes, 1/2/4/8-way shards
     python -m dtas_b200.retune --shape 4096x4096 --shape 5120x13824 --out my_table.json
+    python -m dtas_b200.retune --shape 2560x2560 --merge-into dtas_b200/tables/b200_gemm.json --out dtas_b200/tables/b200_gemm.json
 
 The reference tunes every PrimFunc of a model once, offline, and ships the per-range winners
 inside the generated host code (python/dtas/engine/tuner.py:103-133, 211-299).  This is the
@@ -31,6 +32,12 @@ def default_shapes():
     return shapes
 
 
+def merge_tables(old, new):
+    """Shapes of `old` that `new` does not re-measure, then every shape of `new`."""
+    fresh = {(s["n"], s["k"]) for s in new}
+    return [s for s in old if (s["n"], s["k"]) not in fresh] + list(new)
+
+
 def main():
     import torch
     from . import _abi
@@ -46,6 +53,7 @@ def main():
     ap.add_argument("--device", type=int, default=0)
     ap.add_argument("--min-repeat-ms", type=float, default=10.0)
     ap.add_argument("--details", default=None, help="also write every candidate's time per range to this JSON file")
+    ap.add_argument("--merge-into", default=None, help="an existing table: its shapes are kept, re-measured ones replaced")
     a = ap.parse_args()
     shapes = [tuple(int(v) for v in s.lower().split("x")) for s in a.shape] or default_shapes()
     set_log_level(0)
@@ -71,6 +79,8 @@ def main():
         for r in rows:
             print(f"n={n} k={k} m={r['m_lo']}..{r['m_hi']}: {r['variant']}  {r['us_at_end']} us", flush=True)
         table.append({"n": n, "k": k, "rows": rows})
+    if a.merge_into:
+        table = merge_tables(json.load(open(a.merge_into)).get("gemm", []), table)
     rec = {"device": torch.cuda.get_device_name(dev), "library": _abi.lib().dtas_version().decode(), "gemm": table}
     os.makedirs(os.path.dirname(os.path.abspath(a.out)), exist_ok=True)
     with open(a.out, "w") as f:

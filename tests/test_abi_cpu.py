@@ -125,3 +125,32 @@ def test_ops_reject_cpu_tensors():
         ops.cast(a, torch.zeros(2, 8, dtype=torch.float16))
     with pytest.raises(_abi.DtasError):
         ops.gemm_nt(a.half(), a.half(), torch.zeros(2, 2, dtype=torch.float16))
+
+
+def test_shipped_gemm_table_installs_and_decides(lib):
+    """Every row of the shipped measured table is accepted, the ranges of a shape tile 1 .. 2^30
+    without gaps, and with the table installed the dispatch answers with the row's variant.  It
+    covers the Llama-2-7B shapes with their column shards and the reference model's own weight
+    shapes (experiment/ModelIR/dolly-v2-3b-q0f16/before_dl.py: hidden size 2560, vocabulary 50280)."""
+    import json
+    with open(_abi.DEFAULT_GEMM_TABLE) as f:
+        rec = json.load(f)
+    shapes = {(s["n"], s["k"]): s["rows"] for s in rec["gemm"]}
+    for nk in [(12288, 4096), (4096, 4096), (22016, 4096), (4096, 11008), (2752, 4096), (512, 11008),
+               (7680, 2560), (2560, 2560), (10240, 2560), (2560, 10240), (50280, 2560)]:
+        assert nk in shapes, nk
+    lib.dtas_gemm_table_clear()
+    try:
+        assert _abi._install_default_tables(lib) == sum(len(r) for r in shapes.values())
+        for (n, k), rows in shapes.items():
+            assert rows[0]["m_lo"] == 1 and rows[-1]["m_hi"] == 1 << 30
+            for a, b in zip(rows, rows[1:]):
+                assert b["m_lo"] == a["m_hi"] + 1
+            for r in rows:
+                m = min(r["m_hi"], 8192)
+                got = _abi.variant_of("gemm", m, n, k)
+                # the padded-m suffix of the swapped kernel depends on m inside the range
+                assert got.split("_m")[0] == r["variant"].split("_m")[0], (n, k, m, got, r["variant"])
+    finally:
+        lib.dtas_gemm_table_clear()
+        _abi._install_default_tables(lib)
