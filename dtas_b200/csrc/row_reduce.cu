@@ -259,7 +259,8 @@ __global__ void __launch_bounds__(TPR > kCtaThreads ? TPR : kCtaThreads)
 }
 
 // Any n_cols / any alignment: one CTA per row, scalar accesses, the row re-read from
-// global memory (L2) for each pass.  Only used when the vector path does not apply.
+// global memory (L2) for each pass.  Only used when the vector path does not apply and the row
+// is longer than row_elems_kernel holds in registers (4096 columns).
 __device__ __forceinline__ float ld_as_f32(const __half* p, int64_t i) { return __half2float(p[i]); }
 __device__ __forceinline__ float ld_as_f32(const float* p, int64_t i) { return p[i]; }
 
@@ -330,6 +331,90 @@ __global__ void __launch_bounds__(kCtaThreads)
   }
 }
 
+// Rows whose length or alignment rules out 16-byte vectors (n_cols not a multiple of 8: the
+// reference sweeps softmax over reduction lengths such as 17, 1025 and 2049,
+// experiment/dtas_tuned/general_reduction/softmax/profile_dlight.py:8-52), up to 4096 columns:
+// the same one-read design with scalar accesses.  A row is owned by TPR threads, thread t holds
+// elements t, t + TPR, ... (up to MAXE of them) in registers, so a warp's loads and stores are
+// contiguous, HBM sees every element once in and once out, and rows share a CTA (8 rows of up
+// to 256 columns, 4 of up to 1024, 2 beyond) instead of taking one each.  Measured on 12800
+// rows of fp32: 17 columns 15.5 -> 3.2 us against one CTA per row.
+template <int OP, typename InT, int TPR, int MAXE>
+__global__ void __launch_bounds__(kCtaThreads)
+    row_elems_kernel(const InT* __restrict__ x, const void* __restrict__ p0,
+                     const void* __restrict__ p1, __half* __restrict__ y, int64_t m, int n_cols,
+                     float eps) {
+  constexpr int kRowsPerCta = kCtaThreads / TPR;
+  __shared__ float scratch_a[kCtaThreads / 32];
+  __shared__ float scratch_b[kCtaThreads / 32];
+  const int t = threadIdx.x % TPR;
+  const int64_t row = (int64_t)blockIdx.x * kRowsPerCta + threadIdx.x / TPR;
+  const bool live = row < m;
+  const InT* xr = x + (live ? row : 0) * (int64_t)n_cols;
+  __half* yr = y + (live ? row : 0) * (int64_t)n_cols;
+
+  pdl_wait();
+  pdl_launch_dependents();
+  float v[MAXE];
+#pragma unroll
+  for (int j = 0; j < MAXE; ++j) {
+    const int e = j * TPR + t;
+    v[j] = (live && e < n_cols) ? ld_as_f32(xr, e) : 0.f;
+  }
+
+  if constexpr (OP == ROW_RMSNORM) {
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAXE; ++j) ss = fmaf(v[j], v[j], ss);
+    ss = group_allreduce<TPR>(ss, SumOp(), scratch_a);
+    const float r = 1.0f / sqrtf(ss * (1.0f / (float)n_cols) + eps);
+    const __half* w = static_cast<const __half*>(p0);
+#pragma unroll
+    for (int j = 0; j < MAXE; ++j) {
+      const int e = j * TPR + t;
+      if (live && e < n_cols) yr[e] = __float2half_rn(__fmul_rn(__fmul_rn(v[j], r), __half2float(w[e])));
+    }
+  } else if constexpr (OP == ROW_SOFTMAX) {
+    float mx = kNegHuge;
+#pragma unroll
+    for (int j = 0; j < MAXE; ++j) mx = (j * TPR + t) < n_cols ? fmaxf(mx, v[j]) : mx;
+    mx = group_allreduce<TPR>(mx, MaxOp(), scratch_a);
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAXE; ++j) {
+      v[j] = (j * TPR + t) < n_cols ? fast_exp2((v[j] - mx) * kLog2e) : 0.f;
+      sum += v[j];
+    }
+    sum = group_allreduce<TPR>(sum, SumOp(), scratch_b);
+    const float inv = 1.0f / sum;
+#pragma unroll
+    for (int j = 0; j < MAXE; ++j) {
+      const int e = j * TPR + t;
+      if (live && e < n_cols) yr[e] = __float2half_rn(v[j] * inv);
+    }
+  } else {  // ROW_LAYERNORM
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAXE; ++j) {
+      s1 += v[j];
+      s2 = fmaf(v[j], v[j], s2);
+    }
+    s1 = group_allreduce<TPR>(s1, SumOp(), scratch_a);
+    s2 = group_allreduce<TPR>(s2, SumOp(), scratch_b);
+    const float inv_n = 1.0f / (float)n_cols;
+    const float mean = s1 * inv_n;
+    const float r = 1.0f / sqrtf(__fadd_rn(__fsub_rn(s2 * inv_n, __fmul_rn(mean, mean)), eps));
+    const float* g = static_cast<const float*>(p0);
+    const float* be = static_cast<const float*>(p1);
+#pragma unroll
+    for (int j = 0; j < MAXE; ++j) {
+      const int e = j * TPR + t;
+      if (live && e < n_cols)
+        yr[e] = __float2half_rn(__fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v[j], mean), r), g[e]), be[e]));
+    }
+  }
+}
+
 // ---- dispatch ------------------------------------------------------------------
 // Threads per row (TPR) and chunks per thread (MAXCH), per m-bucket.  From a sweep on B200
 // at 4096 columns (TPR 32..512, m = 33..8192): 256 threads per row up to m = 1024 (short
@@ -341,6 +426,8 @@ struct RowCfg {
   int tpr;
   int maxch;     // 2, 4, 8 or 16
   bool generic;
+  int elems_tpr;  // generic rows of up to 4096 columns: threads per row of row_elems_kernel (0 = not used)
+  int elems_max;  // ... and elements per thread (8 or 16)
 };
 std::atomic<int> g_row_tpr{0};
 
@@ -351,9 +438,13 @@ inline int pow2_ceil(int v) {
 }
 
 inline RowCfg row_cfg(int64_t m, int64_t n_cols, bool vec_ok, int in_dtype) {
-  RowCfg c{0, 0, false};
+  RowCfg c{0, 0, false, 0, 0};
   if (!vec_ok || n_cols > 65536) {
     c.generic = true;
+    if (n_cols <= 256) { c.elems_tpr = 32; c.elems_max = 8; }
+    else if (n_cols <= 1024) { c.elems_tpr = 64; c.elems_max = 16; }
+    else if (n_cols <= 2048) { c.elems_tpr = 128; c.elems_max = 16; }
+    else if (n_cols <= 4096) { c.elems_tpr = 128; c.elems_max = 32; }
     return c;
   }
   const int n_chunks = (int)(n_cols >> 3);
@@ -410,6 +501,21 @@ int launch_tpr(int tpr, const InT* x, const void* p0, const void* p1, __half* y,
 template <int OP, typename InT>
 int launch_typed(const RowCfg& c, const InT* x, const void* p0, const void* p1, __half* y,
                  int64_t m, int64_t n_cols, float eps, const DeviceCtx* ctx, cudaStream_t st) {
+  if (c.generic && c.elems_tpr > 0) {
+    const int64_t rows_per_cta = kCtaThreads / c.elems_tpr;
+    const int64_t grid = (m + rows_per_cta - 1) / rows_per_cta;
+    if (grid > 0x7fffffffLL) DTAS_FAIL(DTAS_EINVAL, "row op: too many rows (%lld)", (long long)m);
+    const int nc = (int)n_cols;
+    if (c.elems_tpr == 32)
+      launch_kernel(row_elems_kernel<OP, InT, 32, 8>, (unsigned)grid, kCtaThreads, 0, st, x, p0, p1, y, m, nc, eps);
+    else if (c.elems_tpr == 64)
+      launch_kernel(row_elems_kernel<OP, InT, 64, 16>, (unsigned)grid, kCtaThreads, 0, st, x, p0, p1, y, m, nc, eps);
+    else if (c.elems_max == 16)
+      launch_kernel(row_elems_kernel<OP, InT, 128, 16>, (unsigned)grid, kCtaThreads, 0, st, x, p0, p1, y, m, nc, eps);
+    else
+      launch_kernel(row_elems_kernel<OP, InT, 128, 32>, (unsigned)grid, kCtaThreads, 0, st, x, p0, p1, y, m, nc, eps);
+    return after_launch("row_elems_kernel");
+  }
   if (c.generic) {
     int64_t grid = m < (int64_t)ctx->sm_count * 8 ? m : (int64_t)ctx->sm_count * 8;
     launch_kernel(row_generic_kernel<OP, InT>, (unsigned)grid, kCtaThreads, 0, st, x, p0, p1, y, m, n_cols, eps);
@@ -464,7 +570,9 @@ void row_set_override(int tpr) { g_row_tpr.store(tpr); }
 void row_variant_name(RowOp op, int64_t m, int64_t n_cols, char* buf, int len) {
   static const char* names[] = {"rms_norm", "softmax", "layer_norm"};
   const RowCfg c = row_cfg(m, n_cols, n_cols % 8 == 0, DTAS_F16);
-  if (c.generic)
+  if (c.generic && c.elems_tpr > 0)
+    snprintf(buf, len, "%s_generic_elems_tpr%d_e%d", names[op], c.elems_tpr, c.elems_max);
+  else if (c.generic)
     snprintf(buf, len, "%s_generic_cta256", names[op]);
   else
     snprintf(buf, len, "%s_regs_tpr%d_ch%d", names[op], c.tpr, c.maxch);

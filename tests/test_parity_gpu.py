@@ -83,6 +83,24 @@ def test_elementwise_reference_signature_and_dtypes(cuda_device):
         util.assert_bit_exact(np_of(out), a.numpy(), f"copy {dt}")
 
 
+@pytest.mark.parametrize("m,h", [(1, 1), (1, 3), (1, 4), (1, 5), (7, 37), (1, 2051), (300, 2560), (4096, 2560), (3, 70001)])
+def test_cast_f16_f32_lengths(cuda_device, m, h):
+    """fp16 -> fp32 (the reference's cast, tuning_test/tune_cast.py:10-21) moves 4-element vectors:
+    tails of 0..3 elements, one full-size case, and a view that starts 2 bytes off alignment."""
+    x = seeded_normal((m, h), 400 + h, "float16")
+    big, y = guarded((m, h), torch.float32, cuda_device, 3.0)
+    ops.cast(x.to(cuda_device), y)
+    torch.cuda.synchronize()
+    util.assert_bit_exact(np_of(y), oracle.cast(x.numpy(), np.float32), f"cast f16->f32 {m}x{h}")
+    assert_guards(big, m * h, 3.0, f"cast f16->f32 {m}x{h}")
+    if m == 1:
+        src = torch.zeros(h + 1, dtype=torch.float16, device=cuda_device)
+        src[1:] = x.to(cuda_device).view(-1)
+        out = torch.empty((1, h), dtype=torch.float32, device=cuda_device)
+        ops.cast(src[1:].view(1, h), out)
+        util.assert_bit_exact(np_of(out), oracle.cast(x.numpy(), np.float32), f"cast f16->f32 misaligned {h}")
+
+
 def test_elementwise_ragged_lengths_and_misalignment(cuda_device):
     """Every m in 1..40 at a tiny odd H (tails shorter than a vector), a few random
     lengths up to ~70k elements, and buffers that start 2 bytes off a 16-byte boundary."""
@@ -146,6 +164,42 @@ def test_row_ops_other_row_lengths(cuda_device, m, h):
     util.assert_reduction_close(np_of(y), oracle.rms_norm(x.numpy(), w.numpy(), 1e-6), f"rms_norm {m}x{h}")
     ops.softmax(xd, y)
     util.assert_reduction_close(np_of(y), oracle.softmax(x.numpy()), f"softmax {m}x{h}")
+
+
+@pytest.mark.parametrize("dtype", ["float16", "float32"])
+@pytest.mark.parametrize("m,h", [(1, 1), (700, 17), (9, 255), (37, 257), (5, 1023), (130, 1025), (3, 2047), (66, 2049),
+                                 (7, 4095), (3, 4097), (2, 5001)])
+def test_row_ops_ragged_row_lengths(cuda_device, m, h, dtype):
+    """Row lengths that are not a multiple of 8 (the reference sweeps softmax over 17, 1025, 2049:
+    experiment/dtas_tuned/general_reduction/softmax/profile_dlight.py:8-52): every configuration of
+    the scalar register kernel (rows up to 256 / 1024 / 2048 / 4096 columns), rows sharing a CTA with
+    the last CTA partly empty, and the one-CTA-per-row kernel beyond 4096; nothing written past the
+    end."""
+    x = seeded_normal((m, h), 90 + h, dtype)
+    xd = x.to(cuda_device)
+    name = _abi.variant_of("softmax", m, h)
+    assert ("elems" in name) == (h <= 4096) and "generic" in name, name
+    big, y = guarded((m, h), torch.float16, cuda_device, 9.0)
+    ops.softmax(xd, y)
+    torch.cuda.synchronize()
+    util.assert_reduction_close(np_of(y), oracle.softmax(x.numpy()), f"softmax {dtype} {m}x{h}")
+    assert_guards(big, m * h, 9.0, f"softmax {m}x{h}")
+    if dtype == "float16":
+        w = seeded_normal((h,), 91 + h, "float16", scale=0.1, mean=1.0)
+        big, y = guarded((m, h), torch.float16, cuda_device, 9.0)
+        ops.rms_norm(xd, w.to(cuda_device), y)
+        torch.cuda.synchronize()
+        util.assert_reduction_close(np_of(y), oracle.rms_norm(x.numpy(), w.numpy(), 1e-6), f"rms_norm {m}x{h}")
+        assert_guards(big, m * h, 9.0, f"rms_norm {m}x{h}")
+    else:
+        g = seeded_normal((h,), 92 + h, "float32", scale=0.1, mean=1.0)
+        b = seeded_normal((h,), 93 + h, "float32", scale=0.1)
+        big, y = guarded((m, h), torch.float16, cuda_device, 9.0)
+        ops.layer_norm(xd, g.to(cuda_device), b.to(cuda_device), y, eps=1e-5)
+        torch.cuda.synchronize()
+        util.assert_reduction_close(np_of(y), oracle.layer_norm(x.numpy(), g.numpy(), b.numpy(), 1e-5),
+                                    f"layer_norm {m}x{h}", abs_floor=1e-6)
+        assert_guards(big, m * h, 9.0, f"layer_norm {m}x{h}")
 
 
 def test_reference_reduction_workloads_fp32_in(cuda_device):
