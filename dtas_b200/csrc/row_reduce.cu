@@ -336,9 +336,9 @@ __global__ void __launch_bounds__(kCtaThreads)
 // experiment/dtas_tuned/general_reduction/softmax/profile_dlight.py:8-52), up to 4096 columns:
 // the same one-read design with scalar accesses.  A row is owned by TPR threads, thread t holds
 // elements t, t + TPR, ... (up to MAXE of them) in registers, so a warp's loads and stores are
-// contiguous, HBM sees every element once in and once out, and rows share a CTA (8 rows of up
-// to 256 columns, 4 of up to 1024, 2 beyond) instead of taking one each.  Measured on 12800
-// rows of fp32: 17 columns 15.5 -> 3.2 us against one CTA per row.
+// contiguous, HBM sees every element once in and once out, and short rows share a CTA (8 rows of
+// up to 256 columns, 2 of up to 1024) instead of taking one each.  Measured on 12800 rows of
+// fp32: 17 columns 15.5 -> 3.2 us, 1025 columns 36 -> 25 us against one CTA per row.
 template <int OP, typename InT, int TPR, int MAXE>
 __global__ void __launch_bounds__(kCtaThreads)
     row_elems_kernel(const InT* __restrict__ x, const void* __restrict__ p0,
@@ -441,10 +441,12 @@ inline RowCfg row_cfg(int64_t m, int64_t n_cols, bool vec_ok, int in_dtype) {
   RowCfg c{0, 0, false, 0, 0};
   if (!vec_ok || n_cols > 65536) {
     c.generic = true;
+    // scalar loads put only 4 bytes per thread in flight, so long rows take a whole CTA each:
+    // 128 threads x 32 elements ran a 2049-column softmax in 181 us, 256 x 16 in 44 us
     if (n_cols <= 256) { c.elems_tpr = 32; c.elems_max = 8; }
-    else if (n_cols <= 1024) { c.elems_tpr = 64; c.elems_max = 16; }
-    else if (n_cols <= 2048) { c.elems_tpr = 128; c.elems_max = 16; }
-    else if (n_cols <= 4096) { c.elems_tpr = 128; c.elems_max = 32; }
+    else if (n_cols <= 1024) { c.elems_tpr = 128; c.elems_max = 8; }
+    else if (n_cols <= 2048) { c.elems_tpr = 256; c.elems_max = 8; }
+    else if (n_cols <= 4096) { c.elems_tpr = 256; c.elems_max = 16; }
     return c;
   }
   const int n_chunks = (int)(n_cols >> 3);
@@ -462,6 +464,15 @@ inline RowCfg row_cfg(int64_t m, int64_t n_cols, bool vec_ok, int in_dtype) {
   const int forced = g_row_tpr.load();
   if (forced >= 32 && forced <= 1024 && (forced & (forced - 1)) == 0) tpr = forced;
   if (tpr > max_tpr) tpr = max_tpr;
+  // from 512 rows up, at least two chunks per thread where the row has them: rows of 2-4 KB ran
+  // 15-35 % faster with 32-64 threads than with 128 (12800 x 1024 fp16 softmax: 9.5 us against
+  // 15.0); below that the launch is latency-bound and more threads per row are faster
+  // (256 x 2560 fp32 layer norm: 2.2 us with 256 threads, 2.7 us with 128)
+  if (forced == 0 && m >= 512) {
+    int by_chunks = pow2_ceil(n_chunks / 2 + 1) / 2;   // largest power of two <= n_chunks / 2
+    if (by_chunks < 32) by_chunks = 32;
+    if (tpr > by_chunks) tpr = by_chunks;
+  }
   while (tpr <= 1024 && (n_chunks + tpr - 1) / tpr > cap_for(tpr)) tpr *= 2;
   if (tpr > 1024) {
     c.generic = true;
@@ -508,12 +519,12 @@ int launch_typed(const RowCfg& c, const InT* x, const void* p0, const void* p1, 
     const int nc = (int)n_cols;
     if (c.elems_tpr == 32)
       launch_kernel(row_elems_kernel<OP, InT, 32, 8>, (unsigned)grid, kCtaThreads, 0, st, x, p0, p1, y, m, nc, eps);
-    else if (c.elems_tpr == 64)
-      launch_kernel(row_elems_kernel<OP, InT, 64, 16>, (unsigned)grid, kCtaThreads, 0, st, x, p0, p1, y, m, nc, eps);
-    else if (c.elems_max == 16)
-      launch_kernel(row_elems_kernel<OP, InT, 128, 16>, (unsigned)grid, kCtaThreads, 0, st, x, p0, p1, y, m, nc, eps);
+    else if (c.elems_tpr == 128)
+      launch_kernel(row_elems_kernel<OP, InT, 128, 8>, (unsigned)grid, kCtaThreads, 0, st, x, p0, p1, y, m, nc, eps);
+    else if (c.elems_max == 8)
+      launch_kernel(row_elems_kernel<OP, InT, 256, 8>, (unsigned)grid, kCtaThreads, 0, st, x, p0, p1, y, m, nc, eps);
     else
-      launch_kernel(row_elems_kernel<OP, InT, 128, 32>, (unsigned)grid, kCtaThreads, 0, st, x, p0, p1, y, m, nc, eps);
+      launch_kernel(row_elems_kernel<OP, InT, 256, 16>, (unsigned)grid, kCtaThreads, 0, st, x, p0, p1, y, m, nc, eps);
     return after_launch("row_elems_kernel");
   }
   if (c.generic) {
