@@ -180,12 +180,13 @@ class PeerGatherBuffer:
     and loses to the copy engines beside a large GEMM (m = 8192, N = 22016 on two GPUs: 729 us
     against 619 us; one all-gather behind the kernel: 889 us), while with seven peers it fills
     NVLink from a few SMs and one launch replaces seven copies (eight GPUs: 670 us against 838 us;
-    all-gather: 686 us).  "auto" takes "copy" for two ranks and "kernel" above."""
+    all-gather: 686 us; four GPUs: 657 us against 630 us; all-gather: 739 us).  "auto" takes "copy"
+    up to four ranks and "kernel" above."""
 
     def __init__(self, world: int, m: int, n_local: int, dtype, device, group=None, engine: str = "auto"):
         import torch.distributed._symmetric_memory as symm
         if engine == "auto":
-            engine = "copy" if world <= 2 else "kernel"
+            engine = "copy" if world <= 4 else "kernel"
         if engine not in ("kernel", "copy"):
             raise ValueError("engine is 'auto', 'kernel' (this library's push kernel) or 'copy' (cudaMemcpyAsync per peer)")
         group = group if group is not None else dist.group.WORLD
