@@ -45,6 +45,7 @@ PROTOTYPES = {
     "dtas_gemm_nt_fused": (_i, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _p]),
     "dtas_gemv_fused": (_i, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i, _i, _i, _i, _p]),
     "dtas_gemm_nt_static_scratch": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _i, _i, _p, _p]),
+    "dtas_gemm_nt_static_scratch_plan": (_i, [_i64, _i64, _i64, _i, ctypes.POINTER(_i), ctypes.POINTER(_i)]),
     "dtas_bucket_of": (_i, [ctypes.c_char_p, _i64]),
     "dtas_bucket_count": (_i, [ctypes.c_char_p]),
     "dtas_variant_of": (_i, [ctypes.c_char_p, _i64, _i64, _i64, _i, ctypes.c_char_p, _i]),
@@ -59,6 +60,7 @@ PROTOTYPES = {
     "dtas_last_error": (ctypes.c_char_p, []),
     "dtas_launch_count": (_i64, []),
     "dtas_poll_status": (_i, [_i]),
+    "dtas_selftest_wait_timeout": (_i, [_i, _p, _i64]),
     "dtas_shutdown": (_i, []),
     "dtas_version": (ctypes.c_char_p, []),
 }

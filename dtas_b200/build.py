@@ -52,39 +52,5 @@ def build_library(force=False, verbose=False):
     return LIB_PATH
 
 
-TRACE_LIB_PATH = os.path.join(LIB_DIR, "libdtas_b200_trace.so")
-
-
-def build_trace_library():
-    """The same library with -DDTAS_TRACE: the GEMM kernels stamp a per-CTA timeline that
-    dtas_trace_read() returns (python -m dtas_b200.trace_gemm).  Not loaded by anything else."""
-    os.makedirs(LIB_DIR, exist_ok=True)
-    cmd = [_nvcc()] + NVCC_FLAGS + ["-DDTAS_TRACE", "-o", TRACE_LIB_PATH] + [os.path.join(CSRC, s) for s in SOURCES]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
-    return TRACE_LIB_PATH
-
-
-PROBE_PATH = os.path.join(LIB_DIR, "l2_probe")
-
-
-def build_probe():
-    """The stand-alone per-SM L2 throughput probe (csrc/l2_probe.cu) -> lib/l2_probe."""
-    os.makedirs(LIB_DIR, exist_ok=True)
-    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-o", PROBE_PATH,
-           os.path.join(CSRC, "l2_probe.cu")]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
-    return PROBE_PATH
-
-
 if __name__ == "__main__":
-    import sys
-    if "--probe" in sys.argv:
-        print(build_probe())
-    elif "--trace" in sys.argv:
-        print(build_trace_library())
-    else:
-        print(build_library(force=True, verbose=True))
+    print(build_library(force=True, verbose=True))

@@ -85,18 +85,31 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
 #endif
 
 // ---- per-device context ------------------------------------------------------
+// Split-K scratch of the GEMM: fp32 partial tiles + one arrival counter per output tile.  A call takes
+// the set that belongs to its stream, so calls on different streams of one device never share
+// partial sums or counters and may overlap freely.
+constexpr int kSplitKSlots = 8;
+struct SplitKScratch {
+  bool used = false;
+  cudaStream_t stream = nullptr;   // the stream whose calls own this set
+  float* ws = nullptr;
+  int* counters = nullptr;
+  uint64_t last_use = 0;
+};
 struct DeviceCtx {
   bool ready = false;
   int sm_count = 0;
-  // split-K scratch of the GEMM: fp32 partial tiles + one arrival counter per output tile
-  float* splitk_ws = nullptr;
-  size_t splitk_ws_bytes = 0;
-  int* tile_counters = nullptr;
-  int n_tile_counters = 0;
+  SplitKScratch splitk[kSplitKSlots];
+  uint64_t splitk_clock = 0;
   int* status = nullptr;  // device status word written by bounded waits that gave up
 };
 int get_ctx(int device, DeviceCtx** out);           // creates on first use (device must be current)
-int ensure_splitk_scratch(DeviceCtx* ctx);          // cudaMalloc on first use
+// The split-K scratch set of `st` (created on the stream's first split-K call; cudaMalloc).
+int acquire_splitk_scratch(DeviceCtx* ctx, cudaStream_t st, float** ws, int** counters);
+int reset_splitk_counters(DeviceCtx* ctx);          // after a timeout: every set's counters back to zero
+void free_splitk_scratch(DeviceCtx* ctx);
+// Built-in scratch of dtas_gemm_nt_static_scratch: reads and clears its status word (0 when never used).
+int static_scratch_poll(int device, int* code);
 
 // Makes `device` current for the scope and restores the previous device.
 struct DeviceGuard {

@@ -378,17 +378,25 @@ int dtas_set_pdl(int mode) {
 int64_t dtas_launch_count(void) { return g_launches.load(); }
 
 int dtas_poll_status(int device) {
-  if (device < 0 || device >= kMaxDevices || !g_ctx[device].ready) return DTAS_OK;
-  DeviceGuard g;
-  int rc = g.enter(device);
+  if (device < 0 || device >= kMaxDevices) return DTAS_OK;
+  // the built-in scratch of dtas_gemm_nt_static_scratch carries a status word of its own
+  int static_code = 0;
+  int rc = static_scratch_poll(device, &static_code);
   if (rc) return rc;
   int host = 0;
-  DTAS_CUDA(cudaDeviceSynchronize());
-  DTAS_CUDA(cudaMemcpy(&host, g_ctx[device].status, sizeof(int), cudaMemcpyDeviceToHost));
-  if (host != 0) {
-    DTAS_CUDA(cudaMemset(g_ctx[device].status, 0, sizeof(int)));
-    DTAS_FAIL(DTAS_ETIMEOUT, "a bounded device-side wait gave up (code 0x%x)", host);
+  if (g_ctx[device].ready) {
+    DeviceGuard g;
+    if ((rc = g.enter(device))) return rc;
+    DTAS_CUDA(cudaDeviceSynchronize());
+    DTAS_CUDA(cudaMemcpy(&host, g_ctx[device].status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (host != 0) {
+      DTAS_CUDA(cudaMemset(g_ctx[device].status, 0, sizeof(int)));
+      // a kernel that gave up may have left arrival counters of shared tiles behind
+      if ((rc = reset_splitk_counters(&g_ctx[device]))) return rc;
+    }
   }
+  if (host == 0) host = static_code;
+  if (host != 0) DTAS_FAIL(DTAS_ETIMEOUT, "a bounded device-side wait gave up (code 0x%x)", host);
   return DTAS_OK;
 }
 
@@ -399,8 +407,7 @@ int dtas_shutdown(void) {
     if (!c.ready) continue;
     DeviceGuard g;
     if (g.enter(d) != DTAS_OK) continue;
-    if (c.splitk_ws) cudaFree(c.splitk_ws);
-    if (c.tile_counters) cudaFree(c.tile_counters);
+    free_splitk_scratch(&c);
     if (c.status) cudaFree(c.status);
     c = DeviceCtx();
   }

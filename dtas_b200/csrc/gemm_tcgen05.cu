@@ -53,23 +53,6 @@ constexpr int kEpilogueThreads = 128;
 constexpr int kStageBudget = 192 * 1024;   // bytes of operand ring per CTA
 constexpr int kGroupM = 16;     // m-tiles per rasterisation band
 
-// Optional timeline of one launch (compile with -DDTAS_TRACE; not part of the shipped build):
-// each CTA stamps its SM clock at a few milestones into a device array that
-// dtas_trace_read() copies out.  Slots 14 / 15 hold the global timer at entry / exit.
-#ifdef DTAS_TRACE
-__device__ unsigned long long g_trace[1024][16];
-#define DTAS_TRACE_AT(slot) do { g_trace[blockIdx.x & 1023][slot] = (unsigned long long)clock64(); } while (0)
-#define DTAS_TRACE_G(slot)                                              \
-  do {                                                                  \
-    unsigned long long t_;                                              \
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));              \
-    g_trace[blockIdx.x & 1023][slot] = t_;                              \
-  } while (0)
-#else
-#define DTAS_TRACE_AT(slot) do { } while (0)
-#define DTAS_TRACE_G(slot) do { } while (0)
-#endif
-
 constexpr int ERR_PRODUCER = 0x101, ERR_MMA_FULL = 0x102, ERR_MMA_TMEM = 0x103, ERR_EPILOGUE = 0x104;
 
 // ---------------------------------------------------------------------------------------
@@ -106,13 +89,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return done != 0;
 }
-// Bounded wait: gives up after ~1 s of wall time, records `code` and returns false.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int* status, int code) {
+// Bounded wait: gives up after `limit_ns` (~1 s by default) of wall time, records `code` and returns false.
+constexpr uint64_t kWaitLimitNs = 1000000000ull;
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int* status, int code,
+                                            uint64_t limit_ns = kWaitLimitNs) {
   const uint64_t t0 = global_timer_ns();
   for (;;) {
     for (int i = 0; i < 2048; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (global_timer_ns() - t0 > 1000000000ull) {
+    if (global_timer_ns() - t0 > limit_ns) {
       atomicExch(status, code);
       return false;
     }
@@ -314,7 +299,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   (void)last_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) { DTAS_TRACE_G(14); DTAS_TRACE_AT(0); }
 
   if (threadIdx.x == 0) {
     // descriptor fetch overlaps the set-up below and the wait for the previous kernel
@@ -339,10 +323,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
-  if (threadIdx.x == 0) DTAS_TRACE_AT(1);
   pdl_wait();                 // the previous kernel on the stream is complete from here on
   pdl_launch_dependents();    // the next one may run its own set-up while this one works
-  if (threadIdx.x == 0) DTAS_TRACE_AT(2);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -361,11 +343,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           const uint32_t sa = base + stage * C::kStageBytes;
           tma_load_2d(sa, &tmap_x, kb * BK, mt * BM, full_bar(stage));
           tma_load_2d(sa + C::kABytes, &tmap_w, kb * BK, nt * BN, full_bar(stage));
-          if (kb == sg.kb0) DTAS_TRACE_AT(3);
           if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
         }
       }
-      DTAS_TRACE_AT(4);
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -389,7 +369,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, a.status, ERR_MMA_FULL)) { ok = false; break; }
           tc_fence_after();
-          if (kb == kb0) DTAS_TRACE_AT(5);
           const uint32_t sa = base + stage * C::kStageBytes;
           const uint64_t da = make_kmajor_sw128_desc(sa);
           const uint64_t db = make_kmajor_sw128_desc(sa + C::kABytes);
@@ -402,7 +381,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
         }
         if (ok) umma_commit(tfull_bar(acc));  // accumulator complete
-        DTAS_TRACE_AT(6);
       }
     }
     __syncwarp();
@@ -421,7 +399,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
       if (!mbar_wait(tfull_bar(acc), acc_phase, a.status, ERR_EPILOGUE)) { ok = false; break; }
       tc_fence_after();
-      if (epi_tid == 0) DTAS_TRACE_AT(7);
       const int row = mt * BM + quarter * 32 + lane;
       const bool row_ok = row < a.m;
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
@@ -490,7 +467,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
         __threadfence();
         epilogue_bar_sync();
-        if (epi_tid == 0) DTAS_TRACE_AT(8);
         if (epi_tid == 0) {
           const int old = atomicAdd(&a.counters[sg.tile], 1);
           const uint32_t last = (old == n_parts - 1) ? 1u : 0u;
@@ -500,7 +476,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         epilogue_bar_sync();
         const bool is_last = *last_flag_ptr != 0;
         epilogue_bar_sync();                 // flag consumed before a later tile rewrites it
-        if (epi_tid == 0) DTAS_TRACE_AT(9);
         if (is_last) {
           __threadfence();
           if (row_ok) {
@@ -544,14 +519,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
   }
 
-  if (threadIdx.x == 64) DTAS_TRACE_AT(10);
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) DTAS_TRACE_AT(11);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);
-    if (lane == 0) { DTAS_TRACE_AT(12); DTAS_TRACE_G(15); }
   }
 }
 
@@ -663,7 +635,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   volatile uint32_t* last_flag_ptr = tmem_slot_ptr + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) { DTAS_TRACE_G(14); DTAS_TRACE_AT(0); }
 
   if (threadIdx.x == 0) {
     // descriptor fetch overlaps the set-up below and the wait for the previous kernel
@@ -688,10 +659,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
-  if (threadIdx.x == 0) DTAS_TRACE_AT(1);
   pdl_wait();                 // the previous kernel on the stream is complete from here on
   pdl_launch_dependents();    // the next one may run its own set-up while this one works
-  if (threadIdx.x == 0) DTAS_TRACE_AT(2);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -709,11 +678,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           const uint32_t sa = base + stage * C::kStageBytes;
           tma_load_2d(sa, &tmap_w, kb * BK, nt * BM, full_bar(stage));
           tma_load_2d(sa + C::kWBytes, &tmap_x, kb * BK, 0, full_bar(stage));
-          if (kb == sg.kb0) DTAS_TRACE_AT(3);
           if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
         }
       }
-      DTAS_TRACE_AT(4);
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -736,7 +703,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, a.status, ERR_MMA_FULL)) { ok = false; break; }
           tc_fence_after();
-          if (kb == kb0) DTAS_TRACE_AT(5);
           const uint32_t sa = base + stage * C::kStageBytes;
           const uint64_t da = make_kmajor_sw128_desc(sa);                // W rows: the M side
           const uint64_t db = make_kmajor_sw128_desc(sa + C::kWBytes);   // X rows: the N side
@@ -747,7 +713,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
         }
         if (ok) umma_commit(tfull_bar(acc));
-        DTAS_TRACE_AT(6);
       }
     }
     __syncwarp();
@@ -766,7 +731,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
       if (!mbar_wait(tfull_bar(acc), acc_phase, a.status, ERR_EPILOGUE)) { ok = false; break; }
       tc_fence_after();
-      if (epi_tid == 0) DTAS_TRACE_AT(7);
       const int col = nt * BM + quarter * 32 + lane;        // output column owned by this thread
       const bool col_ok = col < a.n;
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * MN);
@@ -818,7 +782,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
         __threadfence();
         epilogue_bar_sync();
-        if (epi_tid == 0) DTAS_TRACE_AT(8);
         if (epi_tid == 0) {
           const int old = atomicAdd(&a.counters[nt], 1);
           const uint32_t last = (old == n_parts - 1) ? 1u : 0u;
@@ -828,7 +791,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         epilogue_bar_sync();
         const bool is_last = *last_flag_ptr != 0;
         epilogue_bar_sync();
-        if (epi_tid == 0) DTAS_TRACE_AT(9);
         if (is_last) {
           __threadfence();
           const float bias = (a.epi.bias != nullptr && col_ok) ? __half2float(a.epi.bias[col]) : 0.f;
@@ -876,14 +838,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
   }
 
-  if (threadIdx.x == 64) DTAS_TRACE_AT(10);
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) DTAS_TRACE_AT(11);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);
-    if (lane == 0) { DTAS_TRACE_AT(12); DTAS_TRACE_G(15); }
   }
 }
 
@@ -1688,13 +1647,22 @@ constexpr int kTileCounters = 4096;
 //     (tiles shared inside a rasterisation band come from L2),
 // adds a fixed fill/drain cost per work item, multiplies by the number of rounds
 // ceil(work / SMs), and adds the partial-sum traffic of a split.  Larger BN wins ties.
-GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
+// `lim` narrows the search for callers with their own scratch: no override / table, only the tiled
+// single-CTA kernel with a fixed split, partial sums and counters within the given sizes.
+struct PlanLimits {
+  bool use_overrides = true;
+  bool tiled_fixed_only = false;
+  int64_t ws_bytes = (int64_t)kSplitKWorkspaceBytes;
+  int64_t counters = kTileCounters;
+};
+
+GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok, const PlanLimits& lim = PlanLimits()) {
   GemmPlan p{256, 1, 0, !tma_ok};
   const int num_kb = (int)((k + BK - 1) / BK);
   p.kb_per_split = num_kb;
   if (p.simt) return p;
   int obn0 = 0, osp0 = 0;
-  effective_choice(m, n, k, &obn0, &osp0);
+  if (lim.use_overrides) effective_choice(m, n, k, &obn0, &osp0);
   if ((obn0 == 8192 + 64 || obn0 == 8192 + 128) && num_kb >= 2) {   // tile codes 8256 / 8320
     p.bn = obn0 - 8192;
     p.splits = 1;
@@ -1709,7 +1677,8 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
     return p;
   }
   if (obn0 >= 8192) obn0 = 0;      // not applicable to this shape: plan as usual
-  if ((m <= 256 && (obn0 == 1024 || obn0 == 2048)) || (m <= kSwapMaxM && obn0 == 0 && kSwapByDefault)) {
+  if (!lim.tiled_fixed_only &&
+      ((m <= 256 && (obn0 == 1024 || obn0 == 2048)) || (m <= kSwapMaxM && obn0 == 0 && kSwapByDefault))) {
     // Swapped-operand kernel: 128-row W tiles, split K until the work items fill the SMs.
     const int mn = m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256)));
     const int stage_bytes = BM * BK * 2 + ((mn * BK * 2 + 1023) / 1024) * 1024;
@@ -1792,7 +1761,7 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
   auto tiles = [&](int bn) { return m_tiles * ((n + bn - 1) / bn); };
   auto ws_ok = [&](int bn, int slots) {   // partial tiles: [n tile][slot][BN/4][m] float4
     const int64_t n_pad = ((n + bn - 1) / bn) * bn;
-    return tiles(bn) <= kTileCounters && (int64_t)slots * m * n_pad * 4 <= (int64_t)kSplitKWorkspaceBytes;
+    return tiles(bn) <= lim.counters && (int64_t)slots * m * n_pad * 4 <= lim.ws_bytes;
   };
 
   constexpr double kClockGHz = 1.7, kHbmGBs = 6500.0, kItemFixedNs = 1500.0;
@@ -1828,7 +1797,7 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
       const double an = active / am < 1.0 ? 1.0 : active / am;
       const double t_hbm = 128.0 * (an * bn + am * rows_x) / kHbmGBs;
       double cost = (double)rounds * (kb_per * (t_core > t_hbm ? t_core : t_hbm) + kItemFixedNs);
-      if (s == 2 && bn <= 128 && work <= sm_count - 4 && kK2ByDefault) {
+      if (s == 2 && bn <= 128 && work <= sm_count - 4 && kK2ByDefault && !lim.tiled_fixed_only) {
         // the same main loop, the second half handed over through shared memory (~1.5 us measured
         // against ~4.5 us through the workspace at m = 255)
         const double c2 = cost + 1500.0;
@@ -1885,7 +1854,7 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
     sk_bn = obn0 - 4096;
     sk = sk_plan(sk_bn);
     if (sk.per == 0) sk_bn = 0;   // does not fit the workspace: fall through to the fixed plan
-  } else if (obn0 == 0 && osp0 == 0 && kStreamKByDefault && m <= kStreamKMaxM) {
+  } else if (obn0 == 0 && osp0 == 0 && kStreamKByDefault && m <= kStreamKMaxM && !lim.tiled_fixed_only) {
     for (int bi = 0; bi < 3; ++bi) {
       const SkPlan q = sk_plan(kBn[bi]);
       if (q.per > 0 && q.cost < sk.cost * 0.999) {
@@ -1902,7 +1871,7 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok) {
   // k-block it runs at about 0.9x the time of two single-CTA 128 x 256 tiles (1.40-1.50
   // PFLOP/s against 1.30-1.33 at m >= 4096), and its ring is deeper.
   bool pair = false;
-  if (kPairByDefault && m >= kPairMinM) {
+  if (kPairByDefault && m >= kPairMinM && !lim.tiled_fixed_only) {
     const int64_t pm = (m + 2 * BM - 1) / (2 * BM), pn = (n + kPairBN - 1) / kPairBN;
     const int64_t work = pm * pn, slots = sm_count / 2 > 0 ? sm_count / 2 : 1;
     const int64_t rounds = (work + slots - 1) / slots;
@@ -1959,13 +1928,13 @@ template <int BN>
 int launch_tc(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a, int sm_count,
               cudaStream_t st) {
   using C = Cfg<BN>;
-  static bool attr_set[64] = {false};
+  static std::atomic<bool> attr_set[64];   // zero-initialised; set after the attribute call returned
   int dev = 0;
   DTAS_CUDA(cudaGetDevice(&dev));
-  if (dev < 64 && !attr_set[dev]) {
+  if (dev < 64 && !attr_set[dev].load(std::memory_order_acquire)) {
     DTAS_CUDA(cudaFuncSetAttribute(gemm_f16_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    C::kSmemBytes));
-    attr_set[dev] = true;
+    attr_set[dev].store(true, std::memory_order_release);
   }
   const int total = a.m_tiles * a.n_tiles * a.splits;
   int grid = total < sm_count ? total : sm_count;
@@ -1975,11 +1944,11 @@ int launch_tc(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a, i
 }
 
 int launch_pair(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a, int sm_count, cudaStream_t st) {
-  static bool attr_set[64] = {false};
+  static std::atomic<bool> attr_set[64];   // zero-initialised; set after the attribute call returned
   static int max_pairs[64] = {0};
   int dev = 0;
   DTAS_CUDA(cudaGetDevice(&dev));
-  if (dev < 64 && !attr_set[dev]) {
+  if (dev < 64 && !attr_set[dev].load(std::memory_order_acquire)) {
     DTAS_CUDA(cudaFuncSetAttribute(gemm_f16_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    kPairSmemBytes));
     // how many CTA pairs the device can hold at once (one CTA per SM, pairs share a TPC)
@@ -2000,7 +1969,7 @@ int launch_pair(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a,
       n = sm_count / 2;
     }
     max_pairs[dev] = n;
-    attr_set[dev] = true;
+    attr_set[dev].store(true, std::memory_order_release);
   }
   const int total = a.m_tiles * a.n_tiles;
   int pairs = dev < 64 ? max_pairs[dev] : sm_count / 2;
@@ -2012,13 +1981,13 @@ int launch_pair(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a,
 template <int BN>
 int launch_k2(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a, cudaStream_t st) {
   using C = K2Cfg<BN>;
-  static bool attr_set[64] = {false};
+  static std::atomic<bool> attr_set[64];   // zero-initialised; set after the attribute call returned
   int dev = 0;
   DTAS_CUDA(cudaGetDevice(&dev));
-  if (dev < 64 && !attr_set[dev]) {
+  if (dev < 64 && !attr_set[dev].load(std::memory_order_acquire)) {
     DTAS_CUDA(cudaFuncSetAttribute(gemm_f16_tcgen05_k2_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    C::kSmemBytes));
-    attr_set[dev] = true;
+    attr_set[dev].store(true, std::memory_order_release);
   }
   const int64_t grid = 2ll * a.m_tiles * a.n_tiles;
   if (grid > 0x7fffffffLL) DTAS_FAIL(DTAS_EINVAL, "gemm: too many tiles");
@@ -2029,13 +1998,13 @@ int launch_k2(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a, c
 template <int MN, int S>
 int launch_swap_kc(const CUtensorMap& tw, const CUtensorMap& tx, const GemmArgs& a, cudaStream_t st) {
   using C = SwapKcCfg<MN>;
-  static bool attr_set[64] = {false};
+  static std::atomic<bool> attr_set[64];   // zero-initialised; set after the attribute call returned
   int dev = 0;
   DTAS_CUDA(cudaGetDevice(&dev));
-  if (dev < 64 && !attr_set[dev]) {
+  if (dev < 64 && !attr_set[dev].load(std::memory_order_acquire)) {
     DTAS_CUDA(cudaFuncSetAttribute((gemm_f16_tcgen05_swap_kc_kernel<MN, S>), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    C::kSmemBytes));
-    attr_set[dev] = true;
+    attr_set[dev].store(true, std::memory_order_release);
   }
   const int64_t grid = (int64_t)S * a.n_tiles;
   if (grid > 0x7fffffffLL) DTAS_FAIL(DTAS_EINVAL, "gemm: too many tiles");
@@ -2046,13 +2015,13 @@ int launch_swap_kc(const CUtensorMap& tw, const CUtensorMap& tx, const GemmArgs&
 template <int MN>
 int launch_swap(const CUtensorMap& tw, const CUtensorMap& tx, const GemmArgs& a, int sm_count, cudaStream_t st) {
   using C = SwapCfg<MN>;
-  static bool attr_set[64] = {false};
+  static std::atomic<bool> attr_set[64];   // zero-initialised; set after the attribute call returned
   int dev = 0;
   DTAS_CUDA(cudaGetDevice(&dev));
-  if (dev < 64 && !attr_set[dev]) {
+  if (dev < 64 && !attr_set[dev].load(std::memory_order_acquire)) {
     DTAS_CUDA(cudaFuncSetAttribute(gemm_f16_tcgen05_swap_kernel<MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    C::kSmemBytes));
-    attr_set[dev] = true;
+    attr_set[dev].store(true, std::memory_order_release);
   }
   const int total = a.n_tiles * a.splits;
   int grid = total < sm_count ? total : sm_count;
@@ -2067,15 +2036,23 @@ bool gemm_tma_ok(const void* x, const void* w, int64_t k) {
 
 }  // namespace
 
+// A new range replaces whatever the table held for the same (n, k) inside [m_lo, m_hi]: entries that
+// overlap it are trimmed to the part outside (an entry that straddles it is cut in two), so that the
+// latest measurement always wins, whatever ranges an earlier table used.
 int gemm_table_set(int64_t n, int64_t k, int64_t m_lo, int64_t m_hi, int bn, int split_k) {
   std::lock_guard<std::mutex> lock(g_table_mutex);
-  for (TableEntry& e : g_table)
-    if (e.n == n && e.k == k && e.m_lo == m_lo && e.m_hi == m_hi) {
-      e.bn = bn;
-      e.split = split_k;
-      return DTAS_OK;
+  std::vector<TableEntry> kept;
+  kept.reserve(g_table.size() + 2);
+  for (const TableEntry& e : g_table) {
+    if (e.n != n || e.k != k || e.m_hi < m_lo || e.m_lo > m_hi) {
+      kept.push_back(e);
+      continue;
     }
-  g_table.push_back(TableEntry{n, k, m_lo, m_hi, bn, split_k});
+    if (e.m_lo < m_lo) kept.push_back(TableEntry{n, k, e.m_lo, m_lo - 1, e.bn, e.split});
+    if (e.m_hi > m_hi) kept.push_back(TableEntry{n, k, m_hi + 1, e.m_hi, e.bn, e.split});
+  }
+  kept.push_back(TableEntry{n, k, m_lo, m_hi, bn, split_k});
+  g_table.swap(kept);
   return DTAS_OK;
 }
 
@@ -2089,14 +2066,94 @@ void gemm_set_override(int bn, int split_k) {
   g_override_split.store(split_k);
 }
 
-int ensure_splitk_scratch(DeviceCtx* ctx) {
-  if (ctx->splitk_ws != nullptr) return DTAS_OK;
-  DTAS_CUDA(cudaMalloc(&ctx->splitk_ws, kSplitKWorkspaceBytes));
-  ctx->splitk_ws_bytes = kSplitKWorkspaceBytes;
-  DTAS_CUDA(cudaMalloc(&ctx->tile_counters, kTileCounters * sizeof(int)));
-  DTAS_CUDA(cudaMemset(ctx->tile_counters, 0, kTileCounters * sizeof(int)));
-  ctx->n_tile_counters = kTileCounters;
+static std::mutex g_splitk_mutex;
+
+// Split-K calls are re-entrant across streams: the partial tiles and arrival counters a call uses
+// belong to its stream.  A stream gets its set on its first split-K call (two cudaMallocs; never
+// while the stream is being captured), up to kSplitKSlots sets per device.  When more streams than
+// that issue split-K calls, the least recently used set moves to the new stream, ordered behind
+// everything submitted so far to its previous owner by an event, so the two never overlap on it.
+int acquire_splitk_scratch(DeviceCtx* ctx, cudaStream_t st, float** ws, int** counters) {
+  std::lock_guard<std::mutex> lock(g_splitk_mutex);
+  const uint64_t now = ++ctx->splitk_clock;
+  SplitKScratch* unused = nullptr;
+  SplitKScratch* lru = nullptr;
+  for (SplitKScratch& s : ctx->splitk) {
+    if (s.used && s.stream == st) {
+      s.last_use = now;
+      *ws = s.ws;
+      *counters = s.counters;
+      return DTAS_OK;
+    }
+    if (!s.used) {
+      if (unused == nullptr) unused = &s;
+    } else if (lru == nullptr || s.last_use < lru->last_use) {
+      lru = &s;
+    }
+  }
+  if (unused != nullptr) {
+    // allocate and zero into locals, publish last: another thread never sees half a set
+    float* w = nullptr;
+    int* c = nullptr;
+    DTAS_CUDA(cudaMalloc(&w, kSplitKWorkspaceBytes));
+    cudaError_t e = cudaMalloc(&c, kTileCounters * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemsetAsync(c, 0, kTileCounters * sizeof(int), st);   // ordered before the kernel on st
+    if (e != cudaSuccess) {
+      cudaFree(w);
+      if (c != nullptr) cudaFree(c);
+      DTAS_FAIL(DTAS_ECUDA, "gemm: creating the split-K scratch failed: %s", cudaGetErrorString(e));
+    }
+    unused->ws = w;
+    unused->counters = c;
+    unused->stream = st;
+    unused->last_use = now;
+    unused->used = true;
+    *ws = w;
+    *counters = c;
+    return DTAS_OK;
+  }
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+    (void)cudaGetLastError();
+    DTAS_FAIL(DTAS_ECUDA, "gemm: all %d split-K scratch sets of this device belong to other streams and one cannot "
+                          "be moved during stream capture; make one split-K call on this stream before capturing",
+              kSplitKSlots);
+  }
+  cudaEvent_t ev = nullptr;
+  bool ordered = false;
+  if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) == cudaSuccess) {
+    if (cudaEventRecord(ev, lru->stream) == cudaSuccess && cudaStreamWaitEvent(st, ev, 0) == cudaSuccess) ordered = true;
+    cudaEventDestroy(ev);
+  }
+  if (!ordered) {           // the previous owner no longer exists as a stream: wait for the whole device once
+    (void)cudaGetLastError();
+    DTAS_CUDA(cudaDeviceSynchronize());
+  }
+  lru->stream = st;
+  lru->last_use = now;
+  *ws = lru->ws;
+  *counters = lru->counters;
   return DTAS_OK;
+}
+
+// A kernel that gave up on a bounded wait may leave arrival counters of its tiles non-zero; every
+// later split-K launch on that set would then misjudge who arrives last.  Called with the device idle.
+int reset_splitk_counters(DeviceCtx* ctx) {
+  std::lock_guard<std::mutex> lock(g_splitk_mutex);
+  for (SplitKScratch& s : ctx->splitk)
+    if (s.used) DTAS_CUDA(cudaMemset(s.counters, 0, kTileCounters * sizeof(int)));
+  DTAS_CUDA(cudaDeviceSynchronize());
+  return DTAS_OK;
+}
+
+void free_splitk_scratch(DeviceCtx* ctx) {
+  std::lock_guard<std::mutex> lock(g_splitk_mutex);
+  for (SplitKScratch& s : ctx->splitk) {
+    if (!s.used) continue;
+    cudaFree(s.ws);
+    cudaFree(s.counters);
+    s = SplitKScratch();
+  }
 }
 
 // Fills the launcher-owned fields of the epilogue and says whether 16-byte stores into Y rows are aligned.
@@ -2118,8 +2175,10 @@ int launch_gemm(const void* x, const void* w, const Epilogue& epi, void* y, int6
                   (int)n, (int)k, ldy);
     return after_launch("gemm_f16_simt_kernel");
   }
+  float* ws = nullptr;
+  int* counters = nullptr;
   if (p.splits > 1 || p.sk_per > 0) {
-    int rc = ensure_splitk_scratch(ctx);
+    int rc = acquire_splitk_scratch(ctx, st, &ws, &counters);
     if (rc != DTAS_OK) return rc;
   }
   CUtensorMap tx, tw;
@@ -2131,8 +2190,8 @@ int launch_gemm(const void* x, const void* w, const Epilogue& epi, void* y, int6
   GemmArgs a;
   a.y = y;
   a.epi = epi;
-  a.ws = ctx->splitk_ws;
-  a.counters = ctx->tile_counters;
+  a.ws = ws;
+  a.counters = counters;
   a.status = ctx->status;
   a.ldy = ldy;
   a.m = (int)m;
@@ -2159,12 +2218,6 @@ int launch_gemm(const void* x, const void* w, const Epilogue& epi, void* y, int6
     a.n_tiles = (int)((n + BM - 1) / BM);
     a.sk_per = p.sk_per;
     a.slots_cap = p.slots_cap;
-    if (p.sk_per > 0) {
-      rc = ensure_splitk_scratch(ctx);
-      if (rc != DTAS_OK) return rc;
-      a.ws = ctx->splitk_ws;
-      a.counters = ctx->tile_counters;
-    }
     if (p.kc > 0) {
       const int code = (p.swap_mn == 16 ? 0 : (p.swap_mn == 32 ? 10 : 20)) + p.kc;
       switch (code) {
@@ -2277,54 +2330,125 @@ int static_scratch_setup(int device, StaticDev** out) {
   return DTAS_OK;
 }
 
+// Tile width and split of a call on the built-in scratch.  The choice never reads the global override
+// or the measured table (those tune dtas_gemm_nt), and it only considers the tiled kernel with a fixed
+// split whose partial sums fit the array.  A split asked for by the caller is kept when it fits and
+// refused otherwise; split_k = 0 always yields a plan that fits, down to one slice.
+struct StaticPlan {
+  int bn, splits, kb_per;
+  int64_t m_tiles, n_tiles;
+};
+int static_plan(int64_t m, int64_t n, int64_t k, int split_k, StaticPlan* out) {
+  PlanLimits lim;
+  lim.use_overrides = false;
+  lim.tiled_fixed_only = true;
+  lim.ws_bytes = (int64_t)kStaticPartialBytes;
+  lim.counters = kStaticTileCounters;
+  const GemmPlan p = plan_gemm(m, n, k, 148, true, lim);
+  const int num_kb = (int)((k + BK - 1) / BK);
+  StaticPlan sp;
+  sp.bn = p.bn;
+  sp.m_tiles = (m + BM - 1) / BM;
+  sp.n_tiles = (n + p.bn - 1) / p.bn;
+  auto normalise = [&](int want) {
+    sp.kb_per = (num_kb + want - 1) / want;
+    sp.splits = (num_kb + sp.kb_per - 1) / sp.kb_per;     // no empty slice
+  };
+  auto fits = [&]() {
+    return sp.splits == 1 || ((int64_t)sp.splits * m * (sp.n_tiles * sp.bn) * 4 <= (int64_t)kStaticPartialBytes &&
+                              sp.m_tiles * sp.n_tiles <= kStaticTileCounters);
+  };
+  if (split_k > 0) {
+    normalise(split_k > num_kb ? num_kb : split_k);
+    if (!fits())
+      DTAS_FAIL(DTAS_EINVAL,
+                "gemm (static scratch): split_k=%d at m=%lld n=%lld needs %lld bytes of partial sums and %lld tile "
+                "counters; the built-in scratch holds %lld bytes and %d counters (use dtas_gemm_nt, a smaller split, "
+                "or split_k=0)",
+                sp.splits, (long long)m, (long long)n, (long long)((int64_t)sp.splits * m * (sp.n_tiles * sp.bn) * 4),
+                (long long)(sp.m_tiles * sp.n_tiles), (long long)kStaticPartialBytes, kStaticTileCounters);
+  } else {
+    for (int want = p.splits; want >= 1; --want) {          // the planner's split, lowered until it fits
+      normalise(want);
+      if (fits()) break;
+    }
+  }
+  if (sp.m_tiles * sp.n_tiles * sp.splits > 0x7fffffffLL) DTAS_FAIL(DTAS_EINVAL, "gemm (static scratch): too many tiles");
+  *out = sp;
+  return DTAS_OK;
+}
+
+int static_args_check(const void* x, const void* w, int64_t m, int64_t n, int64_t k, int split_k, int dtype) {
+  if (m <= 0) DTAS_FAIL(DTAS_EINVAL, "gemm (static scratch): dynamic dim m must be > 0, got %lld", (long long)m);
+  if (n <= 0 || k <= 0) DTAS_FAIL(DTAS_EINVAL, "gemm (static scratch): n and k must be > 0");
+  if (dtype != DTAS_F16) DTAS_FAIL(DTAS_EUNSUPPORTED, "gemm (static scratch): only fp16 is implemented");
+  if (split_k < 0 || split_k > 64) DTAS_FAIL(DTAS_EINVAL, "gemm (static scratch): split_k must be in [0, 64]");
+  if (m > 0x3fffffffLL || n > 0x3fffffffLL || k > 0x3fffffffLL) DTAS_FAIL(DTAS_EINVAL, "gemm (static scratch): dimension too large");
+  if (!gemm_tma_ok(x, w, k))
+    DTAS_FAIL(DTAS_EALIGN, "gemm (static scratch): x and w must be 16-byte aligned and k a multiple of 8");
+  return DTAS_OK;
+}
+
 }  // namespace
+
+// Status word of the built-in scratch on `device`: read, and cleared when set.  0 when the entry point
+// was never called on that device.  Synchronises the device.
+int static_scratch_poll(int device, int* code) {
+  *code = 0;
+  if (device < 0 || device >= 64) return DTAS_OK;
+  unsigned char* base = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_dev[device].ready) return DTAS_OK;
+    base = g_static_dev[device].base;
+  }
+  DeviceGuard g;
+  int rc = g.enter(device);
+  if (rc) return rc;
+  int* word = reinterpret_cast<int*>(base + kStaticPartialBytes + kStaticCounterBytes);
+  DTAS_CUDA(cudaDeviceSynchronize());
+  DTAS_CUDA(cudaMemcpy(code, word, sizeof(int), cudaMemcpyDeviceToHost));
+  if (*code != 0) DTAS_CUDA(cudaMemset(word, 0, sizeof(int)));
+  return DTAS_OK;
+}
+
 }  // namespace dtas
+
+extern "C" int dtas_gemm_nt_static_scratch_plan(int64_t m, int64_t n, int64_t k, int split_k, int* tile_n,
+                                                int* splits) {
+  using namespace dtas;
+  int rc = static_args_check(nullptr, nullptr, m, n, k, split_k, DTAS_F16);
+  if (rc != DTAS_OK) return rc;
+  StaticPlan sp;
+  if ((rc = static_plan(m, n, k, split_k, &sp)) != DTAS_OK) return rc;
+  if (tile_n != nullptr) *tile_n = sp.bn;
+  if (splits != nullptr) *splits = sp.splits;
+  return DTAS_OK;
+}
 
 extern "C" int dtas_gemm_nt_static_scratch(const void* x, const void* w, const void* bias, void* y, int64_t m,
                                            int64_t n, int64_t k, int64_t ldy, int split_k, int dtype,
                                            int device, void* stream, void* status_word) {
   using namespace dtas;
   if (x == nullptr || w == nullptr || y == nullptr) DTAS_FAIL(DTAS_EINVAL, "gemm (static scratch): NULL operand");
-  if (m <= 0) DTAS_FAIL(DTAS_EINVAL, "gemm (static scratch): dynamic dim m must be > 0, got %lld", (long long)m);
-  if (n <= 0 || k <= 0) DTAS_FAIL(DTAS_EINVAL, "gemm (static scratch): n and k must be > 0");
+  int rc = static_args_check(x, w, m, n, k, split_k, dtype);
+  if (rc != DTAS_OK) return rc;
   if (ldy < n) DTAS_FAIL(DTAS_EINVAL, "gemm (static scratch): ldy (%lld) must be >= n (%lld)", (long long)ldy, (long long)n);
-  if (dtype != DTAS_F16) DTAS_FAIL(DTAS_EUNSUPPORTED, "gemm (static scratch): only fp16 is implemented");
-  if (split_k < 0 || split_k > 64) DTAS_FAIL(DTAS_EINVAL, "gemm (static scratch): split_k must be in [0, 64]");
-  if (m > 0x3fffffffLL || n > 0x3fffffffLL || k > 0x3fffffffLL) DTAS_FAIL(DTAS_EINVAL, "gemm (static scratch): dimension too large");
-  if (!gemm_tma_ok(x, w, k))
-    DTAS_FAIL(DTAS_EALIGN, "gemm (static scratch): x and w must be 16-byte aligned and k a multiple of 8");
-
-  // Tile width from the usual planner; the split factor from the caller, or the planner's.
-  GemmPlan p = plan_gemm(m, n, k, 148, true);
-  const int num_kb = (int)((k + BK - 1) / BK);
-  int splits = split_k > 0 ? (split_k > num_kb ? num_kb : split_k) : p.splits;
-  const int kb_per = (num_kb + splits - 1) / splits;
-  splits = (num_kb + kb_per - 1) / kb_per;
-  const int64_t m_tiles = (m + BM - 1) / BM, n_tiles = (n + p.bn - 1) / p.bn;
-  if (splits > 1) {
-    const int64_t need = (int64_t)splits * m * (n_tiles * p.bn) * 4;   // partials cover whole column tiles
-    if (need > (int64_t)kStaticPartialBytes)
-      DTAS_FAIL(DTAS_EINVAL,
-                "gemm (static scratch): split_k=%d at m=%lld n=%lld needs %lld bytes of partial sums; the built-in "
-                "scratch holds %lld (use dtas_gemm_nt, or a smaller split)",
-                splits, (long long)m, (long long)n, (long long)need, (long long)kStaticPartialBytes);
-    if (m_tiles * n_tiles > kStaticTileCounters)
-      DTAS_FAIL(DTAS_EINVAL, "gemm (static scratch): %lld output tiles; the built-in scratch has %d counters",
-                (long long)(m_tiles * n_tiles), kStaticTileCounters);
-  }
+  StaticPlan sp;
+  if ((rc = static_plan(m, n, k, split_k, &sp)) != DTAS_OK) return rc;
 
   DeviceGuard guard;
-  int rc = guard.enter(device);
-  if (rc != DTAS_OK) return rc;
+  if ((rc = guard.enter(device)) != DTAS_OK) return rc;
   StaticDev* sd = nullptr;
   if ((rc = static_scratch_setup(device, &sd)) != DTAS_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // The array keeps whatever the previous call left: counters and the status word must start at zero.
-  DTAS_CUDA(cudaMemsetAsync(sd->base + kStaticPartialBytes, 0, kStaticTailBytes, st));
+  // The array keeps whatever the previous call left: the arrival counters must start at zero.  The
+  // status word behind them is left alone: it holds a code until dtas_poll_status has reported it.
+  if (sp.splits > 1) DTAS_CUDA(cudaMemsetAsync(sd->base + kStaticPartialBytes, 0, kStaticCounterBytes, st));
 
   CUtensorMap tx, tw;
   if ((rc = make_tmap(&tx, x, m, k, BM)) != DTAS_OK) return rc;
-  if ((rc = make_tmap(&tw, w, n, k, p.bn)) != DTAS_OK) return rc;
+  if ((rc = make_tmap(&tw, w, n, k, sp.bn)) != DTAS_OK) return rc;
   GemmArgs a;
   a.y = y;
   a.epi.bias = (const __half*)bias;
@@ -2336,24 +2460,54 @@ extern "C" int dtas_gemm_nt_static_scratch(const void* x, const void* w, const v
   a.m = (int)m;
   a.n = (int)n;
   a.k = (int)k;
-  a.m_tiles = (int)m_tiles;
-  a.n_tiles = (int)n_tiles;
-  a.splits = splits;
-  a.slots_cap = splits;
-  a.kb_per_split = kb_per;
-  a.num_kb = num_kb;
+  a.m_tiles = (int)sp.m_tiles;
+  a.n_tiles = (int)sp.n_tiles;
+  a.splits = sp.splits;
+  a.slots_cap = sp.splits;
+  a.kb_per_split = sp.kb_per;
+  a.num_kb = (int)((k + BK - 1) / BK);
   a.vec_store = finish_epilogue(a.epi, y, ldy);
-  switch (p.bn) {
+  switch (sp.bn) {
     case 256: return launch_tc<256>(tx, tw, a, sd->sm_count, st);
     case 128: return launch_tc<128>(tx, tw, a, sd->sm_count, st);
     default: return launch_tc<64>(tx, tw, a, sd->sm_count, st);
   }
 }
 
-#ifdef DTAS_TRACE
-// Trace build only: copies the per-CTA timeline of the last GEMM launch (1024 x 16 x u64) to `dst`.
-extern "C" int dtas_trace_read(void* dst) {
-  cudaError_t e = cudaMemcpyFromSymbol(dst, dtas::g_trace, sizeof(unsigned long long) * 1024 * 16);
-  return e == cudaSuccess ? DTAS_OK : DTAS_ECUDA;
+// ---------------------------------------------------------------------------------------
+// Self-test of the bounded waits.  One warp initialises an mbarrier that nothing ever arrives on and
+// waits for it with the limit given by the caller; when the limit runs out the wait records its code
+// in the device status word and the kernel returns normally, exactly as a stuck role of a GEMM
+// kernel would.  Nothing traps or spins without bound; dtas_poll_status then reports DTAS_ETIMEOUT.
+// ---------------------------------------------------------------------------------------
+namespace dtas {
+namespace {
+constexpr int ERR_SELFTEST = 0x1ff;
+__global__ void __launch_bounds__(32) wait_selftest_kernel(int* status, uint64_t limit_ns) {
+  __shared__ __align__(8) uint64_t bar;
+  const uint32_t b = smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    mbar_init(b, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  pdl_wait();
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) (void)mbar_wait_slow(b, 0u, status, ERR_SELFTEST, limit_ns);
+  __syncwarp();
 }
-#endif
+}  // namespace
+}  // namespace dtas
+
+extern "C" int dtas_selftest_wait_timeout(int device, void* stream, int64_t limit_ns) {
+  using namespace dtas;
+  if (limit_ns < 1000 || limit_ns > 100000000)
+    DTAS_FAIL(DTAS_EINVAL, "selftest: the wait limit must be between 1 us and 100 ms, got %lld ns", (long long)limit_ns);
+  DeviceGuard guard;
+  int rc = guard.enter(device);
+  if (rc != DTAS_OK) return rc;
+  DeviceCtx* ctx = nullptr;
+  if ((rc = get_ctx(device, &ctx)) != DTAS_OK) return rc;
+  launch_kernel(wait_selftest_kernel, 1, 32, 0, static_cast<cudaStream_t>(stream), ctx->status, (uint64_t)limit_ns);
+  return after_launch("wait_selftest_kernel");
+}

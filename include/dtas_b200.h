@@ -127,18 +127,26 @@ int dtas_gemv_fused(const void* x, const void* w, const void* bias, const void* 
  * workspace it cudaMallocs on first use; this entry point keeps them in an array that is part
  * of the library image (8 MiB of fp32 partials + 1024 tile counters per GPU that loads the
  * library, held until the process exits) and calls no allocating routine at all.
- *   split_k     : K slices per output tile; 0 lets the planner choose.  The call is rejected with
- *                 DTAS_EINVAL when split_k * m * n * 4 bytes (n rounded up to the tile width) exceed
- *                 8 MiB or the output has more than 1024 tiles; with one slice no scratch is used and any size is accepted.
+ *   split_k     : K slices per output tile.  0 lets the library choose: it starts from the split its
+ *                 cost model prefers and lowers it until the partial sums fit, so split_k = 0 is never
+ *                 refused for size.  A split the caller asks for is refused with DTAS_EINVAL when
+ *                 split_k * m * n * 4 bytes (n rounded up to the tile width) exceed 8 MiB or the output
+ *                 has more than 1024 tiles; with one slice no scratch is used and any size is accepted.
  *                 x and w must be 16-byte aligned and k a multiple of 8 (DTAS_EALIGN otherwise).
+ *                 The tile width and split come from the shape alone: dtas_gemm_set_override and
+ *                 dtas_gemm_table_set, which tune dtas_gemm_nt, do not apply here.
  *   status_word : optional device int32 that receives a non-zero code if a bounded wait inside
- *                 the kernel gives up; NULL keeps the code in the library's own scratch.
+ *                 the kernel gives up; NULL keeps the code in a word of the library's own array,
+ *                 which dtas_poll_status reads and clears like the status word of the other calls.
  * The first call on a device looks up the array's device address; make that call before any
  * stream capture.  Every call on a device uses the same array: the call clears the counters it
- * needs on the given stream, and two calls that overlap on the GPU (different streams) race.   */
+ * needs on the given stream, and two calls that overlap on the GPU (different streams) race.
+ * dtas_gemm_nt_static_scratch_plan reports the tile width and split a call of that shape would
+ * use (same argument checks, no device needed); either output pointer may be NULL.            */
 int dtas_gemm_nt_static_scratch(const void* x, const void* w, const void* bias, void* y,
                                 int64_t m, int64_t n, int64_t k, int64_t ldy, int split_k,
                                 int dtype, int device, void* stream, void* status_word);
+int dtas_gemm_nt_static_scratch_plan(int64_t m, int64_t n, int64_t k, int split_k, int* tile_n, int* splits);
 
 /* ---- dispatch introspection ---------------------------------------------
  * dtas_bucket_of: index of the m-bucket the op dispatches on, the counterpart of
@@ -215,12 +223,19 @@ int dtas_peer_push(const void* src, void* const* dsts, int n_dsts, int64_t bytes
  * dtas_launch_count: kernels launched by this library since load (all threads).
  * dtas_poll_status : reads the device-side status word of `device` (written by a
  *                    kernel whose bounded wait gave up); synchronises the device.
- *                    Returns DTAS_OK or DTAS_ETIMEOUT, and clears the word.
+ *                    Returns DTAS_OK or DTAS_ETIMEOUT, clears the word and re-arms the
+ *                    split-K arrival counters a kernel that gave up may have left behind.
+ * dtas_selftest_wait_timeout: launches one warp that waits, with a limit of limit_ns
+ *                    (1 us .. 100 ms), on a barrier nothing arrives on, so that the bounded-wait
+ *                    path can be exercised: the kernel returns normally once the limit has run
+ *                    out and the next dtas_poll_status reports DTAS_ETIMEOUT.  No counterpart
+ *                    in the reference.
  * dtas_shutdown    : frees per-device workspaces.
  * dtas_version     : "dtas_b200 <semver> sm_100a".                              */
 const char* dtas_last_error(void);
 int64_t dtas_launch_count(void);
 int dtas_poll_status(int device);
+int dtas_selftest_wait_timeout(int device, void* stream, int64_t limit_ns);
 int dtas_shutdown(void);
 const char* dtas_version(void);
 

@@ -152,6 +152,24 @@ def gemm_nt(x, w, bias=None, rows=None, cols=None, out=None):
     return out
 
 
+def gemm_nt_f16acc(x, w, bias=None, rows=None):
+    """Y = X W^T (+ bias) with the fp16 accumulator the reference's own matmul PrimFuncs declare
+    (one rounding per update, bias added by a second rounded stage).  `rows=(r0, r1)` restricts the
+    computed rows; a single-row x gives the reference's GEMV."""
+    x2 = _2d(x)
+    w = np.ascontiguousarray(w)
+    assert x2.dtype == np.float16 and w.dtype == np.float16
+    m, k = x2.shape
+    n = w.shape[0]
+    assert w.shape[1] == k
+    out = np.zeros((m, n), np.float16)
+    r0, r1 = rows if rows is not None else (0, m)
+    b = None if bias is None else np.ascontiguousarray(bias)
+    _c().oracle_gemm_nt_f16acc(_ptr(x2), _ptr(w), _ptr(b) if b is not None else None, _ptr(out), _i64(n), _i64(k),
+                               _i64(r0), _i64(r1))
+    return out
+
+
 def gemm_nt_fused(x, w, bias=None, res1=None, res2=None, act=None, out_dtype=np.float16, rows=None, cols=None, out=None):
     """The fused matmul forms of the model workloads with the reference's stage-by-stage fp16
     rounding: y = cast(((res1 + gelu?(X W^T + bias)) + res2)).  rows / cols restrict the block."""

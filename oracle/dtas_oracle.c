@@ -200,6 +200,28 @@ void oracle_gemv_f16(const f16* x, const f16* w, const f16* bias, f16* y, int64_
   }
 }
 
+/* The same two PrimFuncs exactly as the reference's files state them: the accumulator is an fp16
+ * buffer (experiment/testIR/GEMM/dlight.py:35-44, `var_NT_matmul_intermediate` is "float16" and the
+ * update is `acc = acc + x * w`; experiment/testIR/GEMV/m1n2560k10240/dlight_gemv.py:13-22), and the
+ * bias is added by a second block that rounds to fp16 again (dlight.py:45-50).  TVM's C backend emits
+ * `half + half * half`; with half = _Float16 on x86 that is evaluated in fp32 and rounded once per
+ * update (the product of two fp16 numbers is exact in fp32), which the TVM build of the reference text
+ * confirms bit for bit (tests/golden/make_ref_golden.py).  Rows [row0, row1) are computed. */
+void oracle_gemm_nt_f16acc(const f16* x, const f16* w, const f16* bias, f16* y, int64_t n, int64_t k,
+                           int64_t row0, int64_t row1) {
+#pragma omp parallel for schedule(static) collapse(2)
+  for (int64_t i = row0; i < row1; ++i) {
+    for (int64_t j = 0; j < n; ++j) {
+      f16 acc = (f16)0.0f;
+      const f16* xr = x + i * k;
+      const f16* wr = w + j * k;
+      for (int64_t kk = 0; kk < k; ++kk) acc = (f16)((float)acc + ((float)xr[kk]) * ((float)wr[kk]));
+      if (bias) acc = (f16)((float)acc + (float)bias[j]);
+      y[i * n + j] = acc;
+    }
+  }
+}
+
 /* Fused matmul tails of the model workloads, stage by stage as the reference's TIR stores them
  * (experiment/ModelIR/dolly-v2-3b-q0f16/before_dl.py:163-200 add/add/add, :202-246 + cast,
  * :248-318 add + gelu; decode-time forms :96-114, :408-550): every stage after the matmul is a

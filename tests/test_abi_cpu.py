@@ -154,3 +154,41 @@ def test_shipped_gemm_table_installs_and_decides(lib):
     finally:
         lib.dtas_gemm_table_clear()
         _abi._install_default_tables(lib)
+
+
+def test_a_new_table_range_overrides_the_shipped_ranges(lib):
+    """A freshly tuned range wins over whatever an earlier table held for the same weight shape, whatever
+    ranges that table used: overlapping entries are trimmed, the part outside the new range survives."""
+    lib.dtas_gemm_table_clear()
+    _abi._install_default_tables(lib)
+    try:
+        shipped_16 = _abi.variant_of("gemm", 16, 12288, 4096)
+        shipped_300 = _abi.variant_of("gemm", 300, 12288, 4096)
+        _abi.check(lib.dtas_gemm_table_set(12288, 4096, 1, 256, 256, 1))
+        assert _abi.variant_of("gemm", 16, 12288, 4096) == "gemm_tcgen05_bm128_bn256_bk64_s4_splitk1" != shipped_16
+        assert _abi.variant_of("gemm", 256, 12288, 4096) == "gemm_tcgen05_bm128_bn256_bk64_s4_splitk1"
+        assert _abi.variant_of("gemm", 300, 12288, 4096) == shipped_300      # outside the new range: untouched
+        # a range cut out of the middle of an entry leaves both ends in place
+        lib.dtas_gemm_table_clear()
+        _abi.check(lib.dtas_gemm_table_set(1024, 1024, 1, 1000, 128, 1))
+        _abi.check(lib.dtas_gemm_table_set(1024, 1024, 100, 200, 64, 1))
+        assert "bn128" in _abi.variant_of("gemm", 50, 1024, 1024)
+        assert "bn64" in _abi.variant_of("gemm", 150, 1024, 1024)
+        assert "bn128" in _abi.variant_of("gemm", 500, 1024, 1024)
+    finally:
+        lib.dtas_gemm_table_clear()
+        _abi._install_default_tables(lib)
+
+
+def test_reference_import_lines_resolve():
+    """The import lines of the reference's driver scripts (tuning_test/tune_cast.py:35-36 and the
+    package surface python/dtas/__init__.py:1-8) resolve to this library."""
+    import dtas
+    from dtas.arch import B200, RTX3090
+    from dtas.codegen.runtime_packer import load_module_from_file
+    from dtas.common.config import Config
+    from dtas.engine.tuner import Engine
+    import dtas_b200
+    assert Engine is dtas_b200.Engine and load_module_from_file is dtas_b200.load_module_from_file
+    assert RTX3090(7).dev_id == 7 and B200(0).num_sm == 148 and Config is dtas_b200.Config
+    dtas.set_log_level(dtas.get_log_level())

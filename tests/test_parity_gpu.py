@@ -286,8 +286,11 @@ def test_gemv_streaming_kernel(cuda_device, n, k):
 GEMM_SHAPES = [(12288, 4096), (4096, 4096), (22016, 4096), (4096, 11008)]
 
 
-def _check_gemm_tiles(y_np, x, w, m, n, k, what, n_tiles=24):
-    """Oracle on sampled 128x128 tiles, always including the last (partial) row/column tiles."""
+def _check_gemm_tiles(y_np, x, w, m, n, k, what, n_tiles=64):
+    """fp32-accumulated reference on 128x128 tiles: every tile for m <= 255, else at least 64 sampled
+    ones, always including the last (partial) row / column tiles."""
+    if m <= 255:
+        n_tiles = 1 << 30
     rng = np.random.default_rng(m * 131 + n)
     mt, nt = (m + 127) // 128, (n + 127) // 128
     picks = {(mt - 1, nt - 1), (0, 0), (mt - 1, 0), (0, nt - 1)}
@@ -312,11 +315,12 @@ def test_gemm_baseline(cuda_device, m, n, k):
     y_np = np_of(y)
     assert_guards(big, m * n, 5.0, f"gemm m={m} n={n} k={k}")
     _check_gemm_tiles(y_np, x, w, m, n, k, f"gemm m={m} n={n} k={k} [{_abi.variant_of('gemm', m, n, k)}]")
-    # Whole-matrix cross-check against the library GEMM (checker only, never the product path).
+    # Whole-matrix cross-check against the library GEMM (checker only, never the product path), under
+    # the same rule as the tiles: 1e-2 relative + 1e-2 rms, evaluated on the device.
     ref = (xd @ wd.T).float()
-    err = (y.float() - ref).abs().max().item()
-    scale = ref.abs().max().item()
-    assert err <= 2e-2 * scale, f"gemm m={m} n={n} k={k}: max abs diff {err} vs library GEMM (scale {scale})"
+    rms = ref.double().pow(2).mean().sqrt().item()
+    excess = ((y.float() - ref).abs() - (1e-2 * ref.abs() + 1e-2 * rms)).max().item()
+    assert excess <= 0, f"gemm m={m} n={n} k={k}: an element is {excess} outside 1e-2 rel + 1e-2 rms of the library GEMM"
 
 
 def test_gemm_small_m_full_oracle(cuda_device):

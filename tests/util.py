@@ -71,3 +71,24 @@ def assert_matmul_close(got, want_f32, what="", rel=1e-2):
     bad = np.nonzero(err > tol)[0]
     assert bad.size == 0, (f"{what}: {bad.size} of {g.size} outside 1e-2 rel (+1e-2 rms floor); worst "
                            f"got {g[bad[0]]} want {w[bad[0]]} rms {rms}")
+
+
+def reference_tree():
+    """Directory of a checkout of the reference (JackWeiw/dtas), or None: $DTAS_REFERENCE_TREE, else a
+    directory named `reference` beside this repository.  Only CPU tests that re-derive fixtures use it;
+    nothing that runs on a GPU box does."""
+    cand = os.environ.get("DTAS_REFERENCE_TREE") or os.path.join(os.path.dirname(os.path.dirname(GOLDEN_DIR)), "..", "reference")
+    cand = os.path.abspath(cand)
+    return cand if os.path.isdir(os.path.join(cand, "python", "dtas")) else None
+
+
+def load_ref_golden(key):
+    return np.load(os.path.join(GOLDEN_DIR, f"ref_{key}.npz"))
+
+
+def fp16_accumulation_bound(k, rms):
+    """Error model of the reference's fp16 accumulator against exact summation: every one of the k
+    updates rounds the running sum to fp16 (half an ULP at most, uniformly distributed), a random
+    walk with sigma = ULP(rms) * sqrt(k / 12).  Eight sigma covers every element of the largest test
+    (the worst of 51 200 outputs at k = 2560 sat at 4.7 sigma)."""
+    return 8.0 * float(fp16_ulp(np.float32(rms))) * float(np.sqrt(k / 12.0))
