@@ -87,7 +87,9 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
 // ---- per-device context ------------------------------------------------------
 // Split-K scratch of the GEMM: fp32 partial tiles + one arrival counter per output tile.  A call takes
 // the set that belongs to its stream, so calls on different streams of one device never share
-// partial sums or counters and may overlap freely.
+// partial sums or counters and may overlap freely.  Calls made while their stream is being captured
+// into a CUDA graph take one more set, shared by all captured work of the device (a stream that
+// exists only for a capture should not pin a set for the life of the process).
 constexpr int kSplitKSlots = 8;
 struct SplitKScratch {
   bool used = false;
@@ -100,6 +102,7 @@ struct DeviceCtx {
   bool ready = false;
   int sm_count = 0;
   SplitKScratch splitk[kSplitKSlots];
+  SplitKScratch splitk_capture;     // the set of calls that are being captured into a CUDA graph
   uint64_t splitk_clock = 0;
   int* status = nullptr;  // device status word written by bounded waits that gave up
 };

@@ -2068,13 +2068,58 @@ void gemm_set_override(int bn, int split_k) {
 
 static std::mutex g_splitk_mutex;
 
+// Creates one scratch set.  May run while a stream of this thread is being captured: the capture mode
+// is relaxed for the duration (as allocators that serve captured work do), and the counters are
+// zeroed through a private stream that is waited for, so the set is ready before any launch.
+static int create_splitk_set(SplitKScratch* s) {
+  cudaStreamCaptureMode mode = cudaStreamCaptureModeRelaxed;
+  DTAS_CUDA(cudaThreadExchangeStreamCaptureMode(&mode));
+  float* w = nullptr;
+  int* c = nullptr;
+  cudaStream_t tmp = nullptr;
+  cudaError_t e = cudaMalloc(&w, kSplitKWorkspaceBytes);
+  if (e == cudaSuccess) e = cudaMalloc(&c, kTileCounters * sizeof(int));
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&tmp, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaMemsetAsync(c, 0, kTileCounters * sizeof(int), tmp);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(tmp);
+  if (tmp != nullptr) cudaStreamDestroy(tmp);
+  cudaThreadExchangeStreamCaptureMode(&mode);
+  if (e != cudaSuccess) {
+    if (w != nullptr) cudaFree(w);
+    if (c != nullptr) cudaFree(c);
+    (void)cudaGetLastError();
+    DTAS_FAIL(DTAS_ECUDA, "gemm: creating the split-K scratch failed: %s", cudaGetErrorString(e));
+  }
+  s->ws = w;          // published last, under the caller's lock: nobody sees half a set
+  s->counters = c;
+  s->used = true;
+  return DTAS_OK;
+}
+
 // Split-K calls are re-entrant across streams: the partial tiles and arrival counters a call uses
-// belong to its stream.  A stream gets its set on its first split-K call (two cudaMallocs; never
-// while the stream is being captured), up to kSplitKSlots sets per device.  When more streams than
-// that issue split-K calls, the least recently used set moves to the new stream, ordered behind
-// everything submitted so far to its previous owner by an event, so the two never overlap on it.
+// belong to its stream.  A stream gets its set on its first split-K call (two cudaMallocs), up to
+// kSplitKSlots sets per device.  When more streams than that issue split-K calls, the least recently
+// used set moves to the new stream, ordered behind everything submitted so far to its previous owner
+// by an event, so the two never overlap on it.  Calls that are being captured into a CUDA graph use
+// one further set of their own, shared by all graphs of the device: replays on one stream are
+// ordered; graphs holding split-K calls must not be replayed at the same time on different streams.
 int acquire_splitk_scratch(DeviceCtx* ctx, cudaStream_t st, float** ws, int** counters) {
   std::lock_guard<std::mutex> lock(g_splitk_mutex);
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st, &cap) != cudaSuccess) {
+    (void)cudaGetLastError();
+    cap = cudaStreamCaptureStatusNone;
+  }
+  if (cap != cudaStreamCaptureStatusNone) {
+    SplitKScratch* s = &ctx->splitk_capture;
+    if (!s->used) {
+      int rc = create_splitk_set(s);
+      if (rc != DTAS_OK) return rc;
+    }
+    *ws = s->ws;
+    *counters = s->counters;
+    return DTAS_OK;
+  }
   const uint64_t now = ++ctx->splitk_clock;
   SplitKScratch* unused = nullptr;
   SplitKScratch* lru = nullptr;
@@ -2092,32 +2137,13 @@ int acquire_splitk_scratch(DeviceCtx* ctx, cudaStream_t st, float** ws, int** co
     }
   }
   if (unused != nullptr) {
-    // allocate and zero into locals, publish last: another thread never sees half a set
-    float* w = nullptr;
-    int* c = nullptr;
-    DTAS_CUDA(cudaMalloc(&w, kSplitKWorkspaceBytes));
-    cudaError_t e = cudaMalloc(&c, kTileCounters * sizeof(int));
-    if (e == cudaSuccess) e = cudaMemsetAsync(c, 0, kTileCounters * sizeof(int), st);   // ordered before the kernel on st
-    if (e != cudaSuccess) {
-      cudaFree(w);
-      if (c != nullptr) cudaFree(c);
-      DTAS_FAIL(DTAS_ECUDA, "gemm: creating the split-K scratch failed: %s", cudaGetErrorString(e));
-    }
-    unused->ws = w;
-    unused->counters = c;
     unused->stream = st;
     unused->last_use = now;
-    unused->used = true;
-    *ws = w;
-    *counters = c;
+    int rc = create_splitk_set(unused);
+    if (rc != DTAS_OK) return rc;
+    *ws = unused->ws;
+    *counters = unused->counters;
     return DTAS_OK;
-  }
-  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-  if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
-    (void)cudaGetLastError();
-    DTAS_FAIL(DTAS_ECUDA, "gemm: all %d split-K scratch sets of this device belong to other streams and one cannot "
-                          "be moved during stream capture; make one split-K call on this stream before capturing",
-              kSplitKSlots);
   }
   cudaEvent_t ev = nullptr;
   bool ordered = false;
@@ -2142,6 +2168,7 @@ int reset_splitk_counters(DeviceCtx* ctx) {
   std::lock_guard<std::mutex> lock(g_splitk_mutex);
   for (SplitKScratch& s : ctx->splitk)
     if (s.used) DTAS_CUDA(cudaMemset(s.counters, 0, kTileCounters * sizeof(int)));
+  if (ctx->splitk_capture.used) DTAS_CUDA(cudaMemset(ctx->splitk_capture.counters, 0, kTileCounters * sizeof(int)));
   DTAS_CUDA(cudaDeviceSynchronize());
   return DTAS_OK;
 }
@@ -2153,6 +2180,11 @@ void free_splitk_scratch(DeviceCtx* ctx) {
     cudaFree(s.ws);
     cudaFree(s.counters);
     s = SplitKScratch();
+  }
+  if (ctx->splitk_capture.used) {
+    cudaFree(ctx->splitk_capture.ws);
+    cudaFree(ctx->splitk_capture.counters);
+    ctx->splitk_capture = SplitKScratch();
   }
 }
 

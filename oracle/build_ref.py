@@ -3,8 +3,10 @@ compiled by TVM for the host CPU.  TEST / BASELINE INFRASTRUCTURE, not product.
 
 The reference measures PrimFuncs that TVM builds; its own package cannot be imported against
 the TVM of this image (it needs `tvm._ffi`, a CUDA-enabled TVM and $TVM_HOME), and this TVM
-has no LLVM backend, so the PrimFuncs are built with target "c" and g++ -O2 (plus
--march=native when `native=True`, which the timed baseline uses).  The result needs the same
+has no LLVM backend, so the PrimFuncs are built with target "c" and g++ -O3 -march=x86-64-v3
+(AVX2 + F16C + FMA available, no FMA contraction of the PrimFunc arithmetic is relied on for parity:
+this build is only timed).  -march=native is not used: the library is built on one machine and
+timed on another.  The result needs the same
 TVM runtime to load (oracle/ref_runner.py).  Nothing is copied from the reference tree: the
 PrimFunc text comes from dtas_b200/workloads/tir_defs.py.
 """
@@ -49,7 +51,7 @@ def build_all(quiet=False, force=False):
     mod = td.make_module(ref_functions())
     lib = tvm.build(mod, target="c") if hasattr(tvm, "build") else tvm.compile(mod, target="c")
     os.makedirs(REF_DIR, exist_ok=True)
-    lib.export_library(REF_SO, options=["-O2", "-march=x86-64-v3", "-Dhalf=_Float16"])
+    lib.export_library(REF_SO, options=["-O3", "-march=x86-64-v3", "-Dhalf=_Float16"])
     if not quiet:
         print(f"built {REF_SO} with TVM {tvm.__version__} (target c)")
     return REF_SO
