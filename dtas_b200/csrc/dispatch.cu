@@ -326,7 +326,7 @@ int dtas_variant_of(const char* op, int64_t m, int64_t n, int64_t k, int device,
 }
 
 int dtas_gemm_set_override(int bn, int split_k) {
-  if (!(bn == 0 || bn == 64 || bn == 128 || bn == 256 || bn == 512 || bn == 1024 || bn == 2048 || bn == 4160 || bn == 4224 || bn == 4352 || bn == 8256 || bn == 8320 || (bn >= 16386 && bn <= 16388)))
+  if (!(bn == 0 || bn == 64 || bn == 128 || bn == 256 || bn == 512 || bn == 513 || bn == 1024 || bn == 2048 || bn == 4160 || bn == 4224 || bn == 4352 || bn == 8256 || bn == 8320 || (bn >= 16386 && bn <= 16388)))
     DTAS_FAIL(DTAS_EINVAL, "gemm override: bn must be 0, 64, 128, 256, 512 (two-CTA 256 x 256 tile) 1024 (swapped operands, m <= 256), 2048 (the same with stream-K) or 4096 + 64/128/256 (single-CTA tiles with stream-K)");
   if (split_k < 0 || split_k > 64) DTAS_FAIL(DTAS_EINVAL, "gemm override: split_k must be in [0, 64]");
   gemm_set_override(bn, split_k);
@@ -335,7 +335,7 @@ int dtas_gemm_set_override(int bn, int split_k) {
 
 int dtas_gemm_table_set(int64_t n, int64_t k, int64_t m_lo, int64_t m_hi, int bn, int split_k) {
   if (n <= 0 || k <= 0 || m_lo < 1 || m_hi < m_lo) DTAS_FAIL(DTAS_EINVAL, "gemm table: bad key n=%lld k=%lld m=[%lld,%lld]", (long long)n, (long long)k, (long long)m_lo, (long long)m_hi);
-  if (!(bn == 0 || bn == 64 || bn == 128 || bn == 256 || bn == 512 || bn == 1024 || bn == 2048 || bn == 4160 || bn == 4224 || bn == 4352 || bn == 8256 || bn == 8320 || (bn >= 16386 && bn <= 16388))) DTAS_FAIL(DTAS_EINVAL, "gemm table: bad tile code %d", bn);
+  if (!(bn == 0 || bn == 64 || bn == 128 || bn == 256 || bn == 512 || bn == 513 || bn == 1024 || bn == 2048 || bn == 4160 || bn == 4224 || bn == 4352 || bn == 8256 || bn == 8320 || (bn >= 16386 && bn <= 16388))) DTAS_FAIL(DTAS_EINVAL, "gemm table: bad tile code %d", bn);
   if (split_k < 0 || split_k > 64) DTAS_FAIL(DTAS_EINVAL, "gemm table: split_k must be in [0, 64]");
   return gemm_table_set(n, k, m_lo, m_hi, bn, split_k);
 }

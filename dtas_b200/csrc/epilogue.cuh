@@ -28,6 +28,9 @@ struct Epilogue {
   int vec_res = 0;                // 16-byte loads from residual rows are aligned (set by the launcher)
 };
 
+// Host and device: true when finishing an element costs more than a bias add and a store.
+inline __host__ __device__ bool epi_has_work(const Epilogue& e) { return e.act != DTAS_ACT_NONE || e.res1 != nullptr; }
+
 #ifdef __CUDACC__
 // GELU, erf form: x * (0.5 + 0.5 * erf(x / sqrt(2))), as the reference's workload spells it
 // (before_dl.py:272-318).  erf by the rational approximation 7.1.26 of Abramowitz & Stegun,

@@ -241,6 +241,7 @@ __device__ __forceinline__ void decode_tile(const GemmArgs& a, int tile, int& mt
 // Producer, MMA issuer and epilogue each walk the same sequence with their own iterator.
 struct TileSeg {
   int mt, nt, tile, kb0, kb1, slot, count;
+  int first;   // stream-K: the CTA that holds contribution 0 of this tile
 };
 struct TileIter {
   int pos, end;
@@ -264,8 +265,10 @@ struct TileIter {
       const int first = u0 / a.sk_per, last = (u0 + a.num_kb - 1) / a.sk_per;
       s.count = last - first + 1;
       s.slot = (int)blockIdx.x - first;
+      s.first = first;
       pos += s.kb1 - s.kb0;
     } else {
+      s.first = 0;
       s.tile = pos / a.splits;
       s.slot = pos - s.tile * a.splits;
       s.count = a.splits;
@@ -447,8 +450,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // Partials are float4s of four consecutive columns, laid out
         // [n tile][slot][column group][row]: the 32 lanes of a warp (32 consecutive rows) write
         // and read 512 contiguous bytes; rows at or beyond m are never touched.
-        float4* ws4 = reinterpret_cast<float4*>(a.ws) + (int64_t)nt * a.slots_cap * (BN / 4) * a.m + row;
-        auto ws_off = [&](int slot, int c4) { return ((int64_t)slot * (BN / 4) + c4) * a.m; };
+        // Stream-K: a CTA's range of units cuts at most two tiles (the one it starts in and the one it
+        // ends in), so its partials go to two tile-sized areas of its own, [CTA][first or last
+        // segment][column group][row in tile]: the workspace does not grow with m or n.  Contribution
+        // `slot` of a tile lives with CTA first + slot; it is that CTA's first segment unless the CTA
+        // began before the tile did.
+        const bool compact = a.sk_per > 0;
+        const int r_in_tile = quarter * 32 + lane;
+        const int64_t tile_u0 = (int64_t)sg.tile * a.num_kb;
+        float4* ws4 = compact ? reinterpret_cast<float4*>(a.ws) + r_in_tile
+                              : reinterpret_cast<float4*>(a.ws) + (int64_t)nt * a.slots_cap * (BN / 4) * a.m + row;
+        auto ws_off = [&](int slot, int c4) -> int64_t {
+          if (compact) {
+            const int cta = sg.first + slot;
+            const int which = ((int64_t)cta * a.sk_per >= tile_u0) ? 0 : 1;
+            return ((int64_t)(cta * 2 + which) * (BN / 4) + c4) * BM;
+          }
+          return ((int64_t)slot * (BN / 4) + c4) * a.m;
+        };
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
@@ -950,7 +969,73 @@ __device__ __forceinline__ void decode_pair_work(int w, int m_tiles, int n_tiles
 }
 
 // a.m_tiles / a.n_tiles count 256 x 256 tiles here; a.splits must be 1.
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+// The work of a CTA pair as a sequence of segments: k-blocks [kb0, kb1) of tile `tile`, being
+// contribution `slot` of `count` to it.  Whole tiles are dealt round-robin to the pairs; with stream-K
+// (a.sk_per > 0) the tiles of the last, partial wave are instead cut, as (tile, k-block) units in
+// tile-major order, into equal consecutive runs of a.sk_per units, one per pair, so that the wave ends
+// for all pairs together whatever the tile count (32 tiles on 74 pairs: 28 k-blocks each instead of 64
+// on fewer than half the pairs).  A tile whose units fall to several pairs is finished through the
+// workspace.
+struct PairSeg {
+  int mt, nt, tile, kb0, kb1, slot, count, first;
+};
+struct PairIter {
+  int pos, end;        // whole tiles: next tile, one past the last whole-tile index
+  int spos, send;      // stream-K tail: next unit and end of this pair's run of (tile, k-block) units
+  int tail_first;      // first tile of the tail
+  __device__ __forceinline__ void init(const GemmArgs& a, int pair, int n_pairs) {
+    const int tiles = a.m_tiles * a.n_tiles;
+    pos = pair;
+    end = tiles;
+    spos = send = 0;
+    tail_first = tiles;
+    if (a.sk_per > 0) {
+      // whole waves of tiles are dealt round-robin (pairs running side by side share X and W tiles in
+      // L2); only the tiles of the last, partial wave are cut into equal runs of k-blocks
+      end = tail_first = (tiles / n_pairs) * n_pairs;
+      const int units = (tiles - tail_first) * a.num_kb;
+      spos = min(pair * a.sk_per, units);
+      send = min(spos + a.sk_per, units);
+    }
+  }
+  __device__ __forceinline__ bool next(const GemmArgs& a, int pair, int n_pairs, PairSeg& s) {
+    if (pos < end) {
+      s.tile = pos;
+      s.kb0 = 0;
+      s.kb1 = a.num_kb;
+      s.first = pair;
+      s.count = 1;
+      s.slot = 0;
+      pos += n_pairs;
+    } else if (spos < send) {
+      const int t = spos / a.num_kb;              // tile within the tail
+      s.tile = tail_first + t;
+      s.kb0 = spos - t * a.num_kb;
+      s.kb1 = min(a.num_kb, s.kb0 + (send - spos));
+      const int u0 = t * a.num_kb;
+      s.first = u0 / a.sk_per;
+      s.count = (u0 + a.num_kb - 1) / a.sk_per - s.first + 1;
+      s.slot = pair - s.first;
+      spos += s.kb1 - s.kb0;
+    } else {
+      return false;
+    }
+    decode_pair_work(s.tile, a.m_tiles, a.n_tiles, s.mt, s.nt);
+    return true;
+  }
+};
+// Named barrier over the epilogue warps of a CTA (4 or 8 of them).
+__device__ __forceinline__ void epilogue_bar_sync_n(int threads) {
+  asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
+}
+
+constexpr int kPairMaxThreads = 32 * (2 + 8);   // producer, MMA issuer and up to eight epilogue warps
+
+// Launched with four epilogue warps (192 threads), or with eight (320 threads) when the epilogue has an
+// activation or residuals to work through: of the two warps that share a quarter of the tensor-memory
+// lanes one then finishes columns 0..127 of the tile and the other columns 128..255, so the tail of a
+// 256 x 256 tile is spread over twice the issue slots and hides behind a shorter main loop.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairMaxThreads, 1)
     gemm_f16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_x,
                                  const __grid_constant__ CUtensorMap tmap_w, const GemmArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -964,12 +1049,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(
       gen_base + kPairStages * kPairStageBytes + 8 * (2 * kPairStages + 4));
+  volatile uint32_t* last_flag_ptr = tmem_slot_ptr + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();          // 0 = leader
   const bool leader = rank == 0;
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-  const int total_work = a.m_tiles * a.n_tiles;
   constexpr uint32_t kPeerMask = 0xFEFFFFFFu;       // clears the CTA-rank bit of a shared::cluster address
 
   if (threadIdx.x == 0) {
@@ -982,7 +1067,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(tfull_bar(i), 1);
-      mbar_init(tempty_bar(i), 2 * (kEpilogueThreads / 32));
+      mbar_init(tempty_bar(i), 2 * ((blockDim.x >> 5) - 2));   // every epilogue warp of both CTAs
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1004,12 +1089,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int w = pair; w < total_work && ok; w += n_pairs) {
-        int mt, nt;
-        decode_pair_work(w, a.m_tiles, a.n_tiles, mt, nt);
-        const int row0 = mt * 2 * BM + (int)rank * BM;          // this CTA's 128 rows of X
-        const int col0 = nt * kPairBN + (int)rank * (kPairBN / 2);  // this CTA's 128 rows of W
-        for (int kb = 0; kb < a.num_kb; ++kb) {
+      PairIter it;
+      PairSeg sg;
+      it.init(a, pair, n_pairs);
+      while (ok && it.next(a, pair, n_pairs, sg)) {
+        const int row0 = sg.mt * 2 * BM + (int)rank * BM;          // this CTA's 128 rows of X
+        const int col0 = sg.nt * kPairBN + (int)rank * (kPairBN / 2);  // this CTA's 128 rows of W
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, a.status, ERR_PRODUCER)) { ok = false; break; }
           if (leader) mbar_expect_tx(full_bar(stage), 2 * kPairStageBytes);
           const uint32_t sa = base + stage * kPairStageBytes;
@@ -1035,13 +1121,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       uint32_t phase = 0;
       int iter = 0;
       bool ok = true;
-      for (int w = pair; w < total_work && ok; w += n_pairs, ++iter) {
+      PairIter it;
+      PairSeg sg;
+      it.init(a, pair, n_pairs);
+      for (; ok && it.next(a, pair, n_pairs, sg); ++iter) {
         const int acc = iter & 1;
         const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, a.status, ERR_MMA_TMEM)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kPairBN);
-        for (int kb = 0; kb < a.num_kb; ++kb) {
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, a.status, ERR_MMA_FULL)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = base + stage * kPairStageBytes;
@@ -1049,7 +1138,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
           const uint64_t db = make_kmajor_sw128_desc(sa + kPairHalfBytes);
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; ++kk)
-            umma_f16_pair(d_tmem, da + 2u * kk, db + 2u * kk, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            umma_f16_pair(d_tmem, da + 2u * kk, db + 2u * kk, idesc, (kb > sg.kb0 || kk > 0) ? 1u : 0u);
           umma_commit_pair(empty_bar(stage), 0x3);
           if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
         }
@@ -1060,23 +1149,111 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   } else {
     // ------------------------------------------------------------------ epilogue (both CTAs)
     const int quarter = warp & 3;
+    const int chunks = (kPairBN / 32) / (((int)blockDim.x >> 5) - 2 > 4 ? 2 : 1);   // 32-column chunks per warp
+    const int c_begin = ((warp - 2) >> 2) * chunks, c_end = c_begin + chunks;
+    const int n_epi_threads = (int)blockDim.x - 64;
+    const int epi_tid = (int)threadIdx.x - 64;
     int iter = 0;
     bool ok = true;
-    for (int w = pair; w < total_work && ok; w += n_pairs, ++iter) {
-      int mt, nt;
-      decode_pair_work(w, a.m_tiles, a.n_tiles, mt, nt);
+    PairIter it;
+    PairSeg sg;
+    it.init(a, pair, n_pairs);
+    for (; ok && it.next(a, pair, n_pairs, sg); ++iter) {
+      const int mt = sg.mt, nt = sg.nt;
       const int acc = iter & 1;
       const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
       if (!mbar_wait(tfull_bar(acc), acc_phase, a.status, ERR_EPILOGUE)) { ok = false; break; }
       tc_fence_after();
-      const int row = mt * 2 * BM + (int)rank * BM + quarter * 32 + lane;
+      const int r_in_tile = quarter * 32 + lane;
+      const int row = mt * 2 * BM + (int)rank * BM + r_in_tile;
       const bool row_ok = row < a.m;
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kPairBN);
       const int col_base = nt * kPairBN;
+      if (sg.count > 1) {
+        // Shared tile (stream-K): park this CTA's 128 x 256 partial, then the last CTA of this rank to
+        // arrive at the tile sums the contributions in slot order = K order and runs the epilogue.
+        // A pair's range cuts at most two tiles, so its partials live in two areas of its own,
+        // [pair][first or last segment][rank][column group][row]: a warp writes and reads 512
+        // contiguous bytes.  The two CTAs of a pair count arrivals separately (one counter per tile
+        // and rank): neither waits for the other, and nobody spins.
+        constexpr int kArea = (kPairBN / 4) * BM;                      // float4s of one CTA's partial tile
+        const int64_t tile_u0 = (int64_t)(sg.tile - it.tail_first) * a.num_kb;   // units are counted within the tail
+        auto area_of = [&](int q) -> int64_t {
+          const int which = ((int64_t)q * a.sk_per >= tile_u0) ? 0 : 1;
+          return (int64_t)((q * 2 + which) * 2 + (int)rank) * kArea + r_in_tile;
+        };
+        float4* ws4 = reinterpret_cast<float4*>(a.ws);
+        float4* mine = ws4 + area_of(pair);
+#pragma unroll 1
+        for (int c = c_begin; c < c_end; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_addr + c * 32, r);
+          tmem_ld_wait();
+          if (row_ok && col_base + c * 32 < a.n) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              mine[(c * 8 + q) * BM] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                   __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(tempty_bar(acc), 0);   // tensor memory no longer needed for this tile
+        __threadfence();
+        epilogue_bar_sync_n(n_epi_threads);
+        if (epi_tid == 0) {
+          int* counter = a.counters + (sg.tile * 2 + (int)rank);
+          const int old = atomicAdd(counter, 1);
+          const uint32_t last = (old == sg.count - 1) ? 1u : 0u;
+          if (last) *counter = 0;          // every contributor has arrived: re-arm for the next launch
+          *last_flag_ptr = last;
+        }
+        epilogue_bar_sync_n(n_epi_threads);
+        const bool is_last = *last_flag_ptr != 0;
+        epilogue_bar_sync_n(n_epi_threads);     // flag consumed before a later tile rewrites it
+        if (is_last) {
+          __threadfence();
+          if (row_ok) {
+            const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+            for (int c = c_begin; c < c_end; ++c) {
+              const int col0 = col_base + c * 32;
+              if (col0 >= a.n) break;
+              const int live4 = min(8, (a.n - col0 + 3) >> 2);
+              float f[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) f[j] = 0.f;
+#pragma unroll 1
+              for (int sb = 0; sb < sg.count; sb += 2) {
+                const bool two = sb + 1 < sg.count;
+                const float4* s0 = ws4 + area_of(sg.first + sb) + (int64_t)c * 8 * BM;
+                const float4* s1 = ws4 + area_of(sg.first + (two ? sb + 1 : sb)) + (int64_t)c * 8 * BM;
+                float4 v0[8], v1[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  const bool on = q < live4;
+                  v0[q] = on ? __ldcg(s0 + q * BM) : zero4;
+                  v1[q] = (on && two) ? __ldcg(s1 + q * BM) : zero4;
+                }
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  f[4 * q] += v0[q].x; f[4 * q + 1] += v0[q].y; f[4 * q + 2] += v0[q].z; f[4 * q + 3] += v0[q].w;
+                }
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  f[4 * q] += v1[q].x; f[4 * q + 1] += v1[q].y; f[4 * q + 2] += v1[q].z; f[4 * q + 3] += v1[q].w;
+                }
+              }
+              epi_store_row32(a.epi, a.y, a.ldy, a.vec_store, row, col0, a.n, f);
+            }
+          }
+        }
+        continue;
+      }
       if (epi_is_plain(a.epi)) {
         __half* yrow = static_cast<__half*>(a.y) + (int64_t)row * a.ldy;
 #pragma unroll 1
-        for (int c = 0; c < kPairBN / 32; ++c) {
+        for (int c = c_begin; c < c_end; ++c) {
           uint32_t r[32];
           tmem_ld32(t_addr + c * 32, r);
           tmem_ld_wait();
@@ -1086,16 +1263,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       } else {
       // Residual rows are fetched two chunks ahead of their use.
       ResChunk r_next, r_after;
-      if (row_ok && epi_can_prefetch(a.epi, col_base, a.n)) epi_prefetch_res32(a.epi, row, col_base, r_next);
-      if (row_ok && epi_can_prefetch(a.epi, col_base + 32, a.n)) epi_prefetch_res32(a.epi, row, col_base + 32, r_after);
+      const int colb = col_base + c_begin * 32;
+      if (row_ok && epi_can_prefetch(a.epi, colb, a.n)) epi_prefetch_res32(a.epi, row, colb, r_next);
+      if (row_ok && epi_can_prefetch(a.epi, colb + 32, a.n)) epi_prefetch_res32(a.epi, row, colb + 32, r_after);
 #pragma unroll 1
-      for (int c = 0; c < kPairBN / 32; ++c) {
+      for (int c = c_begin; c < c_end; ++c) {
         uint32_t r[32];
         tmem_ld32(t_addr + c * 32, r);
         const int col0 = col_base + c * 32;
         const ResChunk r_now = r_next;
         r_next = r_after;
-        if (row_ok && c + 2 < kPairBN / 32 && epi_can_prefetch(a.epi, col0 + 64, a.n)) epi_prefetch_res32(a.epi, row, col0 + 64, r_after);
+        if (row_ok && c + 2 < c_end && epi_can_prefetch(a.epi, col0 + 64, a.n)) epi_prefetch_res32(a.epi, row, col0 + 64, r_after);
         tmem_ld_wait();
         if (row_ok && col0 < a.n) {
           float f[32];
@@ -1579,6 +1757,7 @@ struct GemmPlan {
   int kb_per_split;
   bool simt;
   bool pair = false;   // two-CTA 256 x 256 tiles (gemm_f16_tcgen05_pair_kernel)
+  bool pair_sk = false;  //   ... with stream-K work distribution over the CTA pairs
   bool k2 = false;     // K cut in two inside a cluster of two CTAs (gemm_f16_tcgen05_k2_kernel<bn>), bn = 64 or 128
   int kc = 0;          // > 0: swapped operands, K cut in kc = 2..4 slices inside a cluster (m <= 64)
   int swap_mn = 0;     // > 0: swapped-operand kernel with the X tile padded to this many rows
@@ -1631,12 +1810,12 @@ constexpr int kStreamKMaxM = 1024;
 constexpr bool kSwapByDefault = true;    // swapped-operand kernel for small m
 constexpr int kSwapMaxM = 64;            // beyond that the X tile crowds W out of the ring
 constexpr bool kPairByDefault = true;    // consider two-CTA tiles
-constexpr int kPairMinM = 257;           // below that a 256-row tile is mostly padding
+constexpr int kPairMinM = 257;           // the cost model considers two-CTA tiles from here; a tuned table may choose them from m = 129
 constexpr bool kK2ByDefault = true;      // consider the cluster K-split kernel where it fits one wave
 constexpr bool kSwapKcByDefault = true;  // the same for the swapped-operand kernel
 constexpr int kSwapKcMaxM = 64;          //   up to this m (the X tile of larger m leaves too little room for the slots)
 constexpr size_t kSplitKWorkspaceBytes = 64ull << 20;
-constexpr int kTileCounters = 4096;
+constexpr int kTileCounters = 16384;
 
 // Tile width and split factor for a call shape: the idea of the reference's policy
 // (python/dtas/policy/wmma_config_emiter.py:148-259 - score every candidate tile with a
@@ -1832,7 +2011,8 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok, c
     const int64_t per = (total + grid - 1) / grid;
     grid = (total + per - 1) / per;
     const int slots = (int)((num_kb - 1) / per) + 2;
-    if (!ws_ok(bn, slots)) return q;
+    // partials: two tile-sized areas per CTA, whatever m and n; counters: one per tile
+    if (m_tiles * n_tiles > lim.counters || grid * 2 * (int64_t)BM * bn * 4 > lim.ws_bytes) return q;
     const double smem_clk = (double)(BM * BK * 2 + bn * BK * 2) / 128.0, mma_clk = 2.0 * bn;
     const double narrow = bn == 256 ? 1.0 : (bn == 128 ? 1.4 : 2.2);
     const double t_core = narrow * (mma_clk > smem_clk ? mma_clk : smem_clk) / kClockGHz;
@@ -1883,13 +2063,21 @@ GemmPlan plan_gemm(int64_t m, int64_t n, int64_t k, int sm_count, bool tma_ok, c
     const double cost = (double)rounds * (num_kb * (t_core > t_hbm ? t_core : t_hbm) + kItemFixedNs);
     pair = cost < (k2_cost < best ? k2_cost : best);
   }
-  if (obn == 512) pair = true;
+  if (obn == 512 || obn == 513) pair = true;
   if (obn == 64 || obn == 128 || obn == 256) pair = false;
   if (pair && obn0 < 4096) {
     p.bn = 256;
     p.splits = 1;
     p.kb_per_split = num_kb;
     p.pair = true;
+    // Stream-K over the pairs only on request (tile code 513, from a tuned table): parking a 128 x 256
+    // fp32 partial per CTA and reading the others back with four warps (~40 GB/s) costs more than an
+    // empty half wave saves on the shapes measured so far (m = 4096, N = 512: 38.6 us against 25.4).
+    const int64_t pm = (m + 2 * BM - 1) / (2 * BM), pn = (n + kPairBN - 1) / kPairBN;
+    const int64_t tiles = pm * pn, slots = sm_count / 2 > 0 ? sm_count / 2 : 1;
+    const bool fits = tiles * 2 <= lim.counters && slots * 4 * (int64_t)BM * kPairBN * 4 <= lim.ws_bytes &&
+                      tiles * num_kb < 0x7fffffffLL;
+    p.pair_sk = fits && !lim.tiled_fixed_only && obn == 513;
     return p;
   }
   if (k2_bn > 0 && k2_cost < best && obn == 0 && osp == 0 && obn0 < 4096) {
@@ -1943,7 +2131,7 @@ int launch_tc(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a, i
   return after_launch("gemm_f16_tcgen05_kernel");
 }
 
-int launch_pair(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a, int sm_count, cudaStream_t st) {
+int launch_pair(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a, int sm_count, cudaStream_t st, bool stream_k) {
   static std::atomic<bool> attr_set[64];   // zero-initialised; set after the attribute call returned
   static int max_pairs[64] = {0};
   int dev = 0;
@@ -1954,7 +2142,7 @@ int launch_pair(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a,
     // how many CTA pairs the device can hold at once (one CTA per SM, pairs share a TPC)
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * (unsigned)(sm_count / 2));
-    cfg.blockDim = dim3(kGemmThreads);
+    cfg.blockDim = dim3(kPairMaxThreads);
     cfg.dynamicSmemBytes = kPairSmemBytes;
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
@@ -1973,8 +2161,19 @@ int launch_pair(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a,
   }
   const int total = a.m_tiles * a.n_tiles;
   int pairs = dev < 64 ? max_pairs[dev] : sm_count / 2;
-  if (pairs > total) pairs = total;
-  launch_kernel(gemm_f16_tcgen05_pair_kernel, 2 * pairs, kGemmThreads, kPairSmemBytes, st, tx, tw, a);
+  GemmArgs ap = a;
+  ap.sk_per = 0;
+  const int tail = total % pairs;       // tiles of the last, partial wave
+  if (stream_k && tail > 0) {
+    const int64_t units = (int64_t)tail * a.num_kb;
+    ap.sk_per = (int)((units + pairs - 1) / pairs);     // every pair takes part: the grid stays at `pairs`
+  } else if (pairs > total) {
+    pairs = total;
+  }
+  // twice the epilogue warps when there is an activation or a residual to work through per element, or
+  // partial tiles to read back (the read rate of a CTA grows with the warps that issue the loads)
+  const int threads = (epi_has_work(a.epi) || ap.sk_per > 0) ? kPairMaxThreads : kGemmThreads;
+  launch_kernel(gemm_f16_tcgen05_pair_kernel, 2 * pairs, threads, kPairSmemBytes, st, tx, tw, ap);
   return after_launch("gemm_f16_tcgen05_pair_kernel");
 }
 
@@ -2209,7 +2408,7 @@ int launch_gemm(const void* x, const void* w, const Epilogue& epi, void* y, int6
   }
   float* ws = nullptr;
   int* counters = nullptr;
-  if (p.splits > 1 || p.sk_per > 0) {
+  if (p.splits > 1 || p.sk_per > 0 || p.pair_sk) {
     int rc = acquire_splitk_scratch(ctx, st, &ws, &counters);
     if (rc != DTAS_OK) return rc;
   }
@@ -2243,7 +2442,7 @@ int launch_gemm(const void* x, const void* w, const Epilogue& epi, void* y, int6
   if (p.pair) {
     a.m_tiles = (int)((m + 2 * BM - 1) / (2 * BM));
     a.n_tiles = (int)((n + kPairBN - 1) / kPairBN);
-    return launch_pair(tx, tw, a, ctx->sm_count, st);
+    return launch_pair(tx, tw, a, ctx->sm_count, st, p.pair_sk);
   }
   if (p.swap_mn > 0) {
     a.m_tiles = 1;
@@ -2286,7 +2485,7 @@ void gemm_variant_name(int64_t m, int64_t n, int64_t k, const DeviceCtx* ctx, ch
     return;
   }
   if (p.pair) {
-    snprintf(buf, len, "gemm_tcgen05_2cta_bm256_bn256_bk64_s%d", kPairStages);
+    snprintf(buf, len, "gemm_tcgen05_2cta_bm256_bn256_bk64_s%d%s", kPairStages, p.pair_sk ? "_streamk" : "");
     return;
   }
   if (p.k2) {

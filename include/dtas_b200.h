@@ -163,7 +163,8 @@ int dtas_variant_of(const char* op, int64_t m, int64_t n, int64_t k, int device,
                     char* buf, int buf_len);
 
 /* Overrides the GEMM dispatch for testing and offline re-tuning: block-tile
- * width bn in {64,128,256} (0 = automatic; 512 = the two-CTA kernel with 256 x 256 tiles;
+ * width bn in {64,128,256} (0 = automatic; 512 = the two-CTA kernel with 256 x 256 tiles dealt out whole,
+ * 513 = the same kernel with stream-K work distribution over the CTA pairs;
  * 1024 = the swapped-operand kernel, which applies to m <= 256; 2048 = the same kernel with
  * stream-K work distribution; 4096 + 64/128/256 = single-CTA tiles of that width with stream-K;
  * 8192 + 64/128 = tiles of that width with K cut in two inside a two-CTA cluster, the second half

@@ -360,16 +360,20 @@ def test_gemm_every_tile_width_and_split(cuda_device, bn, split):
     assert bool((wide[:, :8] == 5.0).all()) and bool((wide[:, 8 + n:] == 5.0).all()), "wrote outside its column slab"
 
 
-@pytest.mark.parametrize("m,n,k", [(1024, 4096, 4096), (4096, 12288, 4096), (1000, 2752, 11008), (300, 520, 72)])
-def test_gemm_two_cta_kernel(cuda_device, m, n, k):
-    """The cta_group::2 kernel (256 x 256 tiles on CTA pairs), forced, on full and ragged shapes."""
+@pytest.mark.parametrize("code", [512, 513])
+@pytest.mark.parametrize("m,n,k", [(1024, 4096, 4096), (4096, 12288, 4096), (1000, 2752, 11008), (300, 520, 72),
+                                   (4096, 512, 4096), (200, 22016, 1024), (130, 1000, 2120)])
+def test_gemm_two_cta_kernel(cuda_device, m, n, k, code):
+    """The cta_group::2 kernel (256 x 256 tiles on CTA pairs), forced, on full and ragged shapes: tiles
+    dealt out whole (512) and with the last, partial wave cut stream-K fashion and finished through the
+    workspace (513; tile counts below, at and above the number of pairs)."""
     x = seeded_normal((m, k), 97, "float16")
     w = seeded_normal((n, k), 98, "float16", scale=0.02)
     xd, wd = x.to(cuda_device), w.to(cuda_device)
     big, y = guarded((m, n), torch.float16, cuda_device, 5.0)
-    _abi.check(_abi.lib().dtas_gemm_set_override(512, 0))
+    _abi.check(_abi.lib().dtas_gemm_set_override(code, 0))
     try:
-        assert "2cta" in _abi.variant_of("gemm", m, n, k)
+        assert "2cta" in _abi.variant_of("gemm", m, n, k) and ("streamk" in _abi.variant_of("gemm", m, n, k)) == (code == 513)
         ops.gemm_nt(xd, wd, y)
         ops.poll_status()
         y2 = torch.empty_like(y)
