@@ -326,7 +326,8 @@ def gather_points(rank, world, dev, barrier):
     alone (this rank's column slab, written into its slot of the [g, m, N/g] buffer) and the
     kernel followed by one NCCL all-gather of that buffer, and the same result by pushing row
     blocks into the peers' buffers behind the kernel (this library's push kernel, or one
-    cudaMemcpyAsync per peer), all timed with CUDA events on the launching stream over a batch of
+    cudaMemcpyAsync per peer), or by the GEMM whose epilogue stores every tile to the peers as well
+    (dtas_gemm_nt_scatter + one barrier), all timed with CUDA events on the launching stream over a batch of
     eager calls, max over ranks.  Weights rotate through enough
     copies that a shard is not served from L2."""
     import torch
@@ -364,7 +365,10 @@ def gather_points(rank, world, dev, barrier):
         local_us = timed(lambda i: lins[i % copies].forward_local(x, out=buf[rank]))
         gathered_us = timed(lambda i: lins[i % copies].forward_gathered(x, buf=buf))
         pushed = {}
-        for engine in ("kernel", "copy"):
+        for engine in ("kernel", "copy", "epilogue"):
+            if engine == "epilogue" and m < 129:
+                pushed[engine] = None          # the GEMM that stores to the peers itself needs 129 rows
+                continue
             pbuf = PeerGatherBuffer(world, m, n_local, f16, dev, engine=engine)
             pushed[engine] = timed(lambda i: lins[i % copies].forward_pushed(x, pbuf, min_push_bytes=0))
             del pbuf
@@ -372,6 +376,7 @@ def gather_points(rank, world, dev, barrier):
                     "kernel_plus_all_gather_us": round(gathered_us, 2),
                     "kernel_plus_peer_push_us": round(pushed["kernel"], 2),
                     "kernel_plus_copy_engine_push_us": round(pushed["copy"], 2),
+                    "gemm_storing_to_peers_us": None if pushed["epilogue"] is None else round(pushed["epilogue"], 2),
                     "gather_bytes_per_rank": 2 * m * n_local, "mode": "eager calls, max over ranks"})
         del lins, buf, x
         torch.cuda.empty_cache()

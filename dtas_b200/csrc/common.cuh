@@ -173,7 +173,7 @@ void gemv_variant_name(int64_t n, int64_t k, const DeviceCtx* ctx, char* buf, in
 void gemv_set_override(int wpr, int unroll);
 
 int launch_gemm(const void* x, const void* w, const Epilogue& epi, void* y, int64_t m, int64_t n,
-                int64_t k, int64_t ldy, DeviceCtx* ctx, cudaStream_t st);
+                int64_t k, int64_t ldy, DeviceCtx* ctx, cudaStream_t st, const PeerOut* peers = nullptr);
 void gemm_variant_name(int64_t m, int64_t n, int64_t k, const DeviceCtx* ctx, char* buf, int len);
 void gemm_set_override(int bn, int split_k);
 int gemm_table_set(int64_t n, int64_t k, int64_t m_lo, int64_t m_hi, int bn, int split_k);

@@ -295,6 +295,33 @@ int dtas_gemm_nt_fused(const void* x, const void* w, const void* bias, const voi
   return launch_add_residuals(y, res1, res2, m * n, c.ctx, c.stream, bucket_of(m));
 }
 
+int dtas_gemm_nt_scatter(const void* x, const void* w, const void* bias, void* y, void* const* peer_ys, int n_peers,
+                         int64_t m, int64_t n, int64_t k, int64_t ldy, int dtype, int device, void* stream) {
+  DTAS_NONNULL("gemm_scatter", x);
+  DTAS_NONNULL("gemm_scatter", w);
+  DTAS_NONNULL("gemm_scatter", y);
+  DTAS_NONNULL("gemm_scatter", peer_ys);
+  if (n_peers < 1 || n_peers > DTAS_MAX_PEERS)
+    DTAS_FAIL(DTAS_EINVAL, "gemm_scatter: n_peers = %d is not in 1..%d", n_peers, DTAS_MAX_PEERS);
+  if (m <= 0) DTAS_FAIL(DTAS_EINVAL, "gemm_scatter: dynamic dim m must be > 0, got %lld", (long long)m);
+  if (n <= 0 || k <= 0) DTAS_FAIL(DTAS_EINVAL, "gemm_scatter: n and k must be > 0");
+  if (ldy < n) DTAS_FAIL(DTAS_EINVAL, "gemm_scatter: ldy (%lld) must be >= n (%lld)", (long long)ldy, (long long)n);
+  if (dtype != DTAS_F16) DTAS_FAIL(DTAS_EUNSUPPORTED, "gemm_scatter: only fp16 is implemented (dtype %d)", dtype);
+  PeerOut peers;
+  peers.n = n_peers;
+  for (int j = 0; j < n_peers; ++j) {
+    if (peer_ys[j] == nullptr) DTAS_FAIL(DTAS_EINVAL, "gemm_scatter: peer_ys[%d] is null", j);
+    if (peer_ys[j] == y) DTAS_FAIL(DTAS_EINVAL, "gemm_scatter: peer_ys[%d] is y itself", j);
+    peers.y[j] = peer_ys[j];
+  }
+  Call c;
+  int rc;
+  if ((rc = c.begin(device, stream))) return rc;
+  Epilogue epi;
+  epi.bias = static_cast<const __half*>(bias);
+  return launch_gemm(x, w, epi, y, m, n, k, ldy, c.ctx, c.stream, &peers);
+}
+
 int dtas_bucket_of(const char* op, int64_t m) {
   if (op_index(op) < 0) return -1;
   return bucket_of(m);

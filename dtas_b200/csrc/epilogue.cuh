@@ -28,6 +28,15 @@ struct Epilogue {
   int vec_res = 0;                // 16-byte loads from residual rows are aligned (set by the launcher)
 };
 
+// Further copies of Y: base pointers of buffers with Y's layout (same row stride, same dtype) in which
+// every stored vector is stored again.  With the output columns of a GEMM sharded over g GPUs these are
+// the places of this rank's slab in the other ranks' gather buffers (peer memory mapped into this
+// process), so the gather rides on the epilogue of the GEMM tile by tile instead of following it.
+struct PeerOut {
+  void* y[DTAS_MAX_PEERS] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  int n = 0;
+};
+
 // Host and device: true when finishing an element costs more than a bias add and a store.
 inline __host__ __device__ bool epi_has_work(const Epilogue& e) { return e.act != DTAS_ACT_NONE || e.res1 != nullptr; }
 
@@ -189,31 +198,42 @@ __device__ __forceinline__ bool epi_is_plain(const Epilogue& e) {
 }
 // The plain tail for 32 consecutive columns of one row, from the raw accumulator words.
 __device__ __forceinline__ void epi_store_row32_plain(const __half* bias, __half* yrow, int vec_store, int col0, int n,
-                                                      uint32_t* r) {
+                                                      uint32_t* r, const PeerOut* peers = nullptr, int64_t row_off = 0) {
   if (bias != nullptr) {
 #pragma unroll
     for (int j = 0; j < 32; ++j)
       if (col0 + j < n) r[j] = __float_as_uint(__uint_as_float(r[j]) + __half2float(bias[col0 + j]));
   }
+  const int n_peers = peers != nullptr ? peers->n : 0;
   if (vec_store && col0 + 32 <= n) {
-    uint4* dst = reinterpret_cast<uint4*>(yrow + col0);
+    uint4 v[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      uint4 v;
       __half2 h0 = __floats2half2_rn(__uint_as_float(r[8 * q + 0]), __uint_as_float(r[8 * q + 1]));
       __half2 h1 = __floats2half2_rn(__uint_as_float(r[8 * q + 2]), __uint_as_float(r[8 * q + 3]));
       __half2 h2 = __floats2half2_rn(__uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5]));
       __half2 h3 = __floats2half2_rn(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7]));
-      v.x = *reinterpret_cast<uint32_t*>(&h0);
-      v.y = *reinterpret_cast<uint32_t*>(&h1);
-      v.z = *reinterpret_cast<uint32_t*>(&h2);
-      v.w = *reinterpret_cast<uint32_t*>(&h3);
-      dst[q] = v;
+      v[q].x = *reinterpret_cast<uint32_t*>(&h0);
+      v[q].y = *reinterpret_cast<uint32_t*>(&h1);
+      v[q].z = *reinterpret_cast<uint32_t*>(&h2);
+      v[q].w = *reinterpret_cast<uint32_t*>(&h3);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(yrow + col0);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) dst[q] = v[q];
+    for (int p = 0; p < n_peers; ++p) {
+      uint4* pd = reinterpret_cast<uint4*>(static_cast<__half*>(peers->y[p]) + row_off + col0);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) pd[q] = v[q];
     }
   } else {
 #pragma unroll
     for (int j = 0; j < 32; ++j)
-      if (col0 + j < n) yrow[col0 + j] = __float2half_rn(__uint_as_float(r[j]));
+      if (col0 + j < n) {
+        const __half h = __float2half_rn(__uint_as_float(r[j]));
+        yrow[col0 + j] = h;
+        for (int p = 0; p < n_peers; ++p) static_cast<__half*>(peers->y[p])[row_off + col0 + j] = h;
+      }
   }
 }
 
@@ -221,7 +241,9 @@ __device__ __forceinline__ void epi_store_row32_plain(const __half* bias, __half
 // products) and stores them.  vec_store: 16-byte stores into Y rows are aligned.  `pre`, when
 // given, holds the residual values of this chunk fetched earlier (epi_prefetch_res32).
 __device__ __forceinline__ void epi_store_row32(const Epilogue& e, void* y, int64_t ldy, int vec_store, int64_t row,
-                                                int col0, int n, float* acc32, const ResChunk* pre = nullptr) {
+                                                int col0, int n, float* acc32, const ResChunk* pre = nullptr,
+                                                const PeerOut* peers = nullptr) {
+  const int n_peers = peers != nullptr ? peers->n : 0;
   if (e.bias != nullptr) {
 #pragma unroll
     for (int j = 0; j < 32; ++j)
@@ -255,24 +277,38 @@ __device__ __forceinline__ void epi_store_row32(const Epilogue& e, void* y, int6
         v.z = *reinterpret_cast<uint32_t*>(&h2);
         v.w = *reinterpret_cast<uint32_t*>(&h3);
         dst[q] = v;
+        for (int p = 0; p < n_peers; ++p)
+          reinterpret_cast<uint4*>(static_cast<__half*>(peers->y[p]) + row * ldy + col0)[q] = v;
       }
     } else {
 #pragma unroll
       for (int j = 0; j < 32; ++j)
-        if (col0 + j < n) yrow[col0 + j] = __float2half_rn(acc32[j]);
+        if (col0 + j < n) {
+          const __half h = __float2half_rn(acc32[j]);
+          yrow[col0 + j] = h;
+          for (int p = 0; p < n_peers; ++p) static_cast<__half*>(peers->y[p])[row * ldy + col0 + j] = h;
+        }
     }
   } else {
     float* yrow = static_cast<float*>(y) + row * ldy;
     if (full) {
       float4* dst = reinterpret_cast<float4*>(yrow + col0);
 #pragma unroll
-      for (int q = 0; q < 8; ++q)
-        dst[q] = make_float4(__half2float(__float2half_rn(acc32[4 * q + 0])), __half2float(__float2half_rn(acc32[4 * q + 1])),
-                             __half2float(__float2half_rn(acc32[4 * q + 2])), __half2float(__float2half_rn(acc32[4 * q + 3])));
+      for (int q = 0; q < 8; ++q) {
+        const float4 v = make_float4(__half2float(__float2half_rn(acc32[4 * q + 0])), __half2float(__float2half_rn(acc32[4 * q + 1])),
+                                     __half2float(__float2half_rn(acc32[4 * q + 2])), __half2float(__float2half_rn(acc32[4 * q + 3])));
+        dst[q] = v;
+        for (int p = 0; p < n_peers; ++p)
+          reinterpret_cast<float4*>(static_cast<float*>(peers->y[p]) + row * ldy + col0)[q] = v;
+      }
     } else {
 #pragma unroll
       for (int j = 0; j < 32; ++j)
-        if (col0 + j < n) yrow[col0 + j] = __half2float(__float2half_rn(acc32[j]));
+        if (col0 + j < n) {
+          const float v = __half2float(__float2half_rn(acc32[j]));
+          yrow[col0 + j] = v;
+          for (int p = 0; p < n_peers; ++p) static_cast<float*>(peers->y[p])[row * ldy + col0 + j] = v;
+        }
     }
   }
 }

@@ -205,6 +205,7 @@ struct GemmArgs {
   int vec_store;      // 1 when 16-byte stores into Y are aligned
   int sk_per = 0;     // > 0: stream-K, every CTA owns sk_per consecutive (tile, k-block) units
   int slots_cap = 0;  // partial-tile slots reserved per output tile in the workspace
+  PeerOut peers;      // two-CTA kernel: further buffers that receive every stored vector of Y
 };
 
 template <int BN>
@@ -951,10 +952,15 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t cta) 
 constexpr int kPairBN = 256;                 // columns of the pair's tile
 constexpr int kPairHalfBytes = BM * BK * 2;  // one 128 x 64 fp16 operand half: 16 KB
 constexpr int kPairStageBytes = 2 * kPairHalfBytes;
-constexpr int kPairStages = 7;
+#ifndef DTAS_PAIR_STAGED_STORE
+#define DTAS_PAIR_STAGED_STORE 1      // 0: one more operand stage instead of the store staging area (for A/B timing)
+#endif
+constexpr int kPairStages = DTAS_PAIR_STAGED_STORE ? 6 : 7;
+// per epilogue warp 32 rows x 128 fp16 columns, staged for row-contiguous stores
+constexpr int kPairStoreStage = DTAS_PAIR_STAGED_STORE ? 4 * 32 * 256 : 0;
 constexpr int kPairTmemCols = 2 * kPairBN;
 constexpr int kPairBarBytes = (2 * kPairStages + 4) * 8 + 16;
-constexpr int kPairSmemBytes = 1024 + kPairStages * kPairStageBytes + kPairBarBytes;
+constexpr int kPairSmemBytes = 1024 + kPairStages * kPairStageBytes + kPairStoreStage + kPairBarBytes;
 static_assert(kPairSmemBytes <= 227 * 1024, "smem");
 constexpr int kPairGroupM = 8;               // 256-row tiles per rasterisation band
 constexpr int ERR_PAIR_TAIL = 0x105;
@@ -1040,7 +1046,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairMaxThreads, 1)
                                  const __grid_constant__ CUtensorMap tmap_w, const GemmArgs a) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bars = base + kPairStages * kPairStageBytes;
+  const uint32_t store_stage = base + kPairStages * kPairStageBytes;
+  const uint32_t bars = store_stage + kPairStoreStage;
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (kPairStages + s); };
   auto tfull_bar = [&](int i) { return bars + 8u * (2 * kPairStages + i); };
@@ -1048,7 +1055,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairMaxThreads, 1)
   const uint32_t tmem_slot = bars + 8u * (2 * kPairStages + 4);
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(
-      gen_base + kPairStages * kPairStageBytes + 8 * (2 * kPairStages + 4));
+      gen_base + kPairStages * kPairStageBytes + kPairStoreStage + 8 * (2 * kPairStages + 4));
   volatile uint32_t* last_flag_ptr = tmem_slot_ptr + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1244,7 +1251,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairMaxThreads, 1)
                   f[4 * q] += v1[q].x; f[4 * q + 1] += v1[q].y; f[4 * q + 2] += v1[q].z; f[4 * q + 3] += v1[q].w;
                 }
               }
-              epi_store_row32(a.epi, a.y, a.ldy, a.vec_store, row, col0, a.n, f);
+              epi_store_row32(a.epi, a.y, a.ldy, a.vec_store, row, col0, a.n, f, nullptr, &a.peers);
             }
           }
         }
@@ -1252,13 +1259,67 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairMaxThreads, 1)
       }
       if (epi_is_plain(a.epi)) {
         __half* yrow = static_cast<__half*>(a.y) + (int64_t)row * a.ldy;
+        // Four warps (the plain launch): 128 columns at a time go through shared memory, so that a warp
+        // stores two whole rows of 256 contiguous bytes per instruction instead of 16 bytes of each of
+        // its 32 rows - full lines for the local Y and, where the result is also stored to other GPUs,
+        // for NVLink.  Thread = row writes its 16-byte vectors at chunk ^ (row & 7): both the writes (a
+        // quarter warp = 8 rows, one chunk) and the reads (a quarter warp = 8 chunks of one row) then
+        // cover all 32 banks.
+        const bool staged = DTAS_PAIR_STAGED_STORE && a.vec_store && warp < 6;
+        uint4* stage = reinterpret_cast<uint4*>(gen_base + (store_stage - base)) + (warp - 2) * (32 * 16);
+        const int row_base = mt * 2 * BM + (int)rank * BM + quarter * 32;
 #pragma unroll 1
-        for (int c = c_begin; c < c_end; ++c) {
-          uint32_t r[32];
-          tmem_ld32(t_addr + c * 32, r);
-          tmem_ld_wait();
-          const int col0 = col_base + c * 32;
-          if (row_ok && col0 < a.n) epi_store_row32_plain(a.epi.bias, yrow, a.vec_store, col0, a.n, r);
+        for (int c = c_begin; c < c_end; c += 4) {
+          const int colb = col_base + c * 32;
+          if (!(staged && c + 4 <= c_end && colb + 128 <= a.n)) {
+#pragma unroll 1
+            for (int cc = c; cc < min(c + 4, c_end); ++cc) {
+              uint32_t r[32];
+              tmem_ld32(t_addr + cc * 32, r);
+              tmem_ld_wait();
+              const int col0 = col_base + cc * 32;
+              if (row_ok && col0 < a.n) epi_store_row32_plain(a.epi.bias, yrow, a.vec_store, col0, a.n, r, &a.peers, (int64_t)row * a.ldy);
+            }
+            continue;
+          }
+#pragma unroll 1
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t r[32];
+            tmem_ld32(t_addr + (c + cc) * 32, r);
+            tmem_ld_wait();
+            if (a.epi.bias != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                r[j] = __float_as_uint(__uint_as_float(r[j]) + __half2float(a.epi.bias[colb + cc * 32 + j]));
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 v;
+              __half2 h0 = __floats2half2_rn(__uint_as_float(r[8 * q + 0]), __uint_as_float(r[8 * q + 1]));
+              __half2 h1 = __floats2half2_rn(__uint_as_float(r[8 * q + 2]), __uint_as_float(r[8 * q + 3]));
+              __half2 h2 = __floats2half2_rn(__uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5]));
+              __half2 h3 = __floats2half2_rn(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7]));
+              v.x = *reinterpret_cast<uint32_t*>(&h0);
+              v.y = *reinterpret_cast<uint32_t*>(&h1);
+              v.z = *reinterpret_cast<uint32_t*>(&h2);
+              v.w = *reinterpret_cast<uint32_t*>(&h3);
+              stage[lane * 16 + ((cc * 4 + q) ^ (lane & 7))] = v;
+            }
+          }
+          __syncwarp();
+          const int ch = lane & 15;
+#pragma unroll 4
+          for (int it = 0; it < 16; ++it) {
+            const int rl = 2 * it + (lane >> 4);
+            const int64_t grow = row_base + rl;
+            if (grow < a.m) {
+              const uint4 v = stage[rl * 16 + (ch ^ (rl & 7))];
+              const int64_t off = grow * a.ldy + colb + ch * 8;
+              *reinterpret_cast<uint4*>(static_cast<__half*>(a.y) + off) = v;
+              for (int p = 0; p < a.peers.n; ++p) *reinterpret_cast<uint4*>(static_cast<__half*>(a.peers.y[p]) + off) = v;
+            }
+          }
+          __syncwarp();
         }
       } else {
       // Residual rows are fetched two chunks ahead of their use.
@@ -1280,7 +1341,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairMaxThreads, 1)
 #pragma unroll
           for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
           epi_store_row32(a.epi, a.y, a.ldy, a.vec_store, row, col0, a.n, f,
-                          epi_can_prefetch(a.epi, col0, a.n) ? &r_now : nullptr);
+                          epi_can_prefetch(a.epi, col0, a.n) ? &r_now : nullptr, &a.peers);
         }
       }
       }
@@ -1810,6 +1871,7 @@ constexpr int kStreamKMaxM = 1024;
 constexpr bool kSwapByDefault = true;    // swapped-operand kernel for small m
 constexpr int kSwapMaxM = 64;            // beyond that the X tile crowds W out of the ring
 constexpr bool kPairByDefault = true;    // consider two-CTA tiles
+constexpr int kScatterMinM = 129;        // dtas_gemm_nt_scatter: rows from which a 256-row tile is at least half full
 constexpr int kPairMinM = 257;           // the cost model considers two-CTA tiles from here; a tuned table may choose them from m = 129
 constexpr bool kK2ByDefault = true;      // consider the cluster K-split kernel where it fits one wave
 constexpr bool kSwapKcByDefault = true;  // the same for the swapped-operand kernel
@@ -2395,10 +2457,18 @@ static int finish_epilogue(Epilogue& e, const void* y, int64_t ldy) {
 }
 
 int launch_gemm(const void* x, const void* w, const Epilogue& epi, void* y, int64_t m, int64_t n,
-                int64_t k, int64_t ldy, DeviceCtx* ctx, cudaStream_t st) {
+                int64_t k, int64_t ldy, DeviceCtx* ctx, cudaStream_t st, const PeerOut* peers) {
   if (m > 0x7fffffffLL / 2 || n > 0x7fffffffLL / 2 || k > 0x7fffffffLL / 2)
     DTAS_FAIL(DTAS_EINVAL, "gemm: dimension too large");
-  const GemmPlan p = plan_gemm(m, n, k, ctx->sm_count, gemm_tma_ok(x, w, k));
+  GemmPlan p = plan_gemm(m, n, k, ctx->sm_count, gemm_tma_ok(x, w, k));
+  const bool scatter = peers != nullptr && peers->n > 0;
+  if (scatter && !p.pair) {
+    // only the two-CTA kernel stores to further buffers; it serves any m, at a loss below ~128 rows
+    if (p.simt || m < kScatterMinM)
+      DTAS_FAIL(DTAS_EUNSUPPORTED, "gemm (scatter): needs m >= %d, 16-byte aligned operands and k a multiple of 8", kScatterMinM);
+    p = GemmPlan{256, 1, (int)((k + BK - 1) / BK), false};
+    p.pair = true;
+  }
   if (p.simt) {
     dim3 grid((unsigned)((n + 15) / 16), (unsigned)((m + 15) / 16));
     if (grid.y > 65535) DTAS_FAIL(DTAS_EUNSUPPORTED, "gemm: unaligned operands with m > 1048560");
@@ -2436,6 +2506,11 @@ int launch_gemm(const void* x, const void* w, const Epilogue& epi, void* y, int6
   a.kb_per_split = p.kb_per_split;
   a.num_kb = (int)((k + BK - 1) / BK);
   a.vec_store = finish_epilogue(a.epi, y, ldy);
+  if (scatter) {
+    a.peers = *peers;
+    for (int j = 0; j < peers->n; ++j)
+      if (!aligned16(peers->y[j])) a.vec_store = 0;      // scalar stores everywhere rather than a fault
+  }
   if ((int64_t)a.m_tiles * a.n_tiles * a.splits > 0x7fffffffLL)
     DTAS_FAIL(DTAS_EINVAL, "gemm: too many tiles");
   if (p.k2) return p.bn == 128 ? launch_k2<128>(tx, tw, a, st) : launch_k2<64>(tx, tw, a, st);

@@ -131,8 +131,12 @@ class ColumnShardedLinear:
         every other rank's buffer over NVLink while the next block is computed.  A barrier across
         ranks on the launching stream ends the call (every rank's pushes have landed), and one
         opens it when the buffer has been used before (every rank has finished reading the previous
-        contents).  Results equal forward_gathered's bit for bit as long as a row block selects
-        a kernel with the same K order as the whole m would (no split-K from 1024 rows up).
+        contents; readers of the buffer must be on the launching stream, which is the only stream the
+        barrier orders).  Results equal forward_gathered's bit for bit as long as a row block selects a
+        kernel with the same K order as the whole m would (no split-K from 1024 rows up) and takes the
+        same residual route: with residuals and m >= 2048, forward_gathered adds them in a pass of its
+        own behind the GEMM (two roundings) while a row block below 2048 rows adds them in the GEMM
+        epilogue (one rounding), so those results agree to one fp16 ULP, not bit for bit.
 
         The two barriers and the second stream cost about 80 us of host and launch time, so a
         slab below `min_push_bytes` takes forward_gathered's route (one all-gather) into the same
@@ -140,12 +144,19 @@ class ColumnShardedLinear:
         m = x.shape[0]
         if pbuf.local.shape != (self.world, m, self.n_local):
             raise ValueError(f"gather buffer is {tuple(pbuf.local.shape)}, expected {(self.world, m, self.n_local)}")
-        if m * self.n_local * pbuf.local.element_size() < min_push_bytes:
-            return self.forward_gathered(x, buf=pbuf.local, res1=res1, res2=res2)
         main = torch.cuda.current_stream(x.device)
         if pbuf.used:
-            pbuf.barrier()
+            pbuf.barrier()       # every rank has finished reading the previous contents (on its launching stream)
         pbuf.used = True
+        if m * self.n_local * pbuf.local.element_size() < min_push_bytes:
+            return self.forward_gathered(x, buf=pbuf.local, res1=res1, res2=res2)
+        if pbuf.engine == "epilogue" and self.world > 1 and m >= 129 and res1 is None and self.act is None \
+                and self._compute is None:
+            # one launch: the GEMM's own epilogue stores every finished tile into the peers' buffers
+            from . import ops
+            ops.gemm_nt_scatter(x, self.w, pbuf.local[self.rank], [p[self.rank] for p in pbuf.peers], bias=self.bias)
+            pbuf.barrier()
+            return pbuf.local
         blocks = max(1, m // max(1, block_rows))
         rows = -(-m // blocks)
         mine = pbuf.local[self.rank]
@@ -186,14 +197,17 @@ class PeerGatherBuffer:
     def __init__(self, world: int, m: int, n_local: int, dtype, device, group=None, engine: str = "auto"):
         import torch.distributed._symmetric_memory as symm
         if engine == "auto":
-            engine = "copy" if world <= 4 else "kernel"
-        if engine not in ("kernel", "copy"):
-            raise ValueError("engine is 'auto', 'kernel' (this library's push kernel) or 'copy' (cudaMemcpyAsync per peer)")
+            engine = "epilogue"
+        if engine not in ("kernel", "copy", "epilogue"):
+            raise ValueError("engine is 'auto', 'kernel' (this library's push kernel), 'copy' (cudaMemcpyAsync per peer) "
+                             "or 'epilogue' (the GEMM stores to the peers itself; other cases fall back to 'copy')")
         group = group if group is not None else dist.group.WORLD
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = world
         self.engine = engine
+        # how row blocks travel when the GEMM cannot store to the peers itself
+        self.push_engine = engine if engine != "epilogue" else ("copy" if world <= 4 else "kernel")
         shape = (world, m, n_local)
         self.local = symm.empty(shape, dtype=dtype, device=device)
         self.handle = symm.rendezvous(self.local, group)
@@ -214,7 +228,7 @@ class PeerGatherBuffer:
         self.side.wait_event(ev)
         src = self.local[slot, r0:r1]
         with torch.cuda.stream(self.side):
-            if self.engine == "kernel":
+            if self.push_engine == "kernel":
                 ops.peer_push(src, [p[slot, r0:r1] for p in self.peers])
             else:
                 for p in self.peers:

@@ -240,6 +240,36 @@ def gemm_nt(x, w, out, bias=None, res1=None, res2=None, act=None):
     return out
 
 
+def gemm_nt_scatter(x, w, out, peers, bias=None):
+    """out[m, N] = x[m, K] @ w[N, K]^T (+ bias), and every stored vector of `out` again into each tensor of
+    `peers`: views, on this device, with out's shape and row stride - the place of this rank's column
+    slab in the other ranks' gather buffers (peer memory).  One launch; the stores to the peers leave
+    from the GEMM's epilogue tile by tile.  Run a barrier across ranks before a gathered buffer is read.
+    Raises DtasError(EUNSUPPORTED) below 129 rows (use gemm_nt and peer_push there)."""
+    import ctypes
+    m, k = _rows_cols(x, "gemm_scatter")
+    mo, n = _rows_cols(out, "gemm_scatter")
+    if x.device.type != "cuda":
+        raise _abi.DtasError(_abi.EINVAL, f"gemm_scatter: tensors must live on a CUDA device, got {x.device}")
+    if w.dim() != 2 or int(w.shape[1]) != k or int(w.shape[0]) != n or mo != m:
+        raise _abi.DtasError(_abi.EINVAL, f"gemm_scatter: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if not (x.dtype == w.dtype == out.dtype == torch.float16) or not x.is_contiguous() or not w.is_contiguous():
+        raise _abi.DtasError(_abi.EUNSUPPORTED, "gemm_scatter: contiguous fp16 operands and an fp16 output")
+    if out.stride(-1) != 1:
+        raise _abi.DtasError(_abi.EINVAL, "gemm_scatter: out must have unit stride in its last dim")
+    ldy = int(out.stride(-2)) if m > 1 else max(int(out.stride(-2)), n)
+    for p in peers:
+        if p.dtype != out.dtype or tuple(p.shape) != tuple(out.shape) or p.stride() != out.stride():
+            raise _abi.DtasError(_abi.EINVAL, "gemm_scatter: every peer view must have out's dtype, shape and strides")
+    if bias is not None and (bias.dtype != torch.float16 or bias.numel() != n or not bias.is_contiguous()):
+        raise _abi.DtasError(_abi.EINVAL, "gemm_scatter: bias must be a contiguous fp16 vector of N elements")
+    dev = x.device.index if x.device.index is not None else torch.cuda.current_device()
+    ptrs = (ctypes.c_void_p * len(peers))(*[p.data_ptr() for p in peers])
+    _chk(_lib().dtas_gemm_nt_scatter(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), ptrs, len(peers), m, n, k,
+                                     ldy, _abi.F16, dev, _raw_stream(dev)))
+    return out
+
+
 def poll_status(device=None):
     """Synchronises `device` and raises DtasError(ETIMEOUT) if a bounded device-side wait gave up."""
     if device is None:

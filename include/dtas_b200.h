@@ -219,6 +219,21 @@ int dtas_set_pdl(int mode);
 #define DTAS_MAX_PEERS 7
 int dtas_peer_push(const void* src, void* const* dsts, int n_dsts, int64_t bytes, int device, void* stream);
 
+/* The same gather fused into the GEMM (no counterpart in the reference).  dtas_gemm_nt_scatter computes
+ * Y = X.W^T (+ bias) exactly like dtas_gemm_nt and stores every finished 16-byte vector of Y a second
+ * time into each of the n_peers buffers in `peer_ys` (host array of device pointers, read during the
+ * call): buffers with Y's layout and row stride ldy - with Y's columns sharded over g GPUs, the place of
+ * this rank's slab in the other ranks' gather buffers, mapped into this process.  The stores leave from
+ * the epilogue of the two-CTA tcgen05 kernel, tile by tile, with plain st.global over NVLink, so the
+ * transfer is spread over the whole GEMM and over every SM instead of following the kernel; nothing
+ * waits on another rank or signals one, so the caller still runs one barrier across ranks before a
+ * gathered buffer is read.  Needs m >= 129, 16-byte aligned x and w and k a multiple of 8
+ * (DTAS_EUNSUPPORTED otherwise: use dtas_gemm_nt and dtas_peer_push); peer buffers that are not 16-byte
+ * aligned are written with scalar stores.  1 <= n_peers <= DTAS_MAX_PEERS.                          */
+int dtas_gemm_nt_scatter(const void* x, const void* w, const void* bias, void* y, void* const* peer_ys,
+                         int n_peers, int64_t m, int64_t n, int64_t k, int64_t ldy, int dtype, int device,
+                         void* stream);
+
 /* ---- bookkeeping ---------------------------------------------------------
  * dtas_last_error : message of the last failing call on this thread ("" if none).
  * dtas_launch_count: kernels launched by this library since load (all threads).

@@ -46,6 +46,23 @@ def _worker(rank, world, port, results):
                 want[:, lo:hi] = slab
             ops.poll_status(rank)
             ok[(m, n, k)] = bool(torch.equal(full, want))
+            # the gathered result against the fp32-accumulated CPU oracle (1e-2 relative + 1e-2 rms), and
+            # against ONE single-GPU call on the whole weight, which may pick another kernel variant and K
+            # order than the shards did: equal within the same bound, not necessarily bit for bit
+            import numpy as np
+            import oracle
+            from tests import util
+            ref = oracle.gemm_nt(x.cpu().numpy(), w.cpu().numpy()).astype(np.float32)
+            whole = torch.empty((m, n), dtype=torch.float16, device=dev)
+            (ops.gemv if m == 1 else ops.gemm_nt)(x, w, whole)
+            ops.poll_status(rank)
+            try:
+                util.assert_matmul_close(full.cpu().numpy(), ref, f"gathered m={m} n={n} k={k}")
+                util.assert_matmul_close(whole.cpu().numpy(), ref, f"single call m={m} n={n} k={k}")
+                ok[("oracle", m, n, k)] = True
+            except AssertionError as e:
+                ok[("oracle", m, n, k)] = False
+                print(e, flush=True)
         # fused tail through the sharded layer: bias + GELU + two residuals, against one single-GPU call
         for m in (1, 40):
             n, k = 2048, 1024
@@ -63,7 +80,7 @@ def _worker(rank, world, port, results):
             ok[("fused", m)] = err <= 2e-2 * want.float().abs().max().item()
         # the gather without a collective on the data: row blocks pushed into the peers' buffers
         from dtas_b200.dist import PeerGatherBuffer
-        for engine in ("kernel", "copy"):
+        for engine in ("kernel", "copy", "epilogue"):
             for (m, n, k, block) in [(1, 4096, 1024, 2048), (40, 2048, 1024, 2048), (2500, 2048, 512, 1024)]:
                 w = seeded_normal((n, k), 22, "float16", scale=0.02).to(dev)
                 b = seeded_normal((n,), 23, "float16", scale=0.5).to(dev)
@@ -78,6 +95,13 @@ def _worker(rank, world, port, results):
                     ops.poll_status(rank)
                     same = same and bool(torch.equal(got, want))
                 ok[("pushed", engine, m)] = same
+                if engine == "epilogue" and m >= 129:
+                    # without residuals the GEMM itself stores to the peers (one launch, one barrier)
+                    x = seeded_normal((m, k), 41, "float16").to(dev)
+                    want = lin.forward_gathered(x).clone()
+                    got = lin.forward_pushed(x, pbuf, min_push_bytes=0)
+                    ops.poll_status(rank)
+                    ok[("scattered", m)] = bool(torch.equal(got, want))
                 del pbuf
         a = seeded_normal((7, 11008), 3, "float16").to(dev)
         b = seeded_normal((7, 11008), 4, "float16").to(dev)

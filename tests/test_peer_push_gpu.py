@@ -55,3 +55,33 @@ def test_peer_push_argument_errors(cuda_device):
     assert lib.dtas_peer_push(src.data_ptr(), same, 1, 128, dev, None) == _abi.EINVAL
     with pytest.raises(_abi.DtasError):
         ops.peer_push(src, [dst])                       # another size
+
+
+@pytest.mark.parametrize("m,n,k,n_peers", [(129, 512, 1024, 1), (300, 1000, 2120, 3), (1024, 2752, 4096, 7), (2500, 520, 264, 2)])
+def test_gemm_scatter_writes_every_peer(cuda_device, m, n, k, n_peers):
+    """dtas_gemm_nt_scatter on one GPU: the peer buffers are ordinary buffers of the same device.  Y and
+    every peer copy hold the bits dtas_gemm_nt produces with the same kernel, column slabs of wider
+    buffers are respected, and rows too few for the two-CTA kernel are refused."""
+    from dtas_b200.reference import seeded_normal
+    x = seeded_normal((m, k), 501, "float16").to(cuda_device)
+    w = seeded_normal((n, k), 502, "float16", scale=0.02).to(cuda_device)
+    b = seeded_normal((n,), 503, "float16", scale=0.1).to(cuda_device)
+    want = torch.empty((m, n), dtype=torch.float16, device=cuda_device)
+    _abi.check(_abi.lib().dtas_gemm_set_override(512, 0))          # the kernel the scatter entry point uses
+    try:
+        ops.gemm_nt(x, w, want, bias=b)
+    finally:
+        _abi.check(_abi.lib().dtas_gemm_set_override(0, 0))
+    wide = [torch.full((m, n + 16), 7.0, dtype=torch.float16, device=cuda_device) for _ in range(n_peers + 1)]
+    views = [t[:, 8:8 + n] for t in wide]
+    ops.gemm_nt_scatter(x, w, views[0], views[1:], bias=b)
+    ops.poll_status()
+    ref = x.float() @ w.float().T + b.float()
+    rms = ref.double().pow(2).mean().sqrt().item()
+    assert (((want.float() - ref).abs() - (1e-2 * ref.abs() + 1e-2 * rms)).max().item()) <= 0
+    for t, v in zip(wide, views):
+        assert torch.equal(v, want)
+        assert bool((t[:, :8] == 7.0).all()) and bool((t[:, 8 + n:] == 7.0).all()), "wrote outside its column slab"
+    small = torch.empty((64, n), dtype=torch.float16, device=cuda_device)
+    with pytest.raises(_abi.DtasError):
+        ops.gemm_nt_scatter(x[:64], w, small, [torch.empty_like(small)])
