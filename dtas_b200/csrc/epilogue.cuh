@@ -237,13 +237,10 @@ __device__ __forceinline__ void epi_store_row32_plain(const __half* bias, __half
   }
 }
 
-// Finishes 32 consecutive output columns col0 .. col0+31 of one row held in acc32 (fp32 dot
-// products) and stores them.  vec_store: 16-byte stores into Y rows are aligned.  `pre`, when
-// given, holds the residual values of this chunk fetched earlier (epi_prefetch_res32).
-__device__ __forceinline__ void epi_store_row32(const Epilogue& e, void* y, int64_t ldy, int vec_store, int64_t row,
-                                                int col0, int n, float* acc32, const ResChunk* pre = nullptr,
-                                                const PeerOut* peers = nullptr) {
-  const int n_peers = peers != nullptr ? peers->n : 0;
+// The arithmetic of the tail on 32 consecutive columns of one row, in place: bias, activation,
+// residuals.  `pre`, when given, holds the residual values of this chunk fetched earlier.
+__device__ __forceinline__ void epi_apply_row32(const Epilogue& e, int64_t row, int col0, int n, float* acc32,
+                                                const ResChunk* pre = nullptr) {
   if (e.bias != nullptr) {
 #pragma unroll
     for (int j = 0; j < 32; ++j)
@@ -260,6 +257,51 @@ __device__ __forceinline__ void epi_store_row32(const Epilogue& e, void* y, int6
     if (e.res1 != nullptr) epi_add_res32(e.res1, row * e.ldr, col0, n, e.vec_res, acc32);
     if (e.res2 != nullptr) epi_add_res32(e.res2, row * e.ldr, col0, n, e.vec_res, acc32);
   }
+}
+// Eight fp32 values -> one 16-byte vector of fp16.
+__device__ __forceinline__ uint4 epi_pack8(const float* f) {
+  uint4 v;
+  __half2 h0 = __floats2half2_rn(f[0], f[1]);
+  __half2 h1 = __floats2half2_rn(f[2], f[3]);
+  __half2 h2 = __floats2half2_rn(f[4], f[5]);
+  __half2 h3 = __floats2half2_rn(f[6], f[7]);
+  v.x = *reinterpret_cast<uint32_t*>(&h0);
+  v.y = *reinterpret_cast<uint32_t*>(&h1);
+  v.z = *reinterpret_cast<uint32_t*>(&h2);
+  v.w = *reinterpret_cast<uint32_t*>(&h3);
+  return v;
+}
+// Row-contiguous stores of a block of 32 rows x (8 * CPR) fp16 columns that the 32 lanes of a warp
+// (lane = row) have parked in shared memory as 16-byte vectors at stage[row * CPR + (chunk ^ (row & 7))]:
+// every store instruction of the warp now writes 32 / CPR whole rows of 16 * CPR contiguous bytes (full
+// 128-byte lines), to Y and to every further copy of Y.  Both the parking writes (a quarter warp = 8
+// rows, one chunk) and these reads (a quarter warp = 8 chunks of a row) cover all 32 banks.
+template <int CPR>
+__device__ __forceinline__ void epi_store_staged_block(const uint4* stage, int lane, int64_t row_base, int m, void* y,
+                                                       int64_t ldy, int col0, const PeerOut& peers) {
+  constexpr int kRowsPerInstr = 32 / CPR;
+  const int ch = lane % CPR;
+#pragma unroll 4
+  for (int it = 0; it < CPR; ++it) {
+    const int rl = kRowsPerInstr * it + lane / CPR;
+    const int64_t grow = row_base + rl;
+    if (grow < m) {
+      const uint4 v = stage[rl * CPR + (ch ^ (rl & 7))];
+      const int64_t off = grow * ldy + col0 + ch * 8;
+      *reinterpret_cast<uint4*>(static_cast<__half*>(y) + off) = v;
+      for (int p = 0; p < peers.n; ++p) *reinterpret_cast<uint4*>(static_cast<__half*>(peers.y[p]) + off) = v;
+    }
+  }
+}
+
+// Finishes 32 consecutive output columns col0 .. col0+31 of one row held in acc32 (fp32 dot
+// products) and stores them.  vec_store: 16-byte stores into Y rows are aligned.  `pre`, when
+// given, holds the residual values of this chunk fetched earlier (epi_prefetch_res32).
+__device__ __forceinline__ void epi_store_row32(const Epilogue& e, void* y, int64_t ldy, int vec_store, int64_t row,
+                                                int col0, int n, float* acc32, const ResChunk* pre = nullptr,
+                                                const PeerOut* peers = nullptr) {
+  const int n_peers = peers != nullptr ? peers->n : 0;
+  epi_apply_row32(e, row, col0, n, acc32, pre);
   const bool full = vec_store && col0 + 32 <= n;
   if (!e.out_f32) {
     __half* yrow = static_cast<__half*>(y) + row * ldy;

@@ -1292,33 +1292,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairMaxThreads, 1)
               for (int j = 0; j < 32; ++j)
                 r[j] = __float_as_uint(__uint_as_float(r[j]) + __half2float(a.epi.bias[colb + cc * 32 + j]));
             }
+            float f[32];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 v;
-              __half2 h0 = __floats2half2_rn(__uint_as_float(r[8 * q + 0]), __uint_as_float(r[8 * q + 1]));
-              __half2 h1 = __floats2half2_rn(__uint_as_float(r[8 * q + 2]), __uint_as_float(r[8 * q + 3]));
-              __half2 h2 = __floats2half2_rn(__uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5]));
-              __half2 h3 = __floats2half2_rn(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7]));
-              v.x = *reinterpret_cast<uint32_t*>(&h0);
-              v.y = *reinterpret_cast<uint32_t*>(&h1);
-              v.z = *reinterpret_cast<uint32_t*>(&h2);
-              v.w = *reinterpret_cast<uint32_t*>(&h3);
-              stage[lane * 16 + ((cc * 4 + q) ^ (lane & 7))] = v;
-            }
+            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) stage[lane * 16 + ((cc * 4 + q) ^ (lane & 7))] = epi_pack8(f + 8 * q);
           }
           __syncwarp();
-          const int ch = lane & 15;
-#pragma unroll 4
-          for (int it = 0; it < 16; ++it) {
-            const int rl = 2 * it + (lane >> 4);
-            const int64_t grow = row_base + rl;
-            if (grow < a.m) {
-              const uint4 v = stage[rl * 16 + (ch ^ (rl & 7))];
-              const int64_t off = grow * a.ldy + colb + ch * 8;
-              *reinterpret_cast<uint4*>(static_cast<__half*>(a.y) + off) = v;
-              for (int p = 0; p < a.peers.n; ++p) *reinterpret_cast<uint4*>(static_cast<__half*>(a.peers.y[p]) + off) = v;
-            }
-          }
+          epi_store_staged_block<16>(stage, lane, row_base, a.m, a.y, a.ldy, colb, a.peers);
           __syncwarp();
         }
       } else {
@@ -1336,10 +1317,24 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairMaxThreads, 1)
         r_next = r_after;
         if (row_ok && c + 2 < c_end && epi_can_prefetch(a.epi, col0 + 64, a.n)) epi_prefetch_res32(a.epi, row, col0 + 64, r_after);
         tmem_ld_wait();
-        if (row_ok && col0 < a.n) {
-          float f[32];
+        // fp16 results go through shared memory in blocks of 64 columns (two chunks) and leave as whole
+        // 128-byte rows; an fp32 output, ragged edges and unaligned buffers are stored from the registers
+        const int blk0 = col_base + (c & ~1) * 32;
+        const bool staged_f = DTAS_PAIR_STAGED_STORE && a.vec_store && !a.epi.out_f32 && blk0 + 64 <= a.n && (c | 1) < c_end;
+        float f[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
+        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
+        if (staged_f) {
+          uint4* stage_f = reinterpret_cast<uint4*>(gen_base + (store_stage - base)) + (warp - 2) * (32 * 8);
+          if (row_ok) epi_apply_row32(a.epi, row, col0, a.n, f, epi_can_prefetch(a.epi, col0, a.n) ? &r_now : nullptr);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) stage_f[lane * 8 + (((c & 1) * 4 + q) ^ (lane & 7))] = epi_pack8(f + 8 * q);
+          if (c & 1) {
+            __syncwarp();
+            epi_store_staged_block<8>(stage_f, lane, mt * 2 * BM + (int)rank * BM + quarter * 32, a.m, a.y, a.ldy, blk0, a.peers);
+            __syncwarp();
+          }
+        } else if (row_ok && col0 < a.n) {
           epi_store_row32(a.epi, a.y, a.ldy, a.vec_store, row, col0, a.n, f,
                           epi_can_prefetch(a.epi, col0, a.n) ? &r_now : nullptr, &a.peers);
         }
