@@ -40,12 +40,20 @@ class PackedOp:
         self.entry = entry
         self.spec = OpSpec.from_dict(entry["spec"])
 
-    def bucket_index(self, m):
-        """Position in the merged range list that serves row count m (clamped above the bound)."""
+    def bucket_index(self, m, m2=None):
+        """Position in the range list that serves the symbolic dim(s): m, and m2 for a function with two
+        (each clamped above its bound)."""
         table = self.entry["index_table"]
         if not table:
             return 0
         width = self.entry["range_div_factor"]
+        if len(self.entry.get("dynamic_args", [])) == 2:
+            starts = sorted({r["start"][1] for r in self.entry["ranges"]})
+            n1 = len(starts)
+            n0 = len(table) // n1
+            i0 = min((m - 1) // width, n0 - 1)
+            i1 = min(((m2 if m2 is not None else 1) - 1) // width, n1 - 1)
+            return table[i0 * n1 + i1]
         return table[min((m - 1) // width, len(table) - 1)]
 
     def _expect(self, t, dtype, cols, what):

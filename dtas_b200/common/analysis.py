@@ -216,6 +216,10 @@ class FuncInfo:
         else:
             self.spec = spec_from_prim_func(func, name)
             self.dynamic_args = self._dynamic_args(func)
+        # for each dynamic argument: "rows" (it multiplies the row count) or "cols" (it is the reduced,
+        # innermost dim, as in a softmax over a symbolic length)
+        self.dynamic_roles = self._dynamic_roles(func) if not isinstance(func, (OpSpec, dict)) else ["rows"] * len(self.dynamic_args)
+        self.static_rows = self._static_rows(func) if not isinstance(func, (OpSpec, dict)) else 1
         self.kind = _KIND_OF[self.spec.kind]
         self.use_fp16 = "float16" in (self.spec.in_dtype, self.spec.out_dtype)
         self.in_dtype = self.spec.in_dtype
@@ -234,6 +238,26 @@ class FuncInfo:
                     else:
                         raise UnsupportedWorkload("at most two dynamic shape dimensions are supported")
         return [getattr(d, "name", str(d)) for d in dyn]
+
+    def _dynamic_roles(self, func):
+        first = func.buffer_map[[p for p in func.params if p in func.buffer_map][0]]
+        last = first.shape[-1]
+        roles = []
+        for name in self.dynamic_args:
+            is_last = _static(last) is None and getattr(last, "name", str(last)) == name
+            roles.append("cols" if is_last else "rows")
+        return roles
+
+    @staticmethod
+    def _static_rows(func):
+        """Product of the static dims of the first input that are not its innermost one."""
+        first = func.buffer_map[[p for p in func.params if p in func.buffer_map][0]]
+        rows = 1
+        for d in first.shape[:-1]:
+            v = _static(d)
+            if v is not None:
+                rows *= v
+        return rows
 
     def __repr__(self):
         return f'FuncInfo("{self.name}", {self.kind.name}, {self.spec})'

@@ -68,21 +68,19 @@ class Engine:
 
     # -- ranges ----------------------------------------------------------------------------
     def gen_range_tuples(self, func_info: FuncInfo, range_div_factor: int):
+        """One tuple of Ranges per bucket: the cartesian product of the range lists of up to two symbolic
+        dims, the first dim slowest (python/dtas/engine/tuner.py:135-154)."""
         if len(func_info.dynamic_args) == 0:
             return [()]
+        import itertools
         range_lists = []
-        dyn_args = func_info.dynamic_args
-        if func_info.spec.op == "softmax" and func_info.spec.cols == 0:
-            # rows and reduction length are both symbolic: the table is keyed on the row-like dim, the
-            # kernel reads the reduction length from the tensor and picks its layout per call
-            dyn_args = dyn_args[:1]
-        for dyn in dyn_args:
+        for dyn in func_info.dynamic_args:
             upper = func_info.spec.upper or self.upper_bound.get(dyn) or DEFAULT_UPPER_BOUND
             self.upper_bound[dyn] = upper
             range_lists.append(generate_range_list(dyn, 1, upper, range_div_factor))
-        if len(range_lists) > 1:
-            raise UnsupportedWorkload("kernels of this library take one symbolic dim (the row count)")
-        return [(r,) for r in range_lists[0]]
+        if len(range_lists) > 2:
+            raise UnsupportedWorkload("at most two symbolic dims are supported")
+        return [tuple(rt) for rt in itertools.product(*range_lists)]
 
     @staticmethod
     def merge_same_configs(range_to_config: Dict[Tuple[Range], Config]) -> Dict[Tuple[Range], Config]:
@@ -97,17 +95,28 @@ class Engine:
         return dict(merged)
 
     def get_index_table(self, merged: Dict[Tuple[Range], Config], range_div_factor: int):
-        """index_table[i] = position in `merged` of the config serving bucket i, plus the
-        statement that computes the bucket index from the dynamic dim (tuner.py:156-209)."""
+        """index_table[i] = position in `merged` of the config serving bucket i, plus the statement(s)
+        that compute the bucket index from the dynamic dim(s) (tuner.py:156-209).  With two symbolic dims
+        the table is row-major over (bucket of the first dim, bucket of the second)."""
         items = list(merged.items())
         if not items or len(items[0][0]) == 0:
             return [], ""
-        name = items[0][0][0].var
-        table = []
-        for i, (rt, _) in enumerate(items):
-            table += [i] * len(range(rt[0].start, rt[0].end + 1, range_div_factor))
-        last = len(table) - 1
-        stmt = f"int64_t index = (({name} - 1)/{range_div_factor}) > {last} ? {last} : ({name} - 1)/{range_div_factor};"
+        width = range_div_factor
+        if len(items[0][0]) == 1:
+            name = items[0][0][0].var
+            table = []
+            for i, (rt, _) in enumerate(items):
+                table += [i] * len(range(rt[0].start, rt[0].end + 1, width))
+            last = len(table) - 1
+            return table, f"int64_t index = (({name} - 1)/{width}) > {last} ? {last} : ({name} - 1)/{width};"
+        # two dims: nothing was merged, one entry per (bucket, bucket)
+        n0 = len({rt[0].start for rt, _ in items})
+        n1 = len({rt[1].start for rt, _ in items})
+        v0, v1 = items[0][0][0].var, items[0][0][1].var
+        table = list(range(len(items)))
+        stmt = (f"int64_t i0 = (({v0} - 1)/{width}) > {n0 - 1} ? {n0 - 1} : ({v0} - 1)/{width}; "
+                f"int64_t i1 = (({v1} - 1)/{width}) > {n1 - 1} ? {n1 - 1} : ({v1} - 1)/{width}; "
+                f"int64_t index = i0 * {n1} + i1;")
         return table, stmt
 
     # -- per function ------------------------------------------------------------------------
@@ -118,10 +127,15 @@ class Engine:
             debug_info(f"{name}: {info.kind.name} {spec}")
         range_to_config: Dict[Tuple[Range], Config] = {}
         for rt in self.gen_range_tuples(info, range_div_factor):
-            m = rt[0].end if rt else 1
-            # a softmax with a symbolic reduction length is described at a nominal length; the kernel
-            # picks its layout from the actual one at call time
-            variant = _abi.variant_of(spec.op, m, spec.cols or 1024, spec.k, getattr(arch, "dev_id", -1))
+            # the call shape at the upper end of the bucket: symbolic row dims multiply the static rows, a
+            # symbolic innermost dim (softmax over a symbolic length) is the row length
+            rows, cols = info.static_rows, spec.cols
+            for r, role in zip(rt, info.dynamic_roles):
+                if role == "cols":
+                    cols = r.end
+                else:
+                    rows *= r.end
+            variant = _abi.variant_of(spec.op, max(1, rows), cols or 1024, spec.k, getattr(arch, "dev_id", -1))
             range_to_config[rt] = config_for(spec.kind, variant)
         merged = self.merge_same_configs(range_to_config)
         table, stmt = self.get_index_table(merged, range_div_factor)
@@ -231,8 +245,11 @@ class Engine:
                 "kind": info.kind.name,
                 "dynamic_args": info.dynamic_args,
                 "range_div_factor": range_div_factor,
-                "ranges": [{"start": rt[0].start, "end": rt[0].end, "suffix": rt[0].to_suffix(),
-                            "config": cfg.to_dict()} if rt else {"config": cfg.to_dict()}
+                "ranges": [({"start": rt[0].start, "end": rt[0].end, "suffix": rt[0].to_suffix(), "config": cfg.to_dict()}
+                            if len(rt) == 1 else
+                            {"start": [r.start for r in rt], "end": [r.end for r in rt],
+                             "suffix": "_".join(r.to_suffix() for r in rt), "config": cfg.to_dict()})
+                           if rt else {"config": cfg.to_dict()}
                            for rt, cfg in merged.items()],
                 "index_table": table,
                 "index_stmt": stmt,

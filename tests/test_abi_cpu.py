@@ -62,7 +62,7 @@ def test_variant_names(lib):
     assert _abi.variant_of("gemv", 1, 4096, 11008) == "gemv_stream_s8_rows1"
     assert _abi.variant_of("gemv", 1, 512, 4096).startswith("gemv_vec16")          # 4 MB: the per-row kernel
     assert _abi.variant_of("gemv", 1, 4096, 16384).startswith("gemv_vec16")        # a row does not fit a stage
-    assert _abi.variant_of("gemm", 8192, 22016, 4096) == "gemm_tcgen05_2cta_bm256_bn256_bk64_s7"
+    assert _abi.variant_of("gemm", 8192, 22016, 4096) == "gemm_tcgen05_2cta_bm256_bn256_bk64_s6"
     assert _abi.variant_of("gemm", 16, 22016, 4096).startswith("gemm_tcgen05_swap_n128_m16")
     assert _abi.variant_of("gemm", 255, 22016, 4096).startswith("gemm_tcgen05_bm128_bn")
     assert _abi.variant_of("gemm", 33, 70, 101) == "gemm_simt_fallback"

@@ -162,3 +162,15 @@ def test_classification_of_softmax_with_two_symbolic_dims():
     rt = Engine(1, True, None).tune_module(td.make_module({"attn_softmax": td.softmax_dynamic(32, "float32")}, upper_bound=2048),
                                            arch=arch.B200(0), range_div_factor=256)
     assert rt["attn_softmax"].spec.cols == 0
+    # the range table is the cartesian product of the two dims' ranges, first dim slowest, as the
+    # reference builds it (python/dtas/engine/tuner.py:135-154): 8 x 8 buckets of 256 up to 2048
+    ent = rt.record["functions"]["attn_softmax"]
+    assert info.dynamic_roles == ["rows", "cols"] and info.static_rows == 32
+    assert len(ent["ranges"]) == 64 and ent["index_table"] == list(range(64))
+    assert ent["ranges"][0]["start"] == [1, 1] and ent["ranges"][0]["end"] == [256, 256]
+    assert ent["ranges"][9]["start"] == [257, 257] and ent["ranges"][63]["end"] == [2048, 2048]
+    assert "i0 * 8 + i1" in ent["index_stmt"]
+    op = rt["attn_softmax"]
+    assert op.bucket_index(1, 1) == 0 and op.bucket_index(257, 300) == 9 and op.bucket_index(10 ** 6, 10 ** 6) == 63
+    # the kernel layout follows the reduction length of the bucket, not a nominal one
+    assert ent["ranges"][0]["config"] != ent["ranges"][7]["config"]
