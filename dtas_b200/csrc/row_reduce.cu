@@ -11,8 +11,6 @@
 // memory hop when TPR > 32) and writes 16-byte fp16 vectors.  HBM sees each element
 // once in and once out: algorithmic bytes 4*n_cols per row for fp16 in/out
 // (+ 2*n_cols once for the RMSNorm weight).  Bound: HBM bandwidth.
-#include <stdlib.h>
-
 #include "common.cuh"
 
 namespace dtas {
@@ -126,18 +124,14 @@ __global__ void __launch_bounds__(TPR > kCtaThreads ? TPR : kCtaThreads)
   __shared__ float scratch_b[kThreads / 32];
 
   const int t = threadIdx.x % TPR;
+  const int64_t row = (int64_t)blockIdx.x * kRowsPerCta + threadIdx.x / TPR;
+  const bool live = row < m;
   const int n_chunks = n_cols >> 3;
+  const InT* xr = x + (live ? row : 0) * (int64_t)n_cols;
+  __half* yr = y + (live ? row : 0) * (int64_t)n_cols;
 
   pdl_wait();
   pdl_launch_dependents();
-  // Rows are dealt to the CTAs round-robin; with one CTA per group of rows (the default grid) the
-  // loop runs once.  Every thread of a CTA makes the same number of trips (the reductions
-  // synchronise the CTA), rows at or beyond m are computed on neutral values and not stored.
-  for (int64_t row0 = (int64_t)blockIdx.x * kRowsPerCta; row0 < m; row0 += (int64_t)gridDim.x * kRowsPerCta) {
-  const int64_t row = row0 + threadIdx.x / TPR;
-  const bool live = row < m;
-  const InT* xr = x + (live ? row : 0) * (int64_t)n_cols;
-  __half* yr = y + (live ? row : 0) * (int64_t)n_cols;
   RawChunk<InT> raw[MAXCH];
 #pragma unroll
   for (int c = 0; c < MAXCH; ++c) {
@@ -261,8 +255,6 @@ __global__ void __launch_bounds__(TPR > kCtaThreads ? TPR : kCtaThreads)
         store_chunk(yr, ch, o);
       }
     }
-  }
-  if constexpr (TPR > 32) __syncthreads();   // the reduction scratch is reused by the next trip
   }
 }
 
@@ -497,10 +489,8 @@ int launch_regs(const InT* x, const void* p0, const void* p1, __half* y, int64_t
                 float eps, cudaStream_t st) {
   constexpr int kThreads = TPR > kCtaThreads ? TPR : kCtaThreads;
   constexpr int kRowsPerCta = kThreads / TPR;
-  int64_t grid = (m + kRowsPerCta - 1) / kRowsPerCta;
+  const int64_t grid = (m + kRowsPerCta - 1) / kRowsPerCta;
   if (grid > 0x7fffffffLL) DTAS_FAIL(DTAS_EINVAL, "row op: too many rows (%lld)", (long long)m);
-  static const int cap = [] { const char* e = getenv("DTAS_B200_ROW_CTAS"); return e ? atoi(e) : 0; }();
-  if (cap > 0 && grid > cap) grid = cap;
   launch_kernel(row_regs_kernel<OP, InT, TPR, MAXCH>, (unsigned)grid, kThreads, 0, st, x, p0, p1, y, m, n_cols, eps);
   return after_launch("row_regs_kernel");
 }
