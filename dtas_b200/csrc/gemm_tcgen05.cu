@@ -206,7 +206,6 @@ struct GemmArgs {
   int sk_per = 0;     // > 0: stream-K, every CTA owns sk_per consecutive (tile, k-block) units
   int slots_cap = 0;  // partial-tile slots reserved per output tile in the workspace
   PeerOut peers;      // two-CTA kernel: further buffers that receive every stored vector of Y
-  const __half* x = nullptr;   // X itself, for kernels that fetch X tiles with cp.async instead of TMA
 };
 
 template <int BN>
@@ -1381,9 +1380,6 @@ struct K2Cfg {
   static_assert(kSmemBytes <= 227 * 1024 && kStages >= 3, "smem");
 };
 constexpr int ERR_K2_DATA = 0x106;
-#ifndef DTAS_K2_X_CPASYNC
-#define DTAS_K2_X_CPASYNC 0     // 1: X tiles by cp.async from the epilogue warps (experimental, A/B timing)
-#endif
 
 __device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t cta) {
   uint32_t r;
@@ -1432,7 +1428,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_x)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w)) : "memory");
     for (int s = 0; s < C::kStages; ++s) {
-      mbar_init(full_bar(s), DTAS_K2_X_CPASYNC ? 1 + kEpilogueThreads : 1);   // the W copy + every thread that fetches X
+      mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
     mbar_init(tfull_bar, 1);
@@ -1458,13 +1454,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       uint32_t phase = 0;
       for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait(empty_bar(stage), phase ^ 1u, a.status, ERR_PRODUCER)) break;
+        mbar_expect_tx(full_bar(stage), C::kStageBytes);
         const uint32_t sa = base + stage * C::kStageBytes;
-        if (DTAS_K2_X_CPASYNC) {
-          mbar_expect_tx(full_bar(stage), C::kBBytes);
-        } else {
-          mbar_expect_tx(full_bar(stage), C::kStageBytes);
-          tma_load_2d(sa, &tmap_x, kb * BK, mt * BM, full_bar(stage));
-        }
+        tma_load_2d(sa, &tmap_x, kb * BK, mt * BM, full_bar(stage));
         tma_load_2d(sa + C::kABytes, &tmap_w, kb * BK, nt * BN, full_bar(stage));
         if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
       }
@@ -1478,7 +1470,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       bool ok = true;
       for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait(full_bar(stage), phase, a.status, ERR_MMA_FULL)) { ok = false; break; }
-        if (DTAS_K2_X_CPASYNC) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // X was written by cp.async
         tc_fence_after();
         const uint32_t sa = base + stage * C::kStageBytes;
         const uint64_t da = make_kmajor_sw128_desc(sa);
@@ -1500,33 +1491,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     const bool row_ok = row < a.m;
     const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const int col_base = nt * BN;
-    if (DTAS_K2_X_CPASYNC) {
-      // While the main loop runs these four warps have nothing to do, and the TMA stream of an SM moves no
-      // more than ~55 GB/s when W comes from HBM - X bytes that travel with it cost as much as W bytes.
-      // So they fetch the X tile of every k-block themselves: 128 rows x 128 bytes = 1024 16-byte chunks,
-      // eight per thread, with cp.async into the 128-byte-swizzled layout the MMA descriptor expects
-      // (chunk c of row r at r * 128 + ((c ^ (r & 7)) * 16); rows at or beyond m are zero-filled), and
-      // each thread's copies arrive on the stage's barrier when they have landed.
-      int stage = 0;
-      uint32_t phase = 0;
-      const __half* xbase = a.x + (int64_t)(mt * BM) * a.k;
-      for (int kb = kb0; kb < kb1; ++kb) {
-        if (!mbar_wait(empty_bar(stage), phase ^ 1u, a.status, ERR_PRODUCER)) break;
-        const uint32_t sa = base + stage * C::kStageBytes;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int id = epi_tid + i * kEpilogueThreads;
-          const int r = id >> 3, c = id & 7;
-          const int kcol = kb * BK + c * 8;
-          const bool on = (mt * BM + r) < a.m && kcol < a.k;
-          const __half* src = on ? xbase + (int64_t)r * a.k + kcol : a.x;
-          const uint32_t dst = sa + (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4));
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(on ? 16 : 0) : "memory");
-        }
-        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(full_bar(stage)) : "memory");
-        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
-      }
-    }
     bool ok = mbar_wait(tfull_bar, 0u, a.status, ERR_EPILOGUE);
     tc_fence_after();
     if (rank == 1) {
@@ -2521,7 +2485,6 @@ int launch_gemm(const void* x, const void* w, const Epilogue& epi, void* y, int6
 
   GemmArgs a;
   a.y = y;
-  a.x = static_cast<const __half*>(x);
   a.epi = epi;
   a.ws = ws;
   a.counters = counters;
