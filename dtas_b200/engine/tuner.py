@@ -152,14 +152,16 @@ class Engine:
         cands = []
         if m_hi <= 256:
             cands += [(1024, s) for s in (1, 2, 3, 4, 6, 8, 12, 16)] + [(2048, 0)]
-            cands += [(bn, s) for bn in (64, 128, 256) for s in (1, 2, 4)] + [(4096 + bn, 0) for bn in (64, 128)]
+            cands += [(bn, s) for bn in (64, 128, 256) for s in (1, 2, 4)] + [(bn, s) for bn in (64, 128) for s in (8, 16)]
+            cands += [(4096 + bn, 0) for bn in (64, 128)]
             cands += [(8192 + 64, 0), (8192 + 128, 0)]
             if m_hi > 128:
                 cands += [(512, 1), (513, 1)]     # a 256-row tile is at least half full
             if m_hi <= 64:
                 cands += [(16384 + s, 0) for s in (2, 3, 4)]
         elif m_hi <= 1024:
-            cands += [(bn, s) for bn in (128, 256) for s in (1, 2)] + [(512, 1), (513, 1), (4096 + 128, 0), (4096 + 256, 0), (8192 + 64, 0), (8192 + 128, 0)]
+            cands += [(bn, s) for bn in (128, 256) for s in (1, 2)] + [(64, s) for s in (1, 2, 4, 8)] + [(128, 4), (128, 8)]
+            cands += [(512, 1), (513, 1), (4096 + 64, 0), (4096 + 128, 0), (4096 + 256, 0), (8192 + 64, 0), (8192 + 128, 0)]
         else:
             # above 1024 rows the two-CTA kernel wins whenever its 256 x 256 tiles fill the SM pairs; on
             # narrow column shards they do not (m = 4096, N = 512: 32 tiles on 74 pairs), and single-CTA
