@@ -371,12 +371,21 @@ def gather_points(rank, world, dev, barrier):
                 continue
             pbuf = PeerGatherBuffer(world, m, n_local, f16, dev, engine=engine)
             pushed[engine] = timed(lambda i: lins[i % copies].forward_pushed(x, pbuf, min_push_bytes=0))
+            if engine == "epilogue":
+                # what arrived in the peers' slots of this rank's buffer is what an all-gather delivers
+                want = lins[0].forward_gathered(x).clone()
+                got = lins[0].forward_pushed(x, pbuf, min_push_bytes=0)
+                torch.cuda.synchronize()
+                flag = torch.tensor([int(torch.equal(got, want))], device=dev, dtype=torch.int32)
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                pushed["epilogue_equals_all_gather"] = bool(flag.item())
             del pbuf
         out.append({"op": op, "m": m, "n": n, "k": k, "kernel_us": round(local_us, 2),
                     "kernel_plus_all_gather_us": round(gathered_us, 2),
                     "kernel_plus_peer_push_us": round(pushed["kernel"], 2),
                     "kernel_plus_copy_engine_push_us": round(pushed["copy"], 2),
                     "gemm_storing_to_peers_us": None if pushed["epilogue"] is None else round(pushed["epilogue"], 2),
+                    "gemm_storing_to_peers_equals_all_gather": pushed.get("epilogue_equals_all_gather"),
                     "gather_bytes_per_rank": 2 * m * n_local, "mode": "eager calls, max over ranks"})
         del lins, buf, x
         torch.cuda.empty_cache()
@@ -559,7 +568,12 @@ def run_gpu(args):
                 dominant = ((op, m_local, n_local, k), t)
         torch.cuda.empty_cache()
     fused = fused_points(dev, peaks) if (per_point and world == 1) else None
-    gathered = gather_points(rank, world, dev, barrier) if (world > 1 and not args.no_points) else None
+    gathered = None
+    if world > 1 and not args.no_points:
+        try:
+            gathered = gather_points(rank, world, dev, barrier)
+        except Exception as e:  # noqa: BLE001 - the extras are reported, never allowed to cost the bench line
+            gathered = [{"error": f"{type(e).__name__}: {e}"[:300]}]
     roofline = None
     if dominant is not None:
         (op, m, n, k), t = dominant
