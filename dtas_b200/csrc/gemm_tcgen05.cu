@@ -216,7 +216,10 @@ struct Cfg {
   static constexpr int kStages = kStageBudget / kStageBytes;
   static constexpr int kTmemCols = 2 * BN;  // two accumulators
   static constexpr int kBarBytes = (2 * kStages + 4) * 8 + 16;
-  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kBarBytes;
+  // per epilogue warp 32 rows x min(BN, 128) fp16 columns, staged for row-contiguous stores
+  static constexpr int kStoreCpr = BN >= 128 ? 16 : 8;            // 16-byte chunks per staged row
+  static constexpr int kStoreStage = 4 * 32 * kStoreCpr * 16;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kStoreStage + kBarBytes;
   static_assert(kTmemCols >= 32 && kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "tmem");
   static_assert(kSmemBytes <= 227 * 1024, "smem");
 };
@@ -289,7 +292,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzle atoms need 1024 B
-  const uint32_t bars = base + C::kStages * C::kStageBytes;
+  const uint32_t store_stage = base + C::kStages * C::kStageBytes;
+  const uint32_t bars = store_stage + C::kStoreStage;
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (C::kStages + s); };
   auto tfull_bar = [&](int i) { return bars + 8u * (2 * C::kStages + i); };
@@ -298,7 +302,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const uint32_t last_flag = tmem_slot + 4;
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
   volatile uint32_t* tmem_slot_ptr =
-      reinterpret_cast<volatile uint32_t*>(gen_base + C::kStages * C::kStageBytes + 8 * (2 * C::kStages + 4));
+      reinterpret_cast<volatile uint32_t*>(gen_base + C::kStages * C::kStageBytes + C::kStoreStage + 8 * (2 * C::kStages + 4));
   volatile uint32_t* last_flag_ptr = tmem_slot_ptr + 1;
   (void)last_flag;
 
@@ -411,13 +415,43 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       if (n_parts == 1) {
         if (epi_is_plain(a.epi)) {
           __half* yrow = static_cast<__half*>(a.y) + (int64_t)row * a.ldy;
+          // blocks of 8 * kStoreCpr columns go through shared memory and leave as whole rows of 128 or 256
+          // contiguous bytes (see epi_store_staged_block); ragged edges and unaligned Y from the registers
+          constexpr int kCpr = C::kStoreCpr, kBlk = kCpr / 4;          // 32-column chunks per staged block
+          uint4* stage = reinterpret_cast<uint4*>(gen_base + (store_stage - base)) + (warp - 2) * (32 * kCpr);
+          const PeerOut no_peers;
 #pragma unroll 1
-          for (int c = 0; c < BN / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld32(t_addr + c * 32, r);
-            tmem_ld_wait();
-            const int col0 = col_base + c * 32;
-            if (row_ok && col0 < a.n) epi_store_row32_plain(a.epi.bias, yrow, a.vec_store, col0, a.n, r);
+          for (int c = 0; c < BN / 32; c += kBlk) {
+            const int colb = col_base + c * 32;
+            if (!(a.vec_store && colb + 8 * kCpr <= a.n)) {
+#pragma unroll 1
+              for (int cc = c; cc < c + kBlk; ++cc) {
+                uint32_t r[32];
+                tmem_ld32(t_addr + cc * 32, r);
+                tmem_ld_wait();
+                const int col0 = col_base + cc * 32;
+                if (row_ok && col0 < a.n) epi_store_row32_plain(a.epi.bias, yrow, a.vec_store, col0, a.n, r);
+              }
+              continue;
+            }
+#pragma unroll 1
+            for (int cc = 0; cc < kBlk; ++cc) {
+              uint32_t r[32];
+              tmem_ld32(t_addr + (c + cc) * 32, r);
+              tmem_ld_wait();
+              float f[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
+              if (a.epi.bias != nullptr) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) f[j] += __half2float(a.epi.bias[colb + cc * 32 + j]);
+              }
+#pragma unroll
+              for (int q = 0; q < 4; ++q) stage[lane * kCpr + ((cc * 4 + q) ^ (lane & 7))] = epi_pack8(f + 8 * q);
+            }
+            __syncwarp();
+            epi_store_staged_block<kCpr>(stage, lane, mt * BM + quarter * 32, a.m, a.y, a.ldy, colb, no_peers);
+            __syncwarp();
           }
         } else {
         // Residual rows are fetched two chunks ahead of their use, so that their latency is not
