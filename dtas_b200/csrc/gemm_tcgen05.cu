@@ -204,6 +204,7 @@ struct GemmArgs {
   int m_tiles, n_tiles, splits, kb_per_split, num_kb;
   int vec_store;      // 1 when 16-byte stores into Y are aligned
   int sk_per = 0;     // > 0: stream-K, every CTA owns sk_per consecutive (tile, k-block) units
+  int sk_first = 0;   // two-CTA kernel, stream-K: first tile of the region that is cut into runs of units
   int slots_cap = 0;  // partial-tile slots reserved per output tile in the workspace
   PeerOut peers;      // two-CTA kernel: further buffers that receive every stored vector of Y
 };
@@ -1011,11 +1012,14 @@ __device__ __forceinline__ void decode_pair_work(int w, int m_tiles, int n_tiles
 // a.m_tiles / a.n_tiles count 256 x 256 tiles here; a.splits must be 1.
 // The work of a CTA pair as a sequence of segments: k-blocks [kb0, kb1) of tile `tile`, being
 // contribution `slot` of `count` to it.  Whole tiles are dealt round-robin to the pairs; with stream-K
-// (a.sk_per > 0) the tiles of the last, partial wave are instead cut, as (tile, k-block) units in
-// tile-major order, into equal consecutive runs of a.sk_per units, one per pair, so that the wave ends
-// for all pairs together whatever the tile count (32 tiles on 74 pairs: 28 k-blocks each instead of 64
-// on fewer than half the pairs).  A tile whose units fall to several pairs is finished through the
-// workspace.
+// (a.sk_per > 0) the tiles from a.sk_first on - the last, partial wave - are instead cut, as
+// (tile, k-block) units in tile-major order, into equal consecutive runs of a.sk_per units, one per
+// pair, so that the wave ends for all pairs together whatever the tile count (32 tiles on 74 pairs: 28
+// k-blocks each instead of 64 on fewer than half the pairs).  A tile whose units fall to several pairs
+// is finished through the workspace.  (Taking the whole wave before the last into the region as well,
+// so that a run is longer than a tile and a tile has two contributors instead of up to six, was
+// measured: 57 against 67 us at m = 255, N = 22016 - still behind the 55 us of whole tiles - and 1-4 %
+// slower from m = 1024 up, where more tiles then pay for the workspace.)
 struct PairSeg {
   int mt, nt, tile, kb0, kb1, slot, count, first;
 };
@@ -1031,8 +1035,8 @@ struct PairIter {
     tail_first = tiles;
     if (a.sk_per > 0) {
       // whole waves of tiles are dealt round-robin (pairs running side by side share X and W tiles in
-      // L2); only the tiles of the last, partial wave are cut into equal runs of k-blocks
-      end = tail_first = (tiles / n_pairs) * n_pairs;
+      // L2); the tiles from a.sk_first on are cut into equal runs of k-blocks
+      end = tail_first = a.sk_first;
       const int units = (tiles - tail_first) * a.num_kb;
       spos = min(pair * a.sk_per, units);
       send = min(spos + a.sk_per, units);
@@ -1237,9 +1241,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairMaxThreads, 1)
                                                    __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
           }
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(tempty_bar(acc), 0);   // tensor memory no longer needed for this tile
         __threadfence();
         epilogue_bar_sync_n(n_epi_threads);
         if (epi_tid == 0) {
@@ -1253,42 +1254,56 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairMaxThreads, 1)
         const bool is_last = *last_flag_ptr != 0;
         epilogue_bar_sync_n(n_epi_threads);     // flag consumed before a later tile rewrites it
         if (is_last) {
+          // The other contributions come back from the workspace; this CTA's own is still in tensor
+          // memory and is added from there at its place in the K order (the same values and the same
+          // sequence of additions whichever contributor happens to arrive last).
           __threadfence();
-          if (row_ok) {
-            const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+          const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 1
-            for (int c = c_begin; c < c_end; ++c) {
-              const int col0 = col_base + c * 32;
-              if (col0 >= a.n) break;
-              const int live4 = min(8, (a.n - col0 + 3) >> 2);
-              float f[32];
+          for (int c = c_begin; c < c_end; ++c) {
+            const int col0 = col_base + c * 32;
+            if (col0 >= a.n) break;
+            const int live4 = row_ok ? min(8, (a.n - col0 + 3) >> 2) : 0;
+            float f[32];
 #pragma unroll
-              for (int j = 0; j < 32; ++j) f[j] = 0.f;
+            for (int j = 0; j < 32; ++j) f[j] = 0.f;
 #pragma unroll 1
-              for (int sb = 0; sb < sg.count; sb += 2) {
-                const bool two = sb + 1 < sg.count;
-                const float4* s0 = ws4 + area_of(sg.first + sb) + (int64_t)c * 8 * BM;
-                const float4* s1 = ws4 + area_of(sg.first + (two ? sb + 1 : sb)) + (int64_t)c * 8 * BM;
-                float4 v0[8], v1[8];
+            for (int sb = 0; sb < sg.count; sb += 2) {
+              const bool two = sb + 1 < sg.count;
+              const bool own0 = sb == sg.slot, own1 = two && sb + 1 == sg.slot;
+              const float4* s0 = ws4 + area_of(sg.first + sb) + (int64_t)c * 8 * BM;
+              const float4* s1 = ws4 + area_of(sg.first + (two ? sb + 1 : sb)) + (int64_t)c * 8 * BM;
+              uint32_t v0[32], v1[32];
 #pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                  const bool on = q < live4;
-                  v0[q] = on ? __ldcg(s0 + q * BM) : zero4;
-                  v1[q] = (on && two) ? __ldcg(s1 + q * BM) : zero4;
-                }
-#pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                  f[4 * q] += v0[q].x; f[4 * q + 1] += v0[q].y; f[4 * q + 2] += v0[q].z; f[4 * q + 3] += v0[q].w;
-                }
-#pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                  f[4 * q] += v1[q].x; f[4 * q + 1] += v1[q].y; f[4 * q + 2] += v1[q].z; f[4 * q + 3] += v1[q].w;
-                }
+              for (int q = 0; q < 8; ++q) {
+                const bool on = q < live4;
+                const float4 t0 = (on && !own0) ? __ldcg(s0 + q * BM) : zero4;
+                const float4 t1 = (on && two && !own1) ? __ldcg(s1 + q * BM) : zero4;
+                v0[4 * q] = __float_as_uint(t0.x); v0[4 * q + 1] = __float_as_uint(t0.y);
+                v0[4 * q + 2] = __float_as_uint(t0.z); v0[4 * q + 3] = __float_as_uint(t0.w);
+                v1[4 * q] = __float_as_uint(t1.x); v1[4 * q + 1] = __float_as_uint(t1.y);
+                v1[4 * q + 2] = __float_as_uint(t1.z); v1[4 * q + 3] = __float_as_uint(t1.w);
               }
-              epi_store_row32(a.epi, a.y, a.ldy, a.vec_store, row, col0, a.n, f, nullptr, &a.peers);
+              if (own0) {                    // the same for the whole warp
+                tmem_ld32(t_addr + c * 32, v0);
+                tmem_ld_wait();
+              } else if (own1) {
+                tmem_ld32(t_addr + c * 32, v1);
+                tmem_ld_wait();
+              }
+#pragma unroll
+              for (int j = 0; j < 32; ++j) f[j] += __uint_as_float(v0[j]);
+              if (two) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) f[j] += __uint_as_float(v1[j]);
+              }
             }
+            if (row_ok) epi_store_row32(a.epi, a.y, a.ldy, a.vec_store, row, col0, a.n, f, nullptr, &a.peers);
           }
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(tempty_bar(acc), 0);   // tensor memory no longer needed for this tile
         continue;
       }
       if (epi_is_plain(a.epi)) {
@@ -2254,9 +2269,12 @@ int launch_pair(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a,
   int pairs = dev < 64 ? max_pairs[dev] : sm_count / 2;
   GemmArgs ap = a;
   ap.sk_per = 0;
+  ap.sk_first = total;
   const int tail = total % pairs;       // tiles of the last, partial wave
   if (stream_k && tail > 0) {
-    const int64_t units = (int64_t)tail * a.num_kb;
+    const int region = tail;
+    const int64_t units = (int64_t)region * a.num_kb;
+    ap.sk_first = total - region;
     ap.sk_per = (int)((units + pairs - 1) / pairs);     // every pair takes part: the grid stays at `pairs`
   } else if (pairs > total) {
     pairs = total;

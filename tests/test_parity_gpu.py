@@ -362,11 +362,12 @@ def test_gemm_every_tile_width_and_split(cuda_device, bn, split):
 
 @pytest.mark.parametrize("code", [512, 513])
 @pytest.mark.parametrize("m,n,k", [(1024, 4096, 4096), (4096, 12288, 4096), (1000, 2752, 11008), (300, 520, 72),
-                                   (4096, 512, 4096), (200, 22016, 1024), (130, 1000, 2120)])
+                                   (4096, 512, 4096), (200, 22016, 1024), (130, 1000, 2120), (2304, 2304, 512),
+                                   (255, 22016, 4096)])
 def test_gemm_two_cta_kernel(cuda_device, m, n, k, code):
     """The cta_group::2 kernel (256 x 256 tiles on CTA pairs), forced, on full and ragged shapes: tiles
     dealt out whole (512) and with the last, partial wave cut stream-K fashion and finished through the
-    workspace (513; tile counts below, at and above the number of pairs)."""
+    workspace (513; tile counts below, just above (81, 86) and far above the number of pairs)."""
     x = seeded_normal((m, k), 97, "float16")
     w = seeded_normal((n, k), 98, "float16", scale=0.02)
     xd, wd = x.to(cuda_device), w.to(cuda_device)
