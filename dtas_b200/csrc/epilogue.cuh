@@ -170,6 +170,22 @@ __device__ __forceinline__ void epi_add_vec32(const uint4* v, float* acc32) {
   }
 }
 
+// bias[col0 .. col0 + 31] added to 32 fp32 values of one row.  Every lane reads the same addresses;
+// a whole chunk of an aligned bias comes in four 16-byte loads instead of 32 two-byte ones.
+__device__ __forceinline__ void epi_add_bias32(const __half* bias, int col0, int n, float* acc32) {
+  if (col0 + 32 <= n && (reinterpret_cast<uintptr_t>(bias + col0) & 15) == 0) {
+    const uint4* src = reinterpret_cast<const uint4*>(bias + col0);
+    uint4 v[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) v[q] = __ldg(src + q);
+    epi_add_vec32(v, acc32);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < n) acc32[j] += __half2float(bias[col0 + j]);
+  }
+}
+
 __device__ __forceinline__ void epi_add_res32(const __half* res, int64_t off, int col0, int n, int vec, float* acc32) {
   if (vec && col0 + 32 <= n) {
     const uint4* src = reinterpret_cast<const uint4*>(res + off + col0);
@@ -199,11 +215,7 @@ __device__ __forceinline__ bool epi_is_plain(const Epilogue& e) {
 // The plain tail for 32 consecutive columns of one row, from the raw accumulator words.
 __device__ __forceinline__ void epi_store_row32_plain(const __half* bias, __half* yrow, int vec_store, int col0, int n,
                                                       uint32_t* r, const PeerOut* peers = nullptr, int64_t row_off = 0) {
-  if (bias != nullptr) {
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (col0 + j < n) r[j] = __float_as_uint(__uint_as_float(r[j]) + __half2float(bias[col0 + j]));
-  }
+  if (bias != nullptr) epi_add_bias32(bias, col0, n, reinterpret_cast<float*>(r));
   const int n_peers = peers != nullptr ? peers->n : 0;
   if (vec_store && col0 + 32 <= n) {
     uint4 v[4];
@@ -241,14 +253,10 @@ __device__ __forceinline__ void epi_store_row32_plain(const __half* bias, __half
 // residuals.  `pre`, when given, holds the residual values of this chunk fetched earlier.
 __device__ __forceinline__ void epi_apply_row32(const Epilogue& e, int64_t row, int col0, int n, float* acc32,
                                                 const ResChunk* pre = nullptr) {
-  if (e.bias != nullptr) {
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (col0 + j < n) acc32[j] += __half2float(e.bias[col0 + j]);
-  }
+  if (e.bias != nullptr) epi_add_bias32(e.bias, col0, n, acc32);
   if (e.act == DTAS_ACT_GELU) {
 #pragma unroll
-    for (int g = 0; g < 32; g += 8) gelu_erf_n<8>(acc32 + g);
+    for (int g = 0; g < 32; g += 8) gelu_erf_n<8>(acc32 + g);   // groups of 4 time the same, of 16 slower
   }
   if (pre != nullptr) {
     epi_add_vec32(pre->v[0], acc32);

@@ -171,6 +171,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// After a wait: makes later uses of the loaded registers depend on the wait.  Where a load is issued well
+// before its wait (to be in flight during other work), nothing else keeps arithmetic on its
+// destination registers from being scheduled ahead of the wait.
+__device__ __forceinline__ void tmem_ld_landed(uint32_t* r) {
+  asm volatile("" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                    "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]));
+  asm volatile("" : "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]),
+                    "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]),
+                    "+r"(r[30]), "+r"(r[31]));
+}
 __device__ __forceinline__ void epilogue_bar_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
 }
@@ -443,10 +453,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               float f[32];
 #pragma unroll
               for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
-              if (a.epi.bias != nullptr) {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) f[j] += __half2float(a.epi.bias[colb + cc * 32 + j]);
-              }
+              if (a.epi.bias != nullptr) epi_add_bias32(a.epi.bias, colb + cc * 32, a.n, f);
 #pragma unroll
               for (int q = 0; q < 4; ++q) stage[lane * kCpr + ((cc * 4 + q) ^ (lane & 7))] = epi_pack8(f + 8 * q);
             }
@@ -1336,11 +1343,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairMaxThreads, 1)
             uint32_t r[32];
             tmem_ld32(t_addr + (c + cc) * 32, r);
             tmem_ld_wait();
-            if (a.epi.bias != nullptr) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                r[j] = __float_as_uint(__uint_as_float(r[j]) + __half2float(a.epi.bias[colb + cc * 32 + j]));
-            }
+            if (a.epi.bias != nullptr) epi_add_bias32(a.epi.bias, colb + cc * 32, a.n, reinterpret_cast<float*>(r));
             float f[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
@@ -1352,30 +1355,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairMaxThreads, 1)
           __syncwarp();
         }
       } else {
-      // Residual rows are fetched two chunks ahead of their use.
-      ResChunk r_next, r_after;
-      const int colb = col_base + c_begin * 32;
-      if (row_ok && epi_can_prefetch(a.epi, colb, a.n)) epi_prefetch_res32(a.epi, row, colb, r_next);
-      if (row_ok && epi_can_prefetch(a.epi, colb + 32, a.n)) epi_prefetch_res32(a.epi, row, colb + 32, r_after);
-#pragma unroll 1
-      for (int c = c_begin; c < c_end; ++c) {
-        uint32_t r[32];
-        tmem_ld32(t_addr + c * 32, r);
+      uint4* stage_f = reinterpret_cast<uint4*>(gen_base + (store_stage - base)) + (warp - 2) * (32 * 8);
+      // One chunk of 32 columns: the tail's arithmetic, then - fp16 results - through shared memory in
+      // blocks of 64 columns (two chunks), which leave as whole 128-byte rows; an fp32 output, ragged
+      // edges and unaligned buffers are stored from the registers.
+      auto finish_chunk = [&](int c, const uint32_t* r, const ResChunk* res) {
         const int col0 = col_base + c * 32;
-        const ResChunk r_now = r_next;
-        r_next = r_after;
-        if (row_ok && c + 2 < c_end && epi_can_prefetch(a.epi, col0 + 64, a.n)) epi_prefetch_res32(a.epi, row, col0 + 64, r_after);
-        tmem_ld_wait();
-        // fp16 results go through shared memory in blocks of 64 columns (two chunks) and leave as whole
-        // 128-byte rows; an fp32 output, ragged edges and unaligned buffers are stored from the registers
         const int blk0 = col_base + (c & ~1) * 32;
         const bool staged_f = DTAS_PAIR_STAGED_STORE && a.vec_store && !a.epi.out_f32 && blk0 + 64 <= a.n && (c | 1) < c_end;
         float f[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
         if (staged_f) {
-          uint4* stage_f = reinterpret_cast<uint4*>(gen_base + (store_stage - base)) + (warp - 2) * (32 * 8);
-          if (row_ok) epi_apply_row32(a.epi, row, col0, a.n, f, epi_can_prefetch(a.epi, col0, a.n) ? &r_now : nullptr);
+          if (row_ok) epi_apply_row32(a.epi, row, col0, a.n, f, res);
 #pragma unroll
           for (int q = 0; q < 4; ++q) stage_f[lane * 8 + (((c & 1) * 4 + q) ^ (lane & 7))] = epi_pack8(f + 8 * q);
           if (c & 1) {
@@ -1384,8 +1376,46 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairMaxThreads, 1)
             __syncwarp();
           }
         } else if (row_ok && col0 < a.n) {
-          epi_store_row32(a.epi, a.y, a.ldy, a.vec_store, row, col0, a.n, f,
-                          epi_can_prefetch(a.epi, col0, a.n) ? &r_now : nullptr, &a.peers);
+          epi_store_row32(a.epi, a.y, a.ldy, a.vec_store, row, col0, a.n, f, res, &a.peers);
+        }
+      };
+      if (a.epi.res1 == nullptr) {
+        // Activation without residuals: the accumulator words of the next chunk are on their way from
+        // tensor memory while the current chunk is worked on (two sets of registers in turn).
+        uint32_t ra[32], rb[32];
+        tmem_ld32(t_addr + c_begin * 32, ra);
+        tmem_ld_wait();
+        tmem_ld_landed(ra);
+#pragma unroll 1
+        for (int c = c_begin; c < c_end; c += 2) {        // c_begin is even: a pair of chunks is a staged block
+          const bool second = c + 1 < c_end;
+          if (second) tmem_ld32(t_addr + (c + 1) * 32, rb);
+          finish_chunk(c, ra, nullptr);
+          tmem_ld_wait();
+          tmem_ld_landed(rb);
+          if (second) {
+            if (c + 2 < c_end) tmem_ld32(t_addr + (c + 2) * 32, ra);
+            finish_chunk(c + 1, rb, nullptr);
+            tmem_ld_wait();
+            tmem_ld_landed(ra);
+          }
+        }
+      } else {
+        // Residual rows are fetched two chunks ahead of their use.
+        ResChunk r_next, r_after;
+        const int colb = col_base + c_begin * 32;
+        if (row_ok && epi_can_prefetch(a.epi, colb, a.n)) epi_prefetch_res32(a.epi, row, colb, r_next);
+        if (row_ok && epi_can_prefetch(a.epi, colb + 32, a.n)) epi_prefetch_res32(a.epi, row, colb + 32, r_after);
+#pragma unroll 1
+        for (int c = c_begin; c < c_end; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_addr + c * 32, r);
+          const int col0 = col_base + c * 32;
+          const ResChunk r_now = r_next;
+          r_next = r_after;
+          if (row_ok && c + 2 < c_end && epi_can_prefetch(a.epi, col0 + 64, a.n)) epi_prefetch_res32(a.epi, row, col0 + 64, r_after);
+          tmem_ld_wait();
+          finish_chunk(c, r, epi_can_prefetch(a.epi, col0, a.n) ? &r_now : nullptr);
         }
       }
       }
