@@ -22,6 +22,8 @@ def main():
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--bn", type=int, default=0, help="gemm: force the tile width (0 = planner)")
     ap.add_argument("--split-k", type=int, default=0, help="gemm: force the split factor (0 = planner)")
+    ap.add_argument("--tail", default="none", choices=["none", "bias", "gelu", "res2"],
+                    help="gemm: what is fused behind the product (bias; bias + erf-GELU; bias + two residuals)")
     a = ap.parse_args()
     dev = torch.device("cuda:0")
     f16 = torch.float16
@@ -45,7 +47,14 @@ def main():
         _abi.check(_abi.lib().dtas_gemm_set_override(a.bn, a.split_k))
         x, w = torch.randn(m, k, device=dev, dtype=f16), torch.randn(n, k, device=dev, dtype=f16) * 0.02
         y = torch.empty(m, n, device=dev, dtype=f16)
-        fn = lambda: ops.gemm_nt(x, w, y)  # noqa: E731
+        kw = {}
+        if a.tail != "none":
+            kw["bias"] = torch.randn(n, device=dev, dtype=f16)
+        if a.tail == "gelu":
+            kw["act"] = "gelu"
+        if a.tail == "res2":
+            kw["res1"], kw["res2"] = torch.randn(m, n, device=dev, dtype=f16), torch.randn(m, n, device=dev, dtype=f16)
+        fn = lambda: ops.gemm_nt(x, w, y, **kw)  # noqa: E731
     fn()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

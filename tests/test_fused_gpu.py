@@ -115,6 +115,28 @@ def test_gemm_fused_unaligned_falls_back(cuda_device):
         util.assert_matmul_close(got, expected(host, t).astype(np.float32), f"gemm res2 m={m} n={n} k={k}")
 
 
+@pytest.mark.parametrize("bn", [128, 512])
+@pytest.mark.parametrize("tail", ["bias", "gelu"])
+def test_gemm_bias_at_an_odd_address(cuda_device, tail, bn):
+    """The row-wise tails read the bias with 16-byte loads where its address allows; a bias that starts one
+    element into a buffer takes the two-byte loads and gives the same result bit for bit (single-CTA tiles
+    and the two-CTA kernel, plain and GELU tails, ragged last column chunk)."""
+    t = TAILS[tail]
+    m, n, k = 300, 1064, 520
+    host, dev = operands(m, n, k, t, 3100 + bn, cuda_device)
+    shifted = torch.empty(n + 1, dtype=torch.float16, device=cuda_device)
+    shifted[1:] = dev[2]
+    lib = _abi.lib()
+    try:
+        _abi.check(lib.dtas_gemm_set_override(bn, 1))
+        got = run_gemm(dev, t, m, n, cuda_device)
+        got_shifted = run_gemm((dev[0], dev[1], shifted[1:], dev[3], dev[4]), t, m, n, cuda_device)
+    finally:
+        lib.dtas_gemm_set_override(0, 0)
+    util.assert_matmul_close(got, expected(host, t).astype(np.float32), f"gemm {tail} bn={bn}")
+    util.assert_bit_exact(got_shifted, got, f"gemm {tail} bn={bn}, bias one element into its buffer")
+
+
 def test_gemm_fused_linearity_in_residual(cuda_device):
     """Full-size property: y(res1) - y(0) == res1 up to fp16 rounding, at m=1024, N=K=4096."""
     m, n, k = 1024, 4096, 4096
