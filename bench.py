@@ -321,7 +321,7 @@ def fused_points(dev, peaks):
 GATHER_POINTS = [("gemm", 8192, 22016, 4096), ("gemm", 64, 4096, 4096), ("gemv", 1, 32000, 4096)]
 
 
-def gather_points(rank, world, dev, barrier):
+def gather_points(rank, world, dev, barrier, multicast=True):
     """N > 1 only: what a caller pays who needs the whole Y on every rank.  Per point the kernel
     alone (this rank's column slab, written into its slot of the [g, m, N/g] buffer) and the
     kernel followed by one NCCL all-gather of that buffer, and the same result by pushing row
@@ -365,20 +365,24 @@ def gather_points(rank, world, dev, barrier):
         local_us = timed(lambda i: lins[i % copies].forward_local(x, out=buf[rank]))
         gathered_us = timed(lambda i: lins[i % copies].forward_gathered(x, buf=buf))
         pushed = {}
-        for engine in ("kernel", "copy", "epilogue"):
-            if engine == "epilogue" and m < 129:
-                pushed[engine] = None          # the GEMM that stores to the peers itself needs 129 rows
-                continue
+        pbuf_has_multicast = False
+        for engine in ("kernel", "copy", "epilogue", "multicast"):
+            pushed[engine] = None
+            if engine in ("epilogue", "multicast") and m < 129:
+                continue                       # the GEMM that stores to the peers itself needs 129 rows
+            if engine == "multicast" and not (multicast and pbuf_has_multicast):
+                continue                       # no multicast mapping of symmetric memory on this system
             pbuf = PeerGatherBuffer(world, m, n_local, f16, dev, engine=engine)
+            pbuf_has_multicast = pbuf.has_multicast()
             pushed[engine] = timed(lambda i: lins[i % copies].forward_pushed(x, pbuf, min_push_bytes=0))
-            if engine == "epilogue":
+            if engine in ("epilogue", "multicast"):
                 # what arrived in the peers' slots of this rank's buffer is what an all-gather delivers
                 want = lins[0].forward_gathered(x).clone()
                 got = lins[0].forward_pushed(x, pbuf, min_push_bytes=0)
                 torch.cuda.synchronize()
                 flag = torch.tensor([int(torch.equal(got, want))], device=dev, dtype=torch.int32)
                 dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-                pushed["epilogue_equals_all_gather"] = bool(flag.item())
+                pushed[engine + "_equals_all_gather"] = bool(flag.item())
             del pbuf
         out.append({"op": op, "m": m, "n": n, "k": k, "kernel_us": round(local_us, 2),
                     "kernel_plus_all_gather_us": round(gathered_us, 2),
@@ -386,6 +390,8 @@ def gather_points(rank, world, dev, barrier):
                     "kernel_plus_copy_engine_push_us": round(pushed["copy"], 2),
                     "gemm_storing_to_peers_us": None if pushed["epilogue"] is None else round(pushed["epilogue"], 2),
                     "gemm_storing_to_peers_equals_all_gather": pushed.get("epilogue_equals_all_gather"),
+                    "gemm_storing_through_multicast_us": None if pushed["multicast"] is None else round(pushed["multicast"], 2),
+                    "gemm_storing_through_multicast_equals_all_gather": pushed.get("multicast_equals_all_gather"),
                     "gather_bytes_per_rank": 2 * m * n_local, "mode": "eager calls, max over ranks"})
         del lins, buf, x
         torch.cuda.empty_cache()

@@ -58,6 +58,8 @@ PROTOTYPES = {
     "dtas_set_pdl": (_i, [_i]),
     "dtas_peer_push": (_i, [_p, ctypes.POINTER(ctypes.c_void_p), _i, _i64, _i, _p]),
     "dtas_gemm_nt_scatter": (_i, [_p, _p, _p, _p, ctypes.POINTER(ctypes.c_void_p), _i, _i64, _i64, _i64, _i64, _i, _i, _p]),
+    "dtas_gemm_nt_scatter_multicast": (_i, [_p, _p, _p, _p, ctypes.POINTER(ctypes.c_void_p), _i, _p, _i64, _i64, _i64, _i64,
+                                            _i, _i, _p]),
     "dtas_last_error": (ctypes.c_char_p, []),
     "dtas_launch_count": (_i64, []),
     "dtas_poll_status": (_i, [_i]),

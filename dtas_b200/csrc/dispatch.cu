@@ -297,6 +297,12 @@ int dtas_gemm_nt_fused(const void* x, const void* w, const void* bias, const voi
 
 int dtas_gemm_nt_scatter(const void* x, const void* w, const void* bias, void* y, void* const* peer_ys, int n_peers,
                          int64_t m, int64_t n, int64_t k, int64_t ldy, int dtype, int device, void* stream) {
+  return dtas_gemm_nt_scatter_multicast(x, w, bias, y, peer_ys, n_peers, nullptr, m, n, k, ldy, dtype, device, stream);
+}
+
+int dtas_gemm_nt_scatter_multicast(const void* x, const void* w, const void* bias, void* y, void* const* peer_ys,
+                                   int n_peers, void* y_multicast, int64_t m, int64_t n, int64_t k, int64_t ldy,
+                                   int dtype, int device, void* stream) {
   DTAS_NONNULL("gemm_scatter", x);
   DTAS_NONNULL("gemm_scatter", w);
   DTAS_NONNULL("gemm_scatter", y);
@@ -313,6 +319,12 @@ int dtas_gemm_nt_scatter(const void* x, const void* w, const void* bias, void* y
     if (peer_ys[j] == nullptr) DTAS_FAIL(DTAS_EINVAL, "gemm_scatter: peer_ys[%d] is null", j);
     if (peer_ys[j] == y) DTAS_FAIL(DTAS_EINVAL, "gemm_scatter: peer_ys[%d] is y itself", j);
     peers.y[j] = peer_ys[j];
+  }
+  if (y_multicast != nullptr) {
+    if ((reinterpret_cast<uintptr_t>(y_multicast) & 15) != 0 || (reinterpret_cast<uintptr_t>(y) & 15) != 0 || (ldy & 7) != 0)
+      DTAS_FAIL(DTAS_EALIGN, "gemm_scatter: the multicast address, y and its row stride must be 16-byte aligned");
+    if (y_multicast == y) DTAS_FAIL(DTAS_EINVAL, "gemm_scatter: y_multicast is y itself");
+    peers.mc = y_multicast;
   }
   Call c;
   int rc;

@@ -32,9 +32,13 @@ struct Epilogue {
 // every stored vector is stored again.  With the output columns of a GEMM sharded over g GPUs these are
 // the places of this rank's slab in the other ranks' gather buffers (peer memory mapped into this
 // process), so the gather rides on the epilogue of the GEMM tile by tile instead of following it.
+// `mc`, when set, is the address of the same slab in a multicast mapping that covers this GPU's buffer
+// and every peer's (an NVLink SHARP multicast object): one multimem.st there lands in all of them, the
+// switch doing the fan-out, so whole staged blocks leave as one store per vector instead of 1 + n.
 struct PeerOut {
   void* y[DTAS_MAX_PEERS] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   int n = 0;
+  void* mc = nullptr;
 };
 
 // Host and device: true when finishing an element costs more than a bias add and a store.
@@ -266,6 +270,13 @@ __device__ __forceinline__ void epi_apply_row32(const Epilogue& e, int64_t row, 
     if (e.res2 != nullptr) epi_add_res32(e.res2, row * e.ldr, col0, n, e.vec_res, acc32);
   }
 }
+// 16 bytes (eight fp16 values) to a multicast address: stored into every buffer the mapping covers.
+__device__ __forceinline__ void epi_multimem_st16(void* addr, const uint4& v) {
+  asm volatile("multimem.st.weak.global.v4.f16x2 [%0], {%1, %2, %3, %4};"
+               :
+               : "l"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
 // Eight fp32 values -> one 16-byte vector of fp16.
 __device__ __forceinline__ uint4 epi_pack8(const float* f) {
   uint4 v;
@@ -296,8 +307,12 @@ __device__ __forceinline__ void epi_store_staged_block(const uint4* stage, int l
     if (grow < m) {
       const uint4 v = stage[rl * CPR + (ch ^ (rl & 7))];
       const int64_t off = grow * ldy + col0 + ch * 8;
-      *reinterpret_cast<uint4*>(static_cast<__half*>(y) + off) = v;
-      for (int p = 0; p < peers.n; ++p) *reinterpret_cast<uint4*>(static_cast<__half*>(peers.y[p]) + off) = v;
+      if (peers.mc != nullptr) {
+        epi_multimem_st16(static_cast<__half*>(peers.mc) + off, v);     // this GPU's copy included
+      } else {
+        *reinterpret_cast<uint4*>(static_cast<__half*>(y) + off) = v;
+        for (int p = 0; p < peers.n; ++p) *reinterpret_cast<uint4*>(static_cast<__half*>(peers.y[p]) + off) = v;
+      }
     }
   }
 }

@@ -150,11 +150,14 @@ class ColumnShardedLinear:
         pbuf.used = True
         if m * self.n_local * pbuf.local.element_size() < min_push_bytes:
             return self.forward_gathered(x, buf=pbuf.local, res1=res1, res2=res2)
-        if pbuf.engine == "epilogue" and self.world > 1 and m >= 129 and res1 is None and self.act is None \
-                and self._compute is None:
-            # one launch: the GEMM's own epilogue stores every finished tile into the peers' buffers
+        if pbuf.engine in ("epilogue", "multicast") and self.world > 1 and m >= 129 and res1 is None \
+                and self.act is None and self._compute is None:
+            # one launch: the GEMM's own epilogue stores every finished tile into the peers' buffers - with
+            # one store per peer, or ("multicast") with one store that the NVLink switch fans out
             from . import ops
-            ops.gemm_nt_scatter(x, self.w, pbuf.local[self.rank], [p[self.rank] for p in pbuf.peers], bias=self.bias)
+            mine = pbuf.local[self.rank]
+            ops.gemm_nt_scatter(x, self.w, mine, [p[self.rank] for p in pbuf.peers], bias=self.bias,
+                                multicast=pbuf.multicast_address(mine) if pbuf.engine == "multicast" else 0)
             pbuf.barrier()
             return pbuf.local
         blocks = max(1, m // max(1, block_rows))
@@ -198,16 +201,17 @@ class PeerGatherBuffer:
         import torch.distributed._symmetric_memory as symm
         if engine == "auto":
             engine = "epilogue"
-        if engine not in ("kernel", "copy", "epilogue"):
-            raise ValueError("engine is 'auto', 'kernel' (this library's push kernel), 'copy' (cudaMemcpyAsync per peer) "
-                             "or 'epilogue' (the GEMM stores to the peers itself; other cases fall back to 'copy')")
+        if engine not in ("kernel", "copy", "epilogue", "multicast"):
+            raise ValueError("engine is 'auto', 'kernel' (this library's push kernel), 'copy' (cudaMemcpyAsync per peer), "
+                             "'epilogue' (the GEMM stores to the peers itself; other cases fall back to 'copy') or "
+                             "'multicast' ('epilogue' with one multimem.st per vector, fanned out by the NVLink switch)")
         group = group if group is not None else dist.group.WORLD
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = world
         self.engine = engine
         # how row blocks travel when the GEMM cannot store to the peers itself
-        self.push_engine = engine if engine != "epilogue" else ("copy" if world <= 4 else "kernel")
+        self.push_engine = engine if engine not in ("epilogue", "multicast") else ("copy" if world <= 4 else "kernel")
         shape = (world, m, n_local)
         self.local = symm.empty(shape, dtype=dtype, device=device)
         self.handle = symm.rendezvous(self.local, group)
@@ -218,6 +222,22 @@ class PeerGatherBuffer:
         self.side = torch.cuda.Stream(device=device)
         self.token = torch.zeros(1, dtype=torch.float32, device=device)
         self.used = False
+        if engine == "multicast" and not self.has_multicast():
+            raise RuntimeError("PeerGatherBuffer: this allocation has no multicast mapping (no NVLink switch multicast "
+                               "on this system, or it is disabled); use engine='epilogue'")
+
+    def has_multicast(self) -> bool:
+        """Whether the symmetric allocation is also mapped through an NVLink multicast object."""
+        return int(getattr(self.handle, "multicast_ptr", 0) or 0) != 0
+
+    def multicast_address(self, view: torch.Tensor) -> int:
+        """Address of `view` (a view of this rank's buffer) in the multicast mapping: a store there lands
+        at the same offset of every rank's buffer."""
+        base = int(self.handle.buffer_ptrs[self.handle.rank])
+        off = view.data_ptr() - base
+        if not (0 <= off < int(self.handle.buffer_size)):
+            raise ValueError("multicast_address: the view does not lie in this rank's symmetric buffer")
+        return int(self.handle.multicast_ptr) + off
 
     def push(self, slot: int, r0: int, r1: int, after: "torch.cuda.Stream") -> None:
         """Rows [r0, r1) of this rank's slot to every peer, on the side stream, behind the work

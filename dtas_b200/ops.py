@@ -240,11 +240,14 @@ def gemm_nt(x, w, out, bias=None, res1=None, res2=None, act=None):
     return out
 
 
-def gemm_nt_scatter(x, w, out, peers, bias=None):
+def gemm_nt_scatter(x, w, out, peers, bias=None, multicast=0):
     """out[m, N] = x[m, K] @ w[N, K]^T (+ bias), and every stored vector of `out` again into each tensor of
     `peers`: views, on this device, with out's shape and row stride - the place of this rank's column
     slab in the other ranks' gather buffers (peer memory).  One launch; the stores to the peers leave
     from the GEMM's epilogue tile by tile.  Run a barrier across ranks before a gathered buffer is read.
+    `multicast`, when not 0, is the address of out's slab in a multicast mapping that covers this GPU's
+    buffer and every peer's (PeerGatherBuffer.multicast_address): whole blocks then leave as one
+    multimem.st per vector and the NVLink switch stores them into every buffer.
     Raises DtasError(EUNSUPPORTED) below 129 rows (use gemm_nt and peer_push there)."""
     import ctypes
     m, k = _rows_cols(x, "gemm_scatter")
@@ -265,8 +268,8 @@ def gemm_nt_scatter(x, w, out, peers, bias=None):
         raise _abi.DtasError(_abi.EINVAL, "gemm_scatter: bias must be a contiguous fp16 vector of N elements")
     dev = x.device.index if x.device.index is not None else torch.cuda.current_device()
     ptrs = (ctypes.c_void_p * len(peers))(*[p.data_ptr() for p in peers])
-    _chk(_lib().dtas_gemm_nt_scatter(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), ptrs, len(peers), m, n, k,
-                                     ldy, _abi.F16, dev, _raw_stream(dev)))
+    _chk(_lib().dtas_gemm_nt_scatter_multicast(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), ptrs, len(peers),
+                                               int(multicast) or None, m, n, k, ldy, _abi.F16, dev, _raw_stream(dev)))
     return out
 
 

@@ -234,6 +234,19 @@ int dtas_gemm_nt_scatter(const void* x, const void* w, const void* bias, void* y
                          int n_peers, int64_t m, int64_t n, int64_t k, int64_t ldy, int dtype, int device,
                          void* stream);
 
+/* dtas_gemm_nt_scatter with the fan-out done by the NVLink switch (no counterpart in the reference).
+ * `y_multicast` is the address of Y's slab in a multicast mapping that covers this GPU's gather buffer and
+ * every peer's at the same offset (CUDA multicast object / NVLink SHARP; in PyTorch the multicast_ptr of
+ * a symmetric-memory allocation plus the slab's offset).  Whole 32-row blocks of the output then leave as
+ * one multimem.st per 16-byte vector, which the switch stores into every buffer of the mapping - this
+ * GPU's own included - instead of one local and n_peers peer stores; ragged edges still go through
+ * `y` and `peer_ys`, which must be given as for dtas_gemm_nt_scatter.  y_multicast == NULL is
+ * dtas_gemm_nt_scatter.  y, y_multicast and ldy * 2 bytes must be multiples of 16 (DTAS_EALIGN).  The
+ * caller's barrier across ranks before the gathered buffer is read stands.                              */
+int dtas_gemm_nt_scatter_multicast(const void* x, const void* w, const void* bias, void* y, void* const* peer_ys,
+                                   int n_peers, void* y_multicast, int64_t m, int64_t n, int64_t k, int64_t ldy,
+                                   int dtype, int device, void* stream);
+
 /* ---- bookkeeping ---------------------------------------------------------
  * dtas_last_error : message of the last failing call on this thread ("" if none).
  * dtas_launch_count: kernels launched by this library since load (all threads).

@@ -80,8 +80,15 @@ def _worker(rank, world, port, results):
             ok[("fused", m)] = err <= 2e-2 * want.float().abs().max().item()
         # the gather without a collective on the data: row blocks pushed into the peers' buffers
         from dtas_b200.dist import PeerGatherBuffer
-        for engine in ("kernel", "copy", "epilogue"):
-            for (m, n, k, block) in [(1, 4096, 1024, 2048), (40, 2048, 1024, 2048), (2500, 2048, 512, 1024)]:
+        probe = PeerGatherBuffer(world, 8, 8, torch.float16, dev)
+        engines = ("kernel", "copy", "epilogue") + (("multicast",) if probe.has_multicast() else ())
+        ok[("multicast mapping present", probe.has_multicast())] = True      # recorded, not required
+        del probe
+        for engine in engines:
+            # the last shape has a ragged last column chunk per rank (1064 = 8 x 128 + 40): whole blocks
+            # leave through the staged path (and, "multicast", through the switch), the rest from registers
+            for (m, n, k, block) in [(1, 4096, 1024, 2048), (40, 2048, 1024, 2048), (2500, 2048, 512, 1024),
+                                     (300, 2128, 512, 2048)]:
                 w = seeded_normal((n, k), 22, "float16", scale=0.02).to(dev)
                 b = seeded_normal((n,), 23, "float16", scale=0.5).to(dev)
                 lin = ColumnShardedLinear(w, n, bias=b)
@@ -95,13 +102,13 @@ def _worker(rank, world, port, results):
                     ops.poll_status(rank)
                     same = same and bool(torch.equal(got, want))
                 ok[("pushed", engine, m)] = same
-                if engine == "epilogue" and m >= 129:
+                if engine in ("epilogue", "multicast") and m >= 129:
                     # without residuals the GEMM itself stores to the peers (one launch, one barrier)
                     x = seeded_normal((m, k), 41, "float16").to(dev)
                     want = lin.forward_gathered(x).clone()
                     got = lin.forward_pushed(x, pbuf, min_push_bytes=0)
                     ops.poll_status(rank)
-                    ok[("scattered", m)] = bool(torch.equal(got, want))
+                    ok[("scattered", engine, m)] = bool(torch.equal(got, want))
                 del pbuf
         a = seeded_normal((7, 11008), 3, "float16").to(dev)
         b = seeded_normal((7, 11008), 4, "float16").to(dev)

@@ -85,3 +85,23 @@ def test_gemm_scatter_writes_every_peer(cuda_device, m, n, k, n_peers):
     small = torch.empty((64, n), dtype=torch.float16, device=cuda_device)
     with pytest.raises(_abi.DtasError):
         ops.gemm_nt_scatter(x[:64], w, small, [torch.empty_like(small)])
+
+
+def test_gemm_scatter_multicast_argument_errors(cuda_device):
+    """dtas_gemm_nt_scatter_multicast refuses, before any launch, a multicast address that is y itself or
+    not 16-byte aligned.  (The route itself needs an NVLink multicast mapping over several GPUs: it is
+    covered by the two-GPU test of the gather engines.)"""
+    m, n, k = 256, 256, 256
+    x = torch.zeros((m, k), dtype=torch.float16, device=cuda_device)
+    w = torch.zeros((n, k), dtype=torch.float16, device=cuda_device)
+    y = torch.empty((m, n), dtype=torch.float16, device=cuda_device)
+    peer = torch.empty_like(y)
+    other = torch.empty((m * n + 8,), dtype=torch.float16, device=cuda_device)
+    before = _abi.launch_count()
+    with pytest.raises(_abi.DtasError) as e:
+        ops.gemm_nt_scatter(x, w, y, [peer], multicast=y.data_ptr())
+    assert e.value.code == _abi.EINVAL
+    with pytest.raises(_abi.DtasError) as e:
+        ops.gemm_nt_scatter(x, w, y, [peer], multicast=other.data_ptr() + 2)
+    assert e.value.code == _abi.EALIGN
+    assert _abi.launch_count() == before
