@@ -321,7 +321,7 @@ def fused_points(dev, peaks):
 GATHER_POINTS = [("gemm", 8192, 22016, 4096), ("gemm", 64, 4096, 4096), ("gemv", 1, 32000, 4096)]
 
 
-def gather_points(rank, world, dev, barrier, multicast=True):
+def gather_points(rank, world, dev, barrier, multicast=True, engines=("kernel", "copy", "epilogue")):
     """N > 1 only: what a caller pays who needs the whole Y on every rank.  Per point the kernel
     alone (this rank's column slab, written into its slot of the [g, m, N/g] buffer) and the
     kernel followed by one NCCL all-gather of that buffer, and the same result by pushing row
@@ -362,18 +362,20 @@ def gather_points(rank, world, dev, barrier, multicast=True):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             return float(t.item())
 
-        local_us = timed(lambda i: lins[i % copies].forward_local(x, out=buf[rank]))
-        gathered_us = timed(lambda i: lins[i % copies].forward_gathered(x, buf=buf))
+        if engines != ("multicast",):
+            local_us = timed(lambda i: lins[i % copies].forward_local(x, out=buf[rank]))
+            gathered_us = timed(lambda i: lins[i % copies].forward_gathered(x, buf=buf))
         pushed = {}
-        pbuf_has_multicast = False
-        for engine in ("kernel", "copy", "epilogue", "multicast"):
+        for engine in engines:
             pushed[engine] = None
             if engine in ("epilogue", "multicast") and m < 129:
                 continue                       # the GEMM that stores to the peers itself needs 129 rows
-            if engine == "multicast" and not (multicast and pbuf_has_multicast):
-                continue                       # no multicast mapping of symmetric memory on this system
-            pbuf = PeerGatherBuffer(world, m, n_local, f16, dev, engine=engine)
-            pbuf_has_multicast = pbuf.has_multicast()
+            pbuf = PeerGatherBuffer(world, m, n_local, f16, dev, engine="epilogue" if engine == "multicast" else engine)
+            if engine == "multicast":
+                if not pbuf.has_multicast():   # no multicast mapping of symmetric memory on this system
+                    del pbuf
+                    continue
+                pbuf.engine = "multicast"
             pushed[engine] = timed(lambda i: lins[i % copies].forward_pushed(x, pbuf, min_push_bytes=0))
             if engine in ("epilogue", "multicast"):
                 # what arrived in the peers' slots of this rank's buffer is what an all-gather delivers
@@ -384,17 +386,28 @@ def gather_points(rank, world, dev, barrier, multicast=True):
                 dist.all_reduce(flag, op=dist.ReduceOp.MIN)
                 pushed[engine + "_equals_all_gather"] = bool(flag.item())
             del pbuf
+        if engines == ("multicast",):
+            return pushed
         out.append({"op": op, "m": m, "n": n, "k": k, "kernel_us": round(local_us, 2),
                     "kernel_plus_all_gather_us": round(gathered_us, 2),
                     "kernel_plus_peer_push_us": round(pushed["kernel"], 2),
                     "kernel_plus_copy_engine_push_us": round(pushed["copy"], 2),
                     "gemm_storing_to_peers_us": None if pushed["epilogue"] is None else round(pushed["epilogue"], 2),
                     "gemm_storing_to_peers_equals_all_gather": pushed.get("epilogue_equals_all_gather"),
-                    "gemm_storing_through_multicast_us": None if pushed["multicast"] is None else round(pushed["multicast"], 2),
-                    "gemm_storing_through_multicast_equals_all_gather": pushed.get("multicast_equals_all_gather"),
+                    "gemm_storing_through_multicast_us": None, "gemm_storing_through_multicast_equals_all_gather": None,
                     "gather_bytes_per_rank": 2 * m * n_local, "mode": "eager calls, max over ranks"})
         del lins, buf, x
         torch.cuda.empty_cache()
+    if engines != ("multicast",) and multicast and out and GATHER_POINTS[0][1] >= 129 and GATHER_POINTS[0][2] % world == 0:
+        # the route through the switch's multicast last, on the first point only, and on its own: whatever
+        # happens to it, the figures above stand
+        try:
+            mc = gather_points(rank, world, dev, barrier, engines=("multicast",))
+            if mc.get("multicast") is not None:
+                out[0]["gemm_storing_through_multicast_us"] = round(mc["multicast"], 2)
+                out[0]["gemm_storing_through_multicast_equals_all_gather"] = mc.get("multicast_equals_all_gather")
+        except Exception as e:  # noqa: BLE001
+            out[0]["gemm_storing_through_multicast_error"] = f"{type(e).__name__}: {e}"[:200]
     return out
 
 
